@@ -1,0 +1,65 @@
+"""One registry from an architecture's name (config.json `architectures[0]`) to its model.
+
+The reference picks its Llama4 engine by "the path is a folder with *.safetensors"
+(src/main.cpp:169-174, src/app/main_helpers.cpp:464-486) and knows no names.
+Here an architecture registers, under each name it answers to, a function that
+reads config.json into its typed configuration and one that turns that
+configuration into a `ModelSpec`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any, Callable
+
+from .llama4 import ConfigError, read_config_json
+from .spec import ModelSpec
+
+
+@dataclass(frozen=True)
+class Architecture:
+    name: str
+    parse_config: Callable[[dict], Any]        # raw config.json dict -> typed configuration
+    build_spec: Callable[[Any], ModelSpec]     # typed configuration -> ModelSpec
+
+
+_ARCHITECTURES: dict[str, Architecture] = {}
+
+
+def register_architecture(arch: Architecture) -> None:
+    _ARCHITECTURES[arch.name] = arch
+
+
+def registered_architectures() -> list[str]:
+    _ensure_builtin()
+    return sorted(_ARCHITECTURES)
+
+
+def get_architecture(name: str) -> Architecture:
+    _ensure_builtin()
+    if name not in _ARCHITECTURES:
+        raise ConfigError(f"architecture '{name}' is not registered; registered: "
+                          + ", ".join(sorted(_ARCHITECTURES)))
+    return _ARCHITECTURES[name]
+
+
+def architecture_of(raw_config: dict) -> Architecture:
+    archs = raw_config.get("architectures")
+    if not archs or not isinstance(archs, list):
+        raise ConfigError("config.json: 'architectures' is missing or empty; registered: "
+                          + ", ".join(registered_architectures()))
+    return get_architecture(archs[0])
+
+
+def spec_from_model_dir(model_dir: str):
+    """(typed configuration, ModelSpec) of the model folder's config.json."""
+    raw = read_config_json(model_dir)
+    arch = architecture_of(raw)
+    cfg = arch.parse_config(raw)
+    spec = arch.build_spec(cfg)
+    spec.validate()
+    return cfg, spec
+
+
+def _ensure_builtin() -> None:
+    # the built-in architectures register themselves on import
+    from ..models import llama4  # noqa: F401

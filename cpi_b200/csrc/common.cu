@@ -1,0 +1,28 @@
+// Error reporting shared by every entry point of the library.
+#include "common.cuh"
+#include <cstring>
+
+namespace cpi {
+static thread_local char g_error[1024] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s: launch failed: %s", what, cudaGetErrorString(e));
+    return 2;
+  }
+  return 0;
+}
+}  // namespace cpi
+
+extern "C" const char* cpi_last_error() { return cpi::g_error; }
+
+// Identifies the build: the loader checks it against the sources it was built from.
+extern "C" int cpi_abi_version() { return 1; }

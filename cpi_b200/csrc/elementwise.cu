@@ -1,0 +1,112 @@
+// Row-wise kernels: token embedding, RMS norm, row gather, expert-output combine.
+//
+// Formulas (file:line of kurulav1/cpi):
+//   embedding   x = Emb[token]                                   src/engine/llama4_cpu_engine.cpp:294-298
+//   rmsnorm     y = x * rsqrt(mean(x^2) + eps) * w, fp32 sums    src/engine/llama4_cpu_engine.cpp:47-62,
+//                                                                src/kernels/kernels.cu:36-99
+// The residual stream is float32 in both precisions; norm outputs take the activation dtype.
+#include "common.cuh"
+
+namespace cpi {
+
+template <typename TT>
+__global__ void embedding_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
+                                 float* __restrict__ out, int hidden, int vocab, int* __restrict__ err) {
+  const int t = blockIdx.x;
+  const int tok = tokens[t];
+  if (tok < 0 || tok >= vocab) {              // never read out of range: flag it and write zeros
+    if (threadIdx.x == 0) atomicExch(err, 1 + t);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = 0.f;
+    return;
+  }
+  const TT* row = table + (size_t)tok * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_f32(row[i]);
+}
+
+// One block per row.  The sum of squares is taken in a fixed order (thread-strided, then a warp
+// tree, then warps in order), so a row's result does not depend on the other rows of the launch.
+template <typename TX, typename TO>
+__global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
+                               const void* __restrict__ w, int w_dtype, TO* __restrict__ out,
+                               long out_stride, int n, float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const TX* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = to_f32(xr[i]);
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+  TO* o = out + (size_t)r * out_stride;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float v = to_f32(xr[i]) * inv;
+    if (w) v *= load_any(w, w_dtype, i);
+    o[i] = from_f32<TO>(v);
+  }
+}
+
+// residual[t] += sum_k y[row_of_slot[t*K + k]] in the order k = 0..K-1.
+template <typename TY>
+__global__ void moe_combine_kernel(float* __restrict__ residual, const TY* __restrict__ y,
+                                   const int* __restrict__ row_of_slot, int top_k, int hidden) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float acc = residual[(size_t)t * hidden + i];
+    for (int k = 0; k < top_k; ++k) {
+      const int r = row_of_slot[t * top_k + k];
+      acc += to_f32(y[(size_t)r * hidden + i]);
+    }
+    residual[(size_t)t * hidden + i] = acc;
+  }
+}
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+  const int t = blockIdx.x;
+  const T* g = gu + (size_t)t * 2 * inter;
+  for (int i = threadIdx.x; i < inter; i += blockDim.x) {
+    const float a = to_f32(g[i]), b = to_f32(g[inter + i]);
+    out[(size_t)t * inter + i] = from_f32<T>(a / (1.0f + expf(-a)) * b);
+  }
+}
+
+}  // namespace cpi
+
+using namespace cpi;
+
+extern "C" int cpi_embedding(const int* tokens, const void* table, int table_dtype, float* out,
+                             int n_tokens, int hidden, int vocab, int* err_flag, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", n_tokens, hidden, vocab);
+  CPI_DISPATCH_DTYPE(table_dtype, TT,
+      embedding_kernel<TT><<<n_tokens, 256, 0, stream>>>(tokens, (const TT*)table, out, hidden, vocab, err_flag));
+  return check_launch("embedding");
+}
+
+extern "C" int cpi_rmsnorm(const void* x, int x_dtype, long x_stride, const int* rows, const void* w,
+                           int w_dtype, void* out, int out_dtype, long out_stride, int n_rows, int n,
+                           float eps, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_REQUIRE(n_rows > 0 && n > 0, "rmsnorm: bad sizes rows=%d n=%d", n_rows, n);
+  const int threads = n <= 256 ? 64 : (n <= 2048 ? 256 : 512);
+  CPI_DISPATCH_DTYPE(x_dtype, TX, CPI_DISPATCH_DTYPE(out_dtype, TO,
+      (rmsnorm_kernel<TX, TO><<<n_rows, threads, 0, stream>>>((const TX*)x, x_stride, rows, w, w_dtype,
+                                                              (TO*)out, out_stride, n, eps))));
+  return check_launch("rmsnorm");
+}
+
+extern "C" int cpi_moe_combine(float* residual, const void* y, int y_dtype, const int* row_of_slot,
+                               int n_tokens, int top_k, int hidden, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_DISPATCH_DTYPE(y_dtype, TY,
+      moe_combine_kernel<TY><<<n_tokens, 256, 0, stream>>>(residual, (const TY*)y, row_of_slot, top_k, hidden));
+  return check_launch("moe_combine");
+}
+
+extern "C" int cpi_swiglu(const void* gate_up, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_DISPATCH_DTYPE(dtype, T, swiglu_kernel<T><<<n_rows, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter));
+  return check_launch("swiglu");
+}

@@ -1,0 +1,226 @@
+"""ctypes bindings of the kernel library: torch tensors in, asynchronous launches on the current stream.
+
+There is no CPU fallback and no library model code behind these functions: if the shared object
+cannot be built or loaded, `load()` raises, and every function below raises with it.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_long, c_float, c_void_p
+
+import torch
+
+from . import build as _build
+
+F32, BF16 = 0, 1
+MODE_STORE, MODE_ADD, MODE_SWIGLU = 0, 1, 2
+WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
+WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
+
+_lib = None
+launch_count = 0          # kernels launched through this module since import (bench reports it)
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def load():
+    global _lib
+    if _lib is None:
+        path = _build.library_path()
+        try:
+            _lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelError(f"cpi_b200: cannot load the kernel library {path}: {e}") from None
+        _lib.cpi_last_error.restype = ctypes.c_char_p
+    return _lib
+
+
+def library_file() -> str:
+    return _build.library_path(build_if_missing=False)
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"cpi_b200 kernels take float32 or bfloat16, not {dt}")
+
+
+def _p(t):
+    return c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _call(name, *args):
+    global launch_count
+    rc = getattr(load(), name)(*args)
+    if rc != 0:
+        raise KernelError(load().cpi_last_error().decode())
+    launch_count += 1
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("cpi_b200 kernels run on CUDA tensors only (there is no CPU path)")
+
+
+def _rowmajor(t, what):
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what}: expected a 2-D tensor with contiguous rows, got shape "
+                          f"{tuple(t.shape)} strides {t.stride()}")
+
+
+# ------------------------------------------------------------------------------------------------
+def embedding(tokens, table, out, err_flag):
+    """out[t, :] = table[tokens[t], :] as float32; a token outside the table sets err_flag[0] = 1 + t."""
+    _need_cuda(tokens, table, out, err_flag)
+    T, H = out.shape
+    assert tokens.dtype == torch.int32 and out.dtype == torch.float32 and out.is_contiguous()
+    assert table.is_contiguous() and table.shape[1] == H
+    _call("cpi_embedding", _p(tokens), _p(table), c_int(dtype_code(table.dtype)), _p(out), c_int(T), c_int(H),
+          c_int(table.shape[0]), _p(err_flag), _stream())
+
+
+def rmsnorm(x, weight, eps, out, rows=None):
+    """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * weight; weight may be None."""
+    _need_cuda(x, weight, out, rows)
+    _rowmajor(x, "rmsnorm x"); _rowmajor(out, "rmsnorm out")
+    n_rows, n = out.shape
+    assert x.shape[1] == n and (rows is not None or x.shape[0] == n_rows)
+    assert rows is None or rows.dtype == torch.int32
+    assert weight is None or (weight.numel() == n and weight.is_contiguous())
+    _call("cpi_rmsnorm", _p(x), c_int(dtype_code(x.dtype)), c_long(x.stride(0)), _p(rows), _p(weight),
+          c_int(F32 if weight is None else dtype_code(weight.dtype)), _p(out), c_int(dtype_code(out.dtype)),
+          c_long(out.stride(0)), c_int(n_rows), c_int(n), c_float(eps), _stream())
+
+
+def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None,
+              row_scale=None, group_offsets=None, n_groups=0, rows_per_group_hint=None):
+    """out[m, n] (+)= sum_k a[a_rows[m] or m, k] * w[g(m)][n, k] on the FP32 pipe (see gemm_simt.cu).
+
+    w is [N, K], or [2N, K] in SWIGLU mode, or [G, N or 2N, K] with group_offsets (int32 [G+1]).
+    """
+    _need_cuda(a, w, out, a_rows, out_rows, row_scale, group_offsets)
+    _rowmajor(a, "gemm a"); _rowmajor(out, "gemm out")
+    K = a.shape[1]
+    if group_offsets is not None:
+        assert w.dim() == 3 and w.is_contiguous() and w.shape[0] == n_groups
+        rows_w, stride_g = w.shape[1], w.shape[1] * w.shape[2]
+    else:
+        _rowmajor(w, "gemm w")
+        rows_w, stride_g = w.shape[0], 0
+    assert w.shape[-1] == K, f"gemm: a has K={K}, w has K={w.shape[-1]}"
+    N = n_out if n_out is not None else (rows_w // 2 if mode == MODE_SWIGLU else rows_w)
+    assert rows_w == (2 * N if mode == MODE_SWIGLU else N)
+    assert out.shape[1] == N
+    M = m_rows if m_rows is not None else (a_rows.numel() if a_rows is not None else a.shape[0])
+    ldw = w.stride(-2)
+    hint = rows_per_group_hint if rows_per_group_hint is not None else M
+    _call("cpi_gemm_simt", _p(a), c_int(dtype_code(a.dtype)), c_long(a.stride(0)), _p(a_rows),
+          _p(w), c_int(dtype_code(w.dtype)), c_long(ldw), c_long(stride_g),
+          _p(out), c_int(dtype_code(out.dtype)), c_long(out.stride(0)), _p(out_rows), _p(row_scale),
+          _p(group_offsets), c_int(n_groups), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(hint), _stream())
+
+
+def qkv_post(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
+             n_heads, n_kv_heads, head_dim, inv_freq=None, interleaved=False, qk_norm=False,
+             norm_before_rope=False, norm_eps=0.0, temperature=None, write_kv=True):
+    """Norm / rotate / scale q and k per head, write q to q_out and k, v into the cache pages."""
+    _need_cuda(qkv, q_out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, inv_freq)
+    _rowmajor(qkv, "qkv_post qkv")
+    T = qkv.shape[0]
+    assert q_out.is_contiguous() and q_out.dtype == qkv.dtype
+    assert k_cache is None or k_cache.dtype == qkv.dtype
+    assert inv_freq is None or (inv_freq.dtype == torch.float32 and inv_freq.numel() == head_dim // 2)
+    fl, sc = (temperature if temperature is not None else (1.0, 0.0))
+    _call("cpi_qkv_post", _p(qkv), c_long(qkv.stride(0)), _p(q_out), _p(k_cache), _p(v_cache),
+          c_int(dtype_code(qkv.dtype)), _p(page_table), c_int(page_table.shape[1]), c_int(page_size),
+          _p(token_seq), _p(token_pos), _p(seq_slot), _p(inv_freq), c_int(int(interleaved)),
+          c_int(int(qk_norm)), c_int(int(norm_before_rope)), c_float(norm_eps),
+          c_int(int(temperature is not None)), c_float(fl), c_float(sc), c_int(T), c_int(n_heads),
+          c_int(n_kv_heads), c_int(head_dim), c_int(int(write_kv)), _stream())
+
+
+def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
+                      n_heads, n_kv_heads, head_dim, window_kind, window_size, scale):
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot)
+    assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype
+    T = q.shape[0]
+    _call("cpi_attention_general", _p(q), _p(out), _p(k_cache), _p(v_cache), c_int(dtype_code(q.dtype)),
+          _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos),
+          _p(seq_slot), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind),
+          c_int(window_size), c_float(scale), _stream())
+
+
+def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None):
+    _need_cuda(h, w, topk_idx, topk_gate, logits_out)
+    _rowmajor(h, "router h")
+    T, H = h.shape
+    E = w.shape[0]
+    assert w.is_contiguous() and w.shape[1] == H
+    assert topk_idx.dtype == torch.int32 and topk_gate.dtype == torch.float32
+    _call("cpi_router_topk", _p(h), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
+          c_int(dtype_code(w.dtype)), _p(logits_out), _p(topk_idx), _p(topk_gate), c_int(T), c_int(H),
+          c_int(E), c_int(top_k), c_int(int(sigmoid_gate)), _stream())
+
+
+def moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot, *, n_tokens, top_k,
+              n_experts):
+    _need_cuda(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot)
+    _call("cpi_moe_lists", _p(topk_idx), _p(topk_gate), _p(group_offsets), _p(row_token), _p(row_scale),
+          _p(row_of_slot), c_int(n_tokens), c_int(top_k), c_int(n_experts), _stream())
+
+
+def moe_combine(residual, y, row_of_slot, *, top_k):
+    _need_cuda(residual, y, row_of_slot)
+    T, H = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and y.is_contiguous()
+    _call("cpi_moe_combine", _p(residual), _p(y), c_int(dtype_code(y.dtype)), _p(row_of_slot), c_int(T),
+          c_int(top_k), c_int(H), _stream())
+
+
+def swiglu(gate_up, out):
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    assert gate_up.shape == (T, 2 * I) and gate_up.is_contiguous() and out.is_contiguous()
+    _call("cpi_swiglu", _p(gate_up), _p(out), c_int(dtype_code(out.dtype)), c_int(T), c_int(I), _stream())
+
+
+def argmax(logits, out):
+    _need_cuda(logits, out)
+    _rowmajor(logits, "argmax logits")
+    assert logits.dtype == torch.float32 and out.dtype == torch.int32
+    R, V = logits.shape
+    _call("cpi_argmax", _p(logits), c_long(logits.stride(0)), c_int(R), c_int(V), _p(out), _stream())
+
+
+def sample(logits, work, temperature, top_k, top_p, uniform, out):
+    _need_cuda(logits, work, temperature, top_k, top_p, uniform, out)
+    _rowmajor(logits, "sample logits")
+    R, V = logits.shape
+    assert logits.dtype == torch.float32 and work.dtype == torch.float32 and work.numel() >= R * V
+    assert temperature.dtype == torch.float32 and top_k.dtype == torch.int32 and top_p.dtype == torch.float32
+    assert uniform.dtype == torch.float32 and out.dtype == torch.int32
+    _call("cpi_sample", _p(logits), c_long(logits.stride(0)), _p(work), c_int(R), c_int(V), _p(temperature),
+          _p(top_k), _p(top_p), _p(uniform), _p(out), _stream())
+
+
+def repetition_penalty(logits, ids, id_offsets, penalty):
+    _need_cuda(logits, ids, id_offsets, penalty)
+    R, V = logits.shape
+    _call("cpi_repetition_penalty", _p(logits), c_long(logits.stride(0)), c_int(R), c_int(V), _p(ids),
+          _p(id_offsets), _p(penalty), _stream())
+
+
+def ban_tokens(logits, ids, id_offsets):
+    _need_cuda(logits, ids, id_offsets)
+    R, V = logits.shape
+    _call("cpi_ban_tokens", _p(logits), c_long(logits.stride(0)), c_int(R), c_int(V), _p(ids), _p(id_offsets),
+          _stream())

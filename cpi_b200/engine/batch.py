@@ -1,0 +1,87 @@
+"""What one step runs: the packed tokens of its sequences and where each token sits.
+
+Every array is int32 on the device, filled from one pinned host buffer with a single copy:
+  tokens[t]     token id                    token_seq[t]  index of its sequence in this step
+  token_pos[t]  absolute position           seq_slot[s]   cache slot of sequence s
+  seq_start[s]  positions cached before     seq_new[s]    tokens the step brings for s
+  want_rows[r]  packed token indices whose logits are asked for
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+
+@dataclass
+class StepBatch:
+    n_tokens: int
+    n_seqs: int
+    n_want: int
+    max_new: int
+    dtype: torch.dtype
+    tokens: torch.Tensor
+    token_seq: torch.Tensor
+    token_pos: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_new: torch.Tensor
+    want_rows: torch.Tensor
+    slots: list
+    starts: list
+    n_new: list
+
+    @property
+    def is_decode(self) -> bool:
+        return self.max_new == 1
+
+
+class BatchStager:
+    """Builds StepBatch objects; owns the pinned host buffer and the device buffer behind them."""
+
+    def __init__(self, device):
+        self.device = torch.device(device)
+        self._cap = 0
+        self._host = self._dev = None
+
+    def _reserve(self, n: int) -> None:
+        if n <= self._cap:
+            return
+        self._cap = max(n, int(self._cap * 1.5), 4096)
+        pin = self.device.type == "cuda"
+        self._host = torch.empty(self._cap, dtype=torch.int32, pin_memory=pin)
+        self._dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+
+    def stage(self, slots, starts, token_lists, wants, dtype) -> StepBatch:
+        B = len(slots)
+        n_new = [len(t) for t in token_lists]
+        T = sum(n_new)
+        R = sum(len(w) for w in wants)
+        total = 3 * T + 3 * B + R
+        self._reserve(total)
+        h = self._host
+        tokens, token_seq, token_pos, want_rows = [], [], [], []
+        base = 0
+        for s, (toks, st, w) in enumerate(zip(token_lists, starts, wants)):
+            n = len(toks)
+            tokens += toks
+            token_seq += [s] * n
+            token_pos += range(st, st + n)
+            want_rows += [base + i for i in w]
+            base += n
+        flat = tokens + token_seq + token_pos + list(slots) + list(starts) + n_new + want_rows
+        h[:total] = torch.tensor(flat, dtype=torch.int32)
+        d = self._dev
+        d[:total].copy_(h[:total], non_blocking=True)
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = d[o:o + n]
+            o += n
+            return v
+
+        return StepBatch(n_tokens=T, n_seqs=B, n_want=R, max_new=max(n_new), dtype=dtype,
+                         tokens=take(T), token_seq=take(T), token_pos=take(T), seq_slot=take(B),
+                         seq_start=take(B), seq_new=take(B), want_rows=take(R),
+                         slots=list(slots), starts=list(starts), n_new=n_new)

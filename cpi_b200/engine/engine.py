@@ -1,0 +1,140 @@
+"""The engine: a loaded model, its cache, and ONE step function.
+
+`step` takes, for each sequence of the batch, its slot, its next tokens and the places among them
+whose logits are wanted.  The sequences of a batch start together (all at position 0, with unequal
+prompt lengths, in one step) and then go on by one token each; a step runs only the tokens it is
+given, against the cache that earlier steps left, as one packed batch without padding.  The
+reference's counterpart is `forward_token(token, position)` for one sequence
+(include/engine/llama4_cuda_engine.hpp:108-116); its "prefill" is a host loop over it
+(src/engine/llama4_cuda_engine.cu:571-580).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from ..cache import CacheManager
+from ..config.registry import architecture_of, spec_from_model_dir
+from ..config.spec import ModelSpec
+from ..csrc import lib as K
+from ..parts import Workspace
+from ..weights import RandomSource, SafetensorsSource
+from .batch import BatchStager
+from .model import DecoderModel
+
+
+def _dtype_of(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        return name
+    table = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}
+    if name not in table:
+        raise ValueError(f"dtype must be bfloat16 or float32, not '{name}'")
+    return table[name]
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+class Engine:
+    def __init__(self, spec: ModelSpec, source, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096,
+                 max_seqs: Optional[int] = None, max_seq_len: Optional[int] = None, page_size: int = 64,
+                 config=None):
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise RuntimeError("cpi_b200 runs on a CUDA device only; there is no CPU path")
+        K.load()                                   # fails loudly when the kernel library is missing
+        torch.cuda.set_device(self.device)
+        self.dtype = _dtype_of(dtype)
+        self.spec, self.config = spec, config
+        self.ws = Workspace(self.device)
+        self.model = DecoderModel(spec, self.dtype, self.device, self.ws)
+        self.model.load(source)
+        kv, state = self.model.cache_requirements()
+        self.cache = CacheManager(kv, state, max_tokens=max_tokens, max_seqs=max_seqs, max_seq_len=max_seq_len,
+                                  page_size=page_size, dtype=self.dtype, device=self.device)
+        self.stager = BatchStager(self.device)
+        self.steps_run = 0
+
+    # ---- construction ----------------------------------------------------------------------------
+    @classmethod
+    def from_model_dir(cls, model_dir: str, **kw) -> "Engine":
+        cfg, spec = spec_from_model_dir(model_dir)
+        src = SafetensorsSource(model_dir)
+        try:
+            return cls(spec, src, config=cfg, **kw)
+        finally:
+            src.close()
+
+    @classmethod
+    def from_random(cls, config_json: dict, seed: int = 0, **kw) -> "Engine":
+        """A model with random weights drawn on the device (nothing is written to disk)."""
+        from .model import tensor_requirements
+        arch = architecture_of(config_json)
+        cfg = arch.parse_config(config_json)
+        spec = arch.build_spec(cfg)
+        src = RandomSource(tensor_requirements(spec), seed, spec.initializer_range)
+        return cls(spec, src, config=cfg, **kw)
+
+    # ---- slots -----------------------------------------------------------------------------------
+    def acquire_slot(self) -> int:
+        return self.cache.acquire()
+
+    def release_slot(self, slot: int) -> None:
+        self.cache.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.cache.lengths[slot]
+
+    # ---- the step --------------------------------------------------------------------------------
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs the entries' tokens as one batch; returns float32 logits [wanted, vocab] on the device,
+        in the order of the entries and of each entry's `want`."""
+        if not entries:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        V = self.spec.vocab_size
+        slots, toks, wants = [], [], []
+        for e in entries:
+            t = [int(x) for x in e.tokens]
+            if not t:
+                raise ValueError(f"slot {e.slot}: a step entry without tokens")
+            for x in t:
+                if not 0 <= x < V:
+                    raise ValueError(f"slot {e.slot}: token id {x} is outside the vocabulary of {V}")
+            w = [int(i) for i in e.want]
+            for i in w:
+                if not 0 <= i < len(t):
+                    raise ValueError(f"slot {e.slot}: wanted place {i} is outside the entry's {len(t)} tokens")
+            slots.append(int(e.slot)); toks.append(t); wants.append(w)
+        n_new = [len(t) for t in toks]
+        starts = self.cache.prepare_step(slots, n_new)
+        batch = self.stager.stage(slots, starts, toks, wants, self.dtype)
+        logits = self.model.run(batch, self.cache)
+        self.cache.commit_step(slots, n_new)
+        self.steps_run += 1
+        return logits
+
+    # ---- inspection ------------------------------------------------------------------------------
+    def capture_routing(self, on: bool = True) -> dict:
+        """Starts (or stops) recording the experts chosen in every step.  Returns {layer index: list}
+        whose lists grow by one int32 tensor [tokens, k] per step while recording is on."""
+        out = {}
+        for i, layer in enumerate(self.model.layers):
+            ff = layer.feed_forward
+            if hasattr(ff, "capture"):
+                ff.capture = [] if on else None
+                if on:
+                    out[i] = ff.capture
+        return out
+
+    def check_device_errors(self) -> None:
+        """Raises if a kernel flagged a bad input since the last check (synchronises)."""
+        code = int(self.model.err_flag.item())
+        if code:
+            self.model.err_flag.zero_()
+            raise RuntimeError(f"embedding: token {code - 1} of a step was outside the vocabulary")

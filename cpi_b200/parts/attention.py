@@ -1,0 +1,101 @@
+"""Attention mixer: grouped-query attention over the paged cache, with a window and a position part.
+
+Reference forward of one token (src/engine/llama4_cpu_engine.cpp:304-325): q, k, v projections
+without bias, per-head weightless RMS norm of q and k, RoPE, cache write, causal softmax attention
+with scale 1/sqrt(D), output projection added to the residual.  This part generalises it by
+parameters: any head counts and head size, the position part (rotary or none), the norm on or off and
+before or after the rotation, a window (all keys, the query's chunk, or the last n keys), and an
+optional temperature on the query; and by batch: any mix of sequences and positions in one call.
+
+params: hidden_size, num_heads, num_kv_heads, head_dim, softmax_scale, position (PartSpec), qk_norm,
+qk_norm_eps, qk_norm_order ("before_rope" | "after_rope"), window {"kind", "size"},
+query_temperature (None or {"floor_scale", "attn_scale"}).
+Tensors under the prefix: self_attn.{q,k,v,o}_proj.weight  ([out, in]).
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.manager import KVRequirement
+from ..csrc import lib as K
+from ..weights.store import TensorReq
+from .base import Mixer, build_part, register_mixer
+from .linear import MODE_ADD, project
+
+
+@register_mixer("attention")
+class AttentionMixer(Mixer):
+    def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
+        super().__init__(spec, prefix)
+        p = spec.params
+        self.has_kv = bool(owns_cache)      # False: every run entry of this layer reads another's cache
+        self.hidden = int(p["hidden_size"])
+        self.nh, self.nkv, self.d = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        if self.nh % self.nkv:
+            raise ValueError(f"attention: {self.nh} heads cannot be grouped over {self.nkv} key/value heads")
+        if self.d % 16 or not 16 <= self.d <= 256:
+            raise ValueError(f"attention: head size {self.d} is not supported (multiples of 16 from 16 to 256)")
+        self.scale = float(p["softmax_scale"])
+        self.position = build_part("position", p["position"])
+        self.qk_norm = bool(p.get("qk_norm", False))
+        self.qk_norm_eps = float(p.get("qk_norm_eps", 0.0))
+        self.norm_before_rope = p.get("qk_norm_order", "after_rope") == "before_rope"
+        w = p.get("window") or {"kind": "full", "size": 0}
+        if w["kind"] not in K.WINDOW_KINDS:
+            raise ValueError(f"attention: unknown window kind '{w['kind']}'")
+        self.window_kind, self.window_size = w["kind"], int(w.get("size", 0))
+        t = p.get("query_temperature")
+        self.temperature = None if t is None else (float(t["floor_scale"]), float(t["attn_scale"]))
+        self.ws = workspace
+        self.w_qkv = self.w_o = None
+
+    # ---- weights ---------------------------------------------------------------------------------
+    def _names(self):
+        a = self.prefix + "self_attn."
+        return a + "q_proj.weight", a + "k_proj.weight", a + "v_proj.weight", a + "o_proj.weight"
+
+    def requirements(self):
+        q, k, v, o = self._names()
+        reqs = [TensorReq(q, (self.nh * self.d, self.hidden)), TensorReq(o, (self.hidden, self.nh * self.d))]
+        if self.has_kv:
+            reqs += [TensorReq(k, (self.nkv * self.d, self.hidden)), TensorReq(v, (self.nkv * self.d, self.hidden))]
+        return reqs
+
+    def load(self, source, device):
+        q, k, v, o = self._names()
+        parts = [source.get(q, device)]
+        if self.has_kv:
+            parts += [source.get(k, device), source.get(v, device)]
+        dt = torch.float32 if any(t.dtype == torch.float32 for t in parts) else torch.bfloat16
+        self.w_qkv = torch.cat([t.to(dt) for t in parts], dim=0).contiguous()    # [Q + 2 KV, H]
+        del parts
+        self.w_o = source.get(o, device).contiguous()
+        self.position.prepare(device)
+
+    # ---- cache -----------------------------------------------------------------------------------
+    def kv_requirement(self):
+        return KVRequirement(self.nkv, self.d, self.window_kind, self.window_size)
+
+    # ---- step ------------------------------------------------------------------------------------
+    def forward(self, h, residual, batch, cache):
+        T = h.shape[0]
+        dt = h.dtype
+        qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), dt)
+        project(h, self.w_qkv, qkv)
+        k_cache, v_cache, table, page_size = cache.kv()
+        q = self.ws.get("attn_q", (T, self.nh * self.d), dt)
+        K.qkv_post(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                   batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+                   inv_freq=self.position.inv_freq, interleaved=self.position.interleaved,
+                   qk_norm=self.qk_norm, norm_before_rope=self.norm_before_rope,
+                   norm_eps=self.qk_norm_eps, temperature=self.temperature,
+                   write_kv=self.has_kv and cache.owns)
+        att = self.ws.get("attn_out", (T, self.nh * self.d), dt)
+        self.attend(q, att, k_cache, v_cache, table, page_size, batch)
+        project(att, self.w_o, residual, MODE_ADD)
+
+    def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
+        K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                            batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+                            window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,
+                            scale=self.scale)

@@ -1,0 +1,27 @@
+"""Named device buffers that live across steps, so that a step allocates nothing once it is warm."""
+from __future__ import annotations
+
+import torch
+
+
+class Workspace:
+    def __init__(self, device):
+        self.device = device
+        self._buffers: dict = {}
+
+    def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = (name, dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < n:
+            cap = max(n, 1)
+            if buf is not None:
+                cap = max(cap, int(buf.numel() * 1.5))
+            buf = torch.empty(cap, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        return buf[:n].view(*shape)
+
+    def bytes_held(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._buffers.values())

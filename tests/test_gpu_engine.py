@@ -1,0 +1,120 @@
+"""Engine against the plain implementation on a GPU: whole prompts, token-by-token tails, unequal batches."""
+import pytest
+import torch
+
+import tiny
+from helpers import Replay, compare_with_plain
+
+pytestmark = pytest.mark.gpu
+
+_dirs, _engines = {}, {}
+
+
+def model_dir(name):
+    if name not in _dirs:
+        _dirs[name] = tiny.make_model_dir(name)
+    return _dirs[name]
+
+
+def engine(name, dtype, max_tokens=1024):
+    from cpi_b200.engine import Engine
+    key = (name, dtype, max_tokens)
+    if key not in _engines:
+        _engines[key] = Engine.from_model_dir(model_dir(name), dtype=dtype, max_tokens=max_tokens)
+    e = _engines[key]
+    assert not e.cache.live_slots(), "a previous test left slots behind"
+    return e
+
+
+def vocab(name):
+    c = tiny.config(name)
+    return c.get("text_config", c)["vocab_size"]
+
+
+CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")]
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_whole_prompts_each_alone(name, dtype):
+    e = engine(name, dtype)
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab(name), 100 + n) for n in (1, 5, 33, 70, 150)}
+    rp = Replay(e)
+    for rid, toks in reqs.items():
+        rp.step([(rid, toks, list(range(len(toks))))])
+        rp.end(rid)
+    worst = compare_with_plain(model_dir(name), reqs, rp, dtype)
+    print(f"whole {name} {dtype}: worst relative error {worst:.3e}")
+    e.cache.check_consistency()
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_last_32_tokens_one_by_one(name, dtype):
+    e = engine(name, dtype)
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab(name), 200 + n) for n in (33, 70, 131)}
+    rp = Replay(e)
+    for rid, toks in reqs.items():
+        n = len(toks)
+        head = n - 32
+        rp.step([(rid, toks[:head], [head - 1])])
+        for i in range(head, n):
+            rp.step([(rid, [toks[i]], [0])])
+        rp.end(rid)
+    positions = {rid: list(range(len(t) - 33, len(t))) for rid, t in reqs.items()}
+    worst = compare_with_plain(model_dir(name), reqs, rp, dtype, positions)
+    print(f"tail32 {name} {dtype}: worst relative error {worst:.3e}")
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_unequal_batches_one_after_another(name, dtype):
+    """Batches of unequal prompts whose shorter requests end earlier; the cache is sized for one batch,
+    so the second and third batch run in slots and pages that the first one gave back."""
+    shapes = {"A": [(5, 24), (17, 9), (40, 24)], "B": [(1, 16), (9, 3), (33, 16), (70, 7)]}[name]
+    need = sum(-(-(p + d) // 64) * 64 for p, d in shapes)
+    e = engine(name, dtype, max_tokens=need)
+    all_reqs = {}
+    rp = Replay(e)
+    for b in range(3):
+        reqs = {f"b{b}_{i}": tiny.random_tokens(p + d, vocab(name), 1000 * b + 10 * i + p)
+                for i, (p, d) in enumerate(shapes)}
+        all_reqs.update(reqs)
+        prompt_len = {f"b{b}_{i}": p for i, (p, d) in enumerate(shapes)}
+        rp.step([(rid, t[:prompt_len[rid]], [prompt_len[rid] - 1]) for rid, t in reqs.items()])
+        live = dict(reqs)
+        step = 0
+        while live:
+            for rid in [r for r, t in live.items() if prompt_len[r] + step >= len(t)]:
+                rp.end(rid)
+                del live[rid]
+            if not live:
+                break
+            rp.step([(rid, [t[prompt_len[rid] + step]], [0]) for rid, t in live.items()])
+            step += 1
+        e.cache.check_consistency()
+        assert e.cache.free_slots == e.cache.max_slots
+    positions = {}
+    for rid, t in all_reqs.items():
+        i = int(rid.split("_")[1])
+        positions[rid] = list(range(shapes[i][0] - 1, len(t)))
+    worst = compare_with_plain(model_dir(name), all_reqs, rp, dtype, positions)
+    print(f"batched {name} {dtype}: worst relative error {worst:.3e}")
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_cuts_agree_bitwise_in_float32(name):
+    """The same position gives the same logits whole, token by token, and inside a batch."""
+    e = engine(name, "float32")
+    V = vocab(name)
+    a, b = tiny.random_tokens(50, V, 1), tiny.random_tokens(21, V, 2)
+    rp = Replay(e)
+    rp.step([("whole", a, [49])]); rp.end("whole")
+    rp.step([("cut", a[:30], [])])
+    for i in range(30, 50):
+        rp.step([("cut", [a[i]], [0])])
+    rp.end("cut")
+    rp.step([("other", b[:20], [19]), ("batched", a[:49], [48])])
+    rp.step([("other", [b[20]], [0]), ("batched", [a[49]], [0])])
+    rp.end("other"); rp.end("batched")
+    w, c, bt = rp.logits["whole"][49], rp.logits["cut"][49], rp.logits["batched"][49]
+    scale = float(w.abs().max())
+    assert float((w - c).abs().max()) <= 2e-6 * scale
+    assert float((w - bt).abs().max()) <= 2e-6 * scale
