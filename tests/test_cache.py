@@ -1,0 +1,132 @@
+"""Cache bookkeeping on the host: slots and pages are never lost, held twice or freed twice."""
+import random
+
+import pytest
+import torch
+
+from cpi_b200.cache import CacheError, CacheFull, CacheManager, KVRequirement, PagePool, StateRequirement
+
+FULL = KVRequirement(2, 16, "full", 0)
+CHUNK = KVRequirement(2, 16, "chunk", 32)
+SLIDE = KVRequirement(2, 16, "sliding", 20)
+
+
+def manager(max_tokens=256, page=16, **kw):
+    return CacheManager({0: CHUNK, 1: CHUNK, 2: FULL, 3: SLIDE}, {3: [StateRequirement("acc", (4,))]},
+                        max_tokens=max_tokens, page_size=page, dtype=torch.float32, device="cpu", **kw)
+
+
+def test_page_pool_rejects_double_free():
+    p = PagePool(3)
+    a, b, c = p.take(), p.take(), p.take()
+    assert sorted([a, b, c]) == [0, 1, 2] and p.free_count == 0
+    with pytest.raises(CacheFull):
+        p.take()
+    p.give_back(b)
+    with pytest.raises(CacheError):
+        p.give_back(b)
+    with pytest.raises(CacheError):
+        p.give_back(7)
+    assert p.take() == b
+
+
+def test_groups_by_requirement_have_storage_of_their_own():
+    m = manager()
+    assert sorted(len(g.entries) for g in m.groups) == [1, 1, 2]
+    g = m.group_of_entry[0]
+    assert g is m.group_of_entry[1] and g is not m.group_of_entry[2]
+    assert g.k.shape == (2, 16, 2, 16, 16)
+    k0, _, table, page = m.kv_view(0)
+    k1, _, _, _ = m.kv_view(1)
+    assert k0.data_ptr() != k1.data_ptr() and page == 16 and table.shape == (16, 16)
+
+
+def test_slots_are_reused_and_double_release_is_an_error():
+    m = manager()
+    s = [m.acquire() for _ in range(m.max_slots)]
+    assert len(set(s)) == m.max_slots
+    with pytest.raises(CacheFull):
+        m.acquire()
+    m.release(s[3])
+    with pytest.raises(CacheError):
+        m.release(s[3])
+    assert m.acquire() == s[3]
+    m.check_consistency()
+
+
+def test_pages_follow_lengths_and_windows():
+    m = manager()
+    s = m.acquire()
+    assert m.prepare_step([s], [40]) == [0]
+    m.commit_step([s], [40])
+    full, chunk, slide = m.group_of_entry[2], m.group_of_entry[0], m.group_of_entry[3]
+    assert sorted(full.blocks[s]) == [0, 1, 2] and sorted(chunk.blocks[s]) == [0, 1, 2]
+    for _ in range(30):
+        m.prepare_step([s], [1]); m.commit_step([s], [1])
+    # length 70: the next position 69 -> chunk [64, 96) needs blocks from 4; sliding needs positions >= 50
+    assert sorted(full.blocks[s]) == [0, 1, 2, 3, 4]
+    assert sorted(chunk.blocks[s]) == [4]
+    assert sorted(slide.blocks[s]) == [3, 4]
+    assert full.table_host[s, 4] == full.blocks[s][4]
+    m.check_consistency()
+    m.release(s)
+    assert all(g.pool.free_count == g.pool.n_pages for g in m.groups)
+
+
+def test_state_is_zeroed_on_acquire():
+    m = manager()
+    s = m.acquire()
+    m.state_view(3, "acc")[s] += 5
+    m.release(s)
+    assert m.acquire() == s and float(m.state_view(3, "acc")[s].abs().sum()) == 0
+
+
+def test_capacity_errors():
+    m = manager(max_tokens=64, page=16, max_seq_len=48)
+    a, b = m.acquire(), m.acquire()
+    with pytest.raises(CacheError, match="longest"):
+        m.prepare_step([a], [49])
+    m.prepare_step([a], [48]); m.commit_step([a], [48])
+    with pytest.raises(CacheFull, match="full"):
+        m.prepare_step([b], [17])
+    with pytest.raises(CacheError, match="twice"):
+        m.prepare_step([a, a], [1, 1])
+    m.release(a); m.release(b)
+    with pytest.raises(CacheError, match="not live"):
+        m.prepare_step([a], [1])
+    m.check_consistency()
+
+
+def test_random_workload_never_loses_a_page():
+    rng = random.Random(0)
+    m = manager(max_tokens=512, page=16)
+    live = {}
+    for it in range(400):
+        if live and rng.random() < 0.25:
+            s = rng.choice(list(live))
+            m.release(s); del live[s]
+        elif len(live) < 6 and rng.random() < 0.4:
+            s = m.acquire()
+            n = rng.randint(1, 60)
+            try:
+                m.prepare_step([s], [n]); m.commit_step([s], [n]); live[s] = n
+            except CacheFull:
+                m.release(s)
+        elif live:
+            slots = list(live)
+            try:
+                m.prepare_step(slots, [1] * len(slots)); m.commit_step(slots, [1] * len(slots))
+                for s in slots:
+                    live[s] += 1
+            except CacheFull:
+                s = slots[0]
+                m.release(s); del live[s]
+        m.check_consistency()
+        for s, n in live.items():
+            assert m.lengths[s] == n
+            full = m.group_of_entry[2]
+            assert sorted(full.blocks[s]) == list(range(-(-n // 16)))
+    for s in list(live):
+        m.release(s)
+    m.check_consistency()
+    assert all(g.pool.free_count == g.pool.n_pages for g in m.groups) and m.free_slots == m.max_slots
