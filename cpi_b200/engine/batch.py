@@ -37,20 +37,29 @@ class StepBatch:
 
 
 class BatchStager:
-    """Builds StepBatch objects; owns the pinned host buffer and the device buffer behind them."""
+    """Builds StepBatch objects.  Index arrays go through a small ring of pinned host buffers, each
+    with a device twin; a buffer is written again only after the copy that last read it has finished,
+    so the host never waits for the step before last."""
+
+    RING = 4
 
     def __init__(self, device):
         self.device = torch.device(device)
         self._cap = 0
-        self._host = self._dev = None
+        self._ring = []
+        self._next = 0
+        self.bytes_staged = 0          # host-to-device bytes of the latest step
 
     def _reserve(self, n: int) -> None:
         if n <= self._cap:
             return
         self._cap = max(n, int(self._cap * 1.5), 4096)
         pin = self.device.type == "cuda"
-        self._host = torch.empty(self._cap, dtype=torch.int32, pin_memory=pin)
-        self._dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+        self._ring = []
+        for _ in range(self.RING):
+            host = torch.empty(self._cap, dtype=torch.int32, pin_memory=pin)
+            dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
+            self._ring.append([host, dev, None])
 
     def stage(self, slots, starts, token_lists, wants, dtype) -> StepBatch:
         B = len(slots)
@@ -59,7 +68,11 @@ class BatchStager:
         R = sum(len(w) for w in wants)
         total = 3 * T + 3 * B + R
         self._reserve(total)
-        h = self._host
+        entry = self._ring[self._next]
+        self._next = (self._next + 1) % self.RING
+        h, d, ev = entry
+        if ev is not None:
+            ev.synchronize()
         tokens, token_seq, token_pos, want_rows = [], [], [], []
         base = 0
         for s, (toks, st, w) in enumerate(zip(token_lists, starts, wants)):
@@ -71,8 +84,11 @@ class BatchStager:
             base += n
         flat = tokens + token_seq + token_pos + list(slots) + list(starts) + n_new + want_rows
         h[:total] = torch.tensor(flat, dtype=torch.int32)
-        d = self._dev
         d[:total].copy_(h[:total], non_blocking=True)
+        self.bytes_staged = total * 4
+        if self.device.type == "cuda":
+            entry[2] = torch.cuda.Event()
+            entry[2].record()
         o = 0
 
         def take(n):

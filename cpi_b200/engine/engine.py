@@ -44,7 +44,7 @@ class StepEntry:
 class Engine:
     def __init__(self, spec: ModelSpec, source, *, dtype="bfloat16", device="cuda:0", max_tokens: int = 4096,
                  max_seqs: Optional[int] = None, max_seq_len: Optional[int] = None, page_size: int = 64,
-                 config=None):
+                 max_step_tokens: int = 8192, config=None):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("cpi_b200 runs on a CUDA device only; there is no CPU path")
@@ -59,6 +59,7 @@ class Engine:
         self.cache = CacheManager(kv, state, max_tokens=max_tokens, max_seqs=max_seqs, max_seq_len=max_seq_len,
                                   page_size=page_size, dtype=self.dtype, device=self.device)
         self.stager = BatchStager(self.device)
+        self.max_step_tokens = max(1, int(max_step_tokens))
         self.steps_run = 0
 
     # ---- construction ----------------------------------------------------------------------------
@@ -111,6 +112,34 @@ class Engine:
                 if not 0 <= i < len(t):
                     raise ValueError(f"slot {e.slot}: wanted place {i} is outside the entry's {len(t)} tokens")
             slots.append(int(e.slot)); toks.append(t); wants.append(w)
+        n_new = [len(t) for t in toks]
+        if sum(n_new) <= self.max_step_tokens:
+            return self._run(slots, toks, wants)
+        # A step larger than the workspace allows runs as pieces, one after the other: whole sequences
+        # while they fit, and a longer sequence in runs of consecutive tokens.  Each piece attends to
+        # what the pieces before it left in the cache, so the result is that of the single step.
+        if len(set(slots)) != len(slots):
+            raise ValueError("a step names the same slot twice")
+        pieces, cur, cur_n = [], [], 0
+        for s, t, w in zip(slots, toks, wants):
+            off = 0
+            while off < len(t):
+                room = self.max_step_tokens - cur_n
+                if room == 0:
+                    pieces.append(cur)
+                    cur, cur_n, room = [], 0, self.max_step_tokens
+                n = min(room, len(t) - off)
+                cur.append((s, t[off:off + n], [i - off for i in w if off <= i < off + n]))
+                cur_n += n
+                off += n
+        if cur:
+            pieces.append(cur)
+        if any(sorted(w) != w for w in wants):
+            raise ValueError("a step larger than max_step_tokens needs each entry's `want` in ascending order")
+        outs = [self._run([c[0] for c in piece], [c[1] for c in piece], [c[2] for c in piece]) for piece in pieces]
+        return torch.cat(outs, dim=0)
+
+    def _run(self, slots, toks, wants) -> torch.Tensor:
         n_new = [len(t) for t in toks]
         starts = self.cache.prepare_step(slots, n_new)
         batch = self.stager.stage(slots, starts, toks, wants, self.dtype)

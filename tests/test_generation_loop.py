@@ -1,0 +1,179 @@
+"""The generation loop's decisions, on a fake engine: order of stop checks, batches, slot reuse."""
+from dataclasses import dataclass
+
+import pytest
+
+from cpi_b200.engine.generate import GenerationRequest, Generator, plan_batches
+from cpi_b200.sampling import SamplingParams
+from cpi_b200.sampling.sampler import banned_by_ngram, uniform_for
+
+
+@dataclass
+class Entry:
+    slot: int
+    tokens: list
+    want: list
+
+
+class FakeCache:
+    def __init__(self, n_pages, page_size, max_seq_len):
+        self.n_pages, self.page_size, self.max_seq_len = n_pages, page_size, max_seq_len
+
+
+class FakeEngine:
+    """next token = (last token + 1) % vocab; records every step; checks slot discipline."""
+
+    def __init__(self, slots=4, n_pages=64, page_size=16, max_seq_len=256, vocab=50):
+        self.cache = FakeCache(n_pages, page_size, max_seq_len)
+        self.free = list(range(slots))
+        self.live = {}
+        self.steps = []
+        self.vocab = vocab
+        self.acquired = []
+
+    def acquire_slot(self):
+        s = self.free.pop(0)
+        self.live[s] = []
+        self.acquired.append(s)
+        return s
+
+    def release_slot(self, s):
+        assert s in self.live, "released twice"
+        del self.live[s]
+        self.free.append(s)
+
+    def step(self, entries):
+        self.steps.append([(e.slot, list(e.tokens)) for e in entries])
+        out = []
+        for e in entries:
+            assert e.slot in self.live
+            if self.live[e.slot]:
+                assert len(e.tokens) == 1, "a started sequence goes on by one token"
+            self.live[e.slot] += list(e.tokens)
+            assert len(self.live[e.slot]) <= self.cache.max_seq_len
+            for _ in e.want:
+                out.append((self.live[e.slot][-1] + 1) % self.vocab)
+        return out
+
+
+class FakeSampler:
+    def sample(self, logits, params, histories, counters):
+        self.last = (params, histories, counters)
+        return list(logits)
+
+
+def gen(engine, **kw):
+    return Generator(engine, FakeSampler(), step_entry=Entry, **kw)
+
+
+def test_stop_token_is_kept_and_ends_the_sequence():
+    e = FakeEngine()
+    g = gen(e, max_batch=4, default_stop_ids=[13])
+    r = g.generate([GenerationRequest([10], 20), GenerationRequest([1, 2, 3], 4)])
+    assert r[0].tokens == [11, 12, 13] and r[0].finish_reason == "stop_token"
+    assert r[1].tokens == [4, 5, 6, 7] and r[1].finish_reason == "max_new" and r[1].prompt_tokens == 3
+    assert not e.live and sorted(e.free) == [0, 1, 2, 3]
+    # prompts run in one step; afterwards one token each; the finished request leaves the batch
+    assert e.steps[0] == [(0, [10]), (1, [1, 2, 3])]
+    assert e.steps[1] == [(0, [11]), (1, [4])] and e.steps[2] == [(0, [12]), (1, [5])]
+    assert e.steps[3] == [(1, [6])] and len(e.steps) == 4
+    assert g.stats.generated_tokens == 7 and g.stats.prompt_tokens == 4 and g.stats.decode_steps == 3
+
+
+def test_request_stop_ids_override_the_models():
+    e = FakeEngine()
+    g = gen(e, max_batch=2, default_stop_ids=[5])
+    r = g.generate([GenerationRequest([3], 6, stop_ids=[]), GenerationRequest([3], 6, stop_ids=[7])])
+    assert r[0].tokens == [4, 5, 6, 7, 8, 9] and r[0].finish_reason == "max_new"
+    assert r[1].tokens == [4, 5, 6, 7] and r[1].finish_reason == "stop_token"
+
+
+def test_callback_stops_after_the_token_is_appended_and_stop_token_wins():
+    e = FakeEngine()
+    g = gen(e, max_batch=2, default_stop_ids=[6])
+    seen = []
+
+    def cb(i, tok):
+        seen.append((i, tok))
+        return tok != 5
+
+    r = g.generate([GenerationRequest([3], 9), GenerationRequest([5], 9)], cb)
+    assert r[0].tokens == [4, 5] and r[0].finish_reason == "callback"
+    assert r[1].tokens == [6] and r[1].finish_reason == "stop_token"
+    assert (1, 6) not in seen                     # the stop check comes before the callback
+
+
+def test_capacity_stop():
+    e = FakeEngine(max_seq_len=8, page_size=4, n_pages=8)
+    g = gen(e, max_batch=1)
+    r = g.generate([GenerationRequest([0, 1, 2, 3, 4], 50)])
+    assert r[0].finish_reason == "capacity" and r[0].tokens == [5, 6, 7, 8]
+    with pytest.raises(ValueError, match="longest"):
+        g.generate([GenerationRequest(list(range(9)), 2)])
+
+
+def test_batches_follow_each_other_in_freed_slots():
+    e = FakeEngine(slots=2)
+    g = gen(e, max_batch=2)
+    r = g.generate([GenerationRequest([i], 2 + i) for i in range(5)])
+    assert [x.tokens for x in r] == [[(i + 1 + j) % 50 for j in range(2 + i)] for i in range(5)]
+    assert g.stats.batches == 3 and e.acquired == [0, 1, 0, 1, 1] or e.acquired[:2] == [0, 1]
+    assert len(e.acquired) == 5 and set(e.acquired) == {0, 1} and not e.live
+
+
+def test_plan_batches_respects_cache_tokens():
+    reqs = [GenerationRequest([0] * p, m) for p, m in [(10, 7), (33, 1), (60, 5), (5, 5)]]
+    # needs, rounded to pages of 16: 16, 48, 64, 16
+    assert plan_batches(reqs, max_batch=8, token_capacity=128, page_size=16, max_seq_len=999) == [[0, 1, 2], [3]]
+    assert plan_batches(reqs, max_batch=2, token_capacity=1 << 20, page_size=16, max_seq_len=999) == [[0, 1], [2, 3]]
+    with pytest.raises(ValueError, match="cache holds"):
+        plan_batches(reqs, max_batch=2, token_capacity=48, page_size=16, max_seq_len=999)
+
+
+def test_empty_prompt_uses_bos_or_fails():
+    e = FakeEngine()
+    with pytest.raises(ValueError, match="empty prompt"):
+        gen(e, max_batch=1).generate([GenerationRequest([], 2)])
+    r = gen(e, max_batch=1, bos_token_id=9).generate([GenerationRequest([], 2)])
+    assert r[0].tokens == [10, 11] and r[0].prompt_tokens == 1
+
+
+def test_slots_are_returned_when_a_step_fails():
+    e = FakeEngine()
+
+    def boom(entries):
+        raise RuntimeError("step failed")
+
+    g = gen(e, max_batch=2)
+    e.step = boom
+    with pytest.raises(RuntimeError):
+        g.generate([GenerationRequest([1], 2), GenerationRequest([2], 2)])
+    assert not e.live and len(e.free) == 4
+
+
+def test_sampler_receives_histories_and_counters():
+    e = FakeEngine()
+    g = gen(e, max_batch=2)
+    sp = SamplingParams(temperature=0.7, seed=3)
+    g.generate([GenerationRequest([1, 2], 3, sp), GenerationRequest([7], 2, sp)])
+    params, hist, counters = g.sampler.last
+    assert hist == [[1, 2, 3, 4]] and counters == [(0, 2)] and params == [sp]
+
+
+def test_ngram_bans_and_uniforms():
+    assert banned_by_ngram([1, 2, 3, 1, 2], 3) == [3]
+    assert banned_by_ngram([1, 2, 1, 3, 1], 2) == [2, 3]
+    assert banned_by_ngram([1, 2], 4) == [] and banned_by_ngram([1, 2, 3], 1) == []
+    u = uniform_for(5, 1, 2)
+    assert 0.0 <= u < 1.0 and u == uniform_for(5, 1, 2)
+    assert len({uniform_for(5, 1, s) for s in range(20)} | {uniform_for(6, 1, 2)}) == 21
+
+
+def test_sampling_params_validation():
+    SamplingParams(temperature=0.0, top_k=100000).validate()
+    with pytest.raises(ValueError, match="top_k"):
+        SamplingParams(temperature=1.0, top_k=1000).validate()
+    with pytest.raises(ValueError):
+        SamplingParams(repetition_penalty=0.0).validate()
+    assert SamplingParams(temperature=0.0).is_plain_greedy
+    assert not SamplingParams(temperature=0.0, repetition_penalty=1.2).is_plain_greedy
