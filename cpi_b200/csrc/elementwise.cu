@@ -72,9 +72,26 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
   }
 }
 
+// dst[r, :] = src[rows[r], :]  (16-byte chunks; width * sizeof(T) must be a multiple of 16)
+__global__ void gather_rows_kernel(const uint4* __restrict__ src, long src_stride16, const int* __restrict__ rows,
+                                   uint4* __restrict__ dst, int chunks) {
+  const int r = blockIdx.x;
+  const uint4* s = src + (size_t)rows[r] * src_stride16;
+  uint4* d = dst + (size_t)r * chunks;
+  for (int i = threadIdx.x; i < chunks; i += blockDim.x) d[i] = s[i];
+}
+
 }  // namespace cpi
 
 using namespace cpi;
+
+extern "C" int cpi_gather_rows(const void* src, long src_stride_bytes, const int* rows, void* dst, int n_rows,
+                               int row_bytes, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  CPI_REQUIRE(row_bytes % 16 == 0 && src_stride_bytes % 16 == 0, "gather_rows: rows of %d bytes (stride %ld) are not 16-byte multiples", row_bytes, src_stride_bytes);
+  gather_rows_kernel<<<n_rows, 128, 0, stream>>>((const uint4*)src, src_stride_bytes / 16, rows, (uint4*)dst, row_bytes / 16);
+  return check_launch("gather_rows");
+}
 
 extern "C" int cpi_embedding(const int* tokens, const void* table, int table_dtype, float* out,
                              int n_tokens, int hidden, int vocab, int* err_flag, cudaStream_t stream) {

@@ -1,0 +1,473 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:  out[t, n] = sum_k X[t, k] * W[g][n, k].
+//
+// One kernel for decode (a handful of tokens) and prefill (thousands).  The WEIGHT tile is the MMA's
+// M operand (128 output features x 64 k), the TOKEN tile its N operand (16..256 tokens x 64 k); both
+// are K-major, staged in shared memory by TMA with the 128-byte swizzle and consumed by
+// tcgen05.mma (kind::f16, bf16 x bf16 -> fp32) with the accumulator in tensor memory.  A decode step
+// therefore fills the 128-wide MMA with weight rows however few tokens there are, and streams every
+// weight byte exactly once.  Roles inside a CTA of 128 threads: one elected thread of warp 0 issues
+// TMA, one of warp 1 issues MMA; a ring of `stages` buffers with full/empty mbarriers couples them;
+// after the last k-tile all four warps read their 32 accumulator lanes with tcgen05.ld and run the
+// epilogue.  The reference has no tensor-core kernel of its own: its counterparts are SIMT GEMV
+// kernels (src/kernels/kernels_ops_matvec.cu:343-418) and one cublasGemmEx call
+// (src/engine/llama4_cuda_engine_setup.cu:579-605).
+//
+// Epilogues (same meaning as the FP32-pipe kernel):  STORE, ADD (float32 residual), SWIGLU (two
+// accumulators: rows n and N + n of W; out = silu(g) * u).  Optional per-token scale, output row
+// scatter, and groups (routed experts): tokens [offsets[g], offsets[g+1]) use W[g].
+//
+// Split-K: when a launch has too few tiles to fill the GPU, the k range is cut into `splits` parts.
+// Each CTA stores its raw accumulators into `partials`; the CTA that takes the last ticket of a tile
+// sums the parts in split order (a fixed order: the result does not depend on arrival order), applies
+// the epilogue and resets the ticket.  `partials` and `tickets` are scratch the caller provides;
+// tickets must be zero before the first launch and are left zero.
+//
+// Every mbarrier wait is bounded: when it runs out the CTA raises `*error_flag`, stops issuing work,
+// lets copies in flight land, frees its tensor memory and returns.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+#include <string>
+#include <cstring>
+
+namespace cpi {
+namespace tc {
+
+constexpr int BM = 128;          // output features per tile (MMA M)
+constexpr int BK = 64;           // k elements per stage: 128 bytes of bf16 = one swizzle row
+constexpr int UMMA_K = 16;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+enum Mode : int { kStore = 0, kAdd = 1, kSwiglu = 2 };
+
+struct Params {
+  void* out; long ldo;
+  const int* out_rows;
+  const float* row_scale;
+  const int* group_offsets; int n_groups;
+  int T;               // logical token rows (all groups)
+  int N;               // output features
+  int k_tiles;         // ceil(K / 64)
+  int splits, k_tiles_per_split;
+  float* partials; int* tickets;
+  int* error_flag;
+};
+
+// ---------------------------------------------------------------------------------------------- PTX
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// K-major operand tile in shared memory, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);        // start address
+  d |= (uint64_t)1 << 16;                          // leading byte offset (unused with this swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                          // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                          // SWIZZLE_128B
+  return d;
+}
+__host__ __device__ constexpr uint32_t instr_desc_bf16(int n) {
+  return (1u << 4)                   // D format: F32
+       | (1u << 7) | (1u << 10)      // A, B format: BF16
+       | ((uint32_t)(n >> 3) << 17)  // N
+       | ((uint32_t)(BM >> 4) << 24);  // M
+}
+
+template <typename TO> __device__ __forceinline__ void store_out(TO* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// ---------------------------------------------------------------------------------------------- kernel
+template <int BN, int MODE, typename TO, int STAGES>
+__global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                      const __grid_constant__ CUtensorMap map_x, Params p) {
+  constexpr int ACC = MODE == kSwiglu ? 2 : 1;
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
+  constexpr uint32_t STAGE_BYTES = ACC * A_BYTES + B_BYTES;
+  constexpr uint32_t TMEM_COLS = ACC * BN < 32 ? 32 : ACC * BN;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s, ticket_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  // ---- which tile ----
+  int group = 0, t_begin = 0, t_end = p.T, tile_t = blockIdx.y;
+  if (p.group_offsets) {
+    bool found = false;
+    for (int g = 0; g < p.n_groups; ++g) {
+      const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
+      const int tiles = (e - b + BN - 1) / BN;
+      if (tile_t < tiles) { group = g; t_begin = b; t_end = e; found = true; break; }
+      tile_t -= tiles;
+    }
+    if (!found) return;
+  }
+  const int t0 = t_begin + tile_t * BN;
+  if (t0 >= t_end) return;
+  const int n0 = blockIdx.x * BM;
+  const int split = blockIdx.z;
+  const int kt_begin = split * p.k_tiles_per_split;
+  const int kt_end = min(p.k_tiles, kt_begin + p.k_tiles_per_split);
+  const int n_kt = kt_end - kt_begin;
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    mbar_init(&accum_bar, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, TMEM_COLS);
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort_flag = &abort_s;
+
+  if (warp == 0 && lane == 0) {
+    // ---- TMA producer ----
+    for (int i = 0; i < n_kt; ++i) {
+      const int s = i % STAGES;
+      if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
+      uint8_t* st = smem + (size_t)s * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      const int k = (kt_begin + i) * BK;
+      tma_load_3d(st, &map_w, &full_bar[s], k, n0, group);
+      if (ACC == 2) tma_load_3d(st + A_BYTES, &map_w, &full_bar[s], k, p.N + n0, group);
+      tma_load_2d(st + ACC * A_BYTES, &map_x, &full_bar[s], k, t0);
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---- MMA issuer ----
+    constexpr uint32_t idesc = instr_desc_bf16(BN);
+    bool ok = true;
+    for (int i = 0; i < n_kt && ok; ++i) {
+      const int s = i % STAGES;
+      ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abort_flag);
+      if (!ok) break;
+      fence_after_sync();
+      const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
+      const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + ACC * A_BYTES);
+#pragma unroll
+      for (int j = 0; j < BK / UMMA_K; ++j) {
+        const uint32_t acc = (i > 0 || j > 0) ? 1u : 0u;
+        umma_bf16(tmem_base, da + 2 * j, db + 2 * j, idesc, acc);
+        if (ACC == 2) umma_bf16(tmem_base + BN, smem_desc_sw128(a_addr + A_BYTES) + 2 * j, db + 2 * j, idesc, acc);
+      }
+      umma_commit(&empty_bar[s]);       // frees the stage once these MMAs have read it
+    }
+    if (ok) umma_commit(&accum_bar);    // accumulators complete
+  }
+  __syncwarp();
+
+  // ---- epilogue: all four warps ----
+  bool ok = mbar_wait(&accum_bar, 0, abort_flag);
+  fence_after_sync();
+  ok = ok && !abort_s;
+
+  const int row = warp * 32 + lane;                       // accumulator lane = output feature n0 + row
+  const int n = n0 + row;
+  const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+  const int n_valid_t = min(BN, t_end - t0);
+  TO* out = reinterpret_cast<TO*>(p.out);
+
+  auto emit = [&](int col, float v, float u) {
+    const int lr = t0 + col;
+    if (col >= n_valid_t || n >= p.N) return;
+    const float s = p.row_scale ? p.row_scale[lr] : 1.0f;
+    v *= s;
+    TO* o = out + (size_t)(p.out_rows ? p.out_rows[lr] : lr) * p.ldo + n;
+    if (MODE == kSwiglu) {
+      u *= s;
+      store_out<TO>(o, v / (1.0f + __expf(-v)) * u);
+    } else if (MODE == kAdd) {
+      store_out<TO>(o, to_f32(*o) + v);
+    } else {
+      store_out<TO>(o, v);
+    }
+  };
+
+  if (ok && p.splits == 1) {
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 16) {
+      float v[16], u[16];
+      tmem_ld16(lane_addr + c, v);
+      if (ACC == 2) tmem_ld16(lane_addr + BN + c, u);
+#pragma unroll
+      for (int j = 0; j < 16; ++j) emit(c + j, v[j], ACC == 2 ? u[j] : 0.f);
+    }
+  } else if (ok) {
+    // raw accumulators -> partials[tile][split][acc][col][row]
+    const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+    float* mine = p.partials + ((tile_id * p.splits + split) * ACC) * (size_t)(BN * BM);
+#pragma unroll 1
+    for (int a = 0; a < ACC; ++a)
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16];
+        tmem_ld16(lane_addr + a * BN + c, v);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) mine[((size_t)a * BN + c + j) * BM + row] = v[j];
+      }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) ticket_s = atomicAdd(&p.tickets[tile_id], 1);
+    __syncthreads();
+    if (ticket_s == p.splits - 1) {
+      __threadfence();
+      const float* base = p.partials + (tile_id * p.splits * ACC) * (size_t)(BN * BM);
+#pragma unroll 1
+      for (int c = 0; c < n_valid_t; ++c) {
+        float v = 0.f, u = 0.f;
+        for (int z = 0; z < p.splits; ++z) {
+          const float* pz = base + ((size_t)z * ACC) * (size_t)(BN * BM);
+          v += __ldcg(pz + (size_t)c * BM + row);
+          if (ACC == 2) u += __ldcg(pz + ((size_t)BN + c) * BM + row);
+        }
+        emit(c, v, u);
+      }
+      if (tid == 0) p.tickets[tile_id] = 0;
+    }
+  }
+
+  if (!ok) {
+    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    // give copies in flight time to land before the shared memory is released
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---------------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(f);
+  });
+  return fn;
+}
+
+struct MapKey {
+  const void* ptr; uint64_t d0, d1, d2, s1, s2; uint32_t b0, b1;
+  bool operator==(const MapKey& o) const { return std::memcmp(this, &o, sizeof(MapKey)) == 0; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    const uint64_t* w = reinterpret_cast<const uint64_t*>(&k);
+    size_t h = 1469598103934665603ull;
+    for (size_t i = 0; i < sizeof(MapKey) / 8; ++i) h = (h ^ w[i]) * 1099511628211ull;
+    return h;
+  }
+};
+
+// bf16 tensor [d2][d1][d0] with byte strides s1, s2; box b0 x b1 x 1, 128-byte swizzle.
+static int get_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1, uint64_t s2, uint32_t b0,
+                   uint32_t b1, CUtensorMap* out) {
+  static std::mutex mu;
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  MapKey key;
+  std::memset(&key, 0, sizeof(key));
+  key.ptr = ptr; key.d0 = d0; key.d1 = d1; key.d2 = d2; key.s1 = s1; key.s2 = s2; key.b0 = b0; key.b1 = b1;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = cache.find(key);
+  if (it != cache.end()) { *out = it->second; return 0; }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) { set_error("gemm_tc: cuTensorMapEncodeTiled is not available from the driver"); return 1; }
+  cuuint64_t dims[3] = {d0, d1, d2};
+  cuuint64_t strides[2] = {s1, s2};
+  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const cuuint32_t rank = d2 > 0 ? 3 : 2;
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) { set_error("gemm_tc: cuTensorMapEncodeTiled failed with code %d", (int)r); return 1; }
+  if (cache.size() > 4096) cache.clear();
+  cache.emplace(key, *out);
+  return 0;
+}
+
+template <int BN, int MODE, typename TO>
+static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+  constexpr int ACC = MODE == kSwiglu ? 2 : 1;
+  constexpr int STAGE = ACC * BM * BK * 2 + BN * BK * 2;
+  constexpr int BUDGET = BN <= 32 ? 108 * 1024 : 196 * 1024;    // two CTAs per SM for narrow token tiles
+  constexpr int S0 = BUDGET / STAGE;
+  constexpr int STAGES = S0 > 8 ? 8 : (S0 < 2 ? 2 : S0);
+  constexpr int SMEM = STAGES * STAGE + 1024;
+  auto kern = gemm_tc_kernel<BN, MODE, TO, STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+      set_error("gemm_tc: cannot reserve %d bytes of shared memory", SMEM);
+      return 1;
+    }
+    attr_set = true;
+  }
+  kern<<<grid, 128, SMEM, stream>>>(mw, mx, p);
+  return check_launch("gemm_tc");
+}
+
+template <int MODE, typename TO>
+static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
+  switch (bn) {
+    case 16:  return launch<16, MODE, TO>(mw, mx, p, grid, s);
+    case 32:  return launch<32, MODE, TO>(mw, mx, p, grid, s);
+    case 64:  return launch<64, MODE, TO>(mw, mx, p, grid, s);
+    case 128: return launch<128, MODE, TO>(mw, mx, p, grid, s);
+    case 256: return launch<256, MODE, TO>(mw, mx, p, grid, s);
+  }
+  set_error("gemm_tc: token tile %d is not supported", bn);
+  return 1;
+}
+
+}  // namespace tc
+}  // namespace cpi
+
+using namespace cpi;
+
+// Token-tile width and split count for a launch (also used by the caller to size the scratch).
+// tiles_hint = expected token tiles per group (rows per group / bn, rounded up), groups_hint = groups in use.
+extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, int* bn_out, int* splits_out,
+                                int* live_y_out) {
+  const int rows_per_group = n_groups > 0 ? (T + n_groups - 1) / n_groups : T;
+  int bn = 16;
+  while (bn < 256 && bn < rows_per_group) bn *= 2;
+  if (swiglu && bn > 256) bn = 256;
+  const int n_tiles = (N + tc::BM - 1) / tc::BM;
+  // token tiles that can hold rows: sum_g ceil(rows_g / bn) <= ceil(T / bn) + min(T, groups); they are
+  // the first values of blockIdx.y, so scratch is only needed for those
+  const int live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
+  const int k_tiles = (K + tc::BK - 1) / tc::BK;
+  int splits = 1;
+  const long ctas = (long)n_tiles * (live_y > 0 ? live_y : 1);
+  if (ctas < 256) {
+    splits = (int)((296 + ctas - 1) / ctas);
+    const int max_by_k = k_tiles / 8 > 0 ? k_tiles / 8 : 1;      // at least 8 k-tiles per split
+    if (splits > max_by_k) splits = max_by_k;
+    if (splits > 16) splits = 16;
+  }
+  const int per = (k_tiles + splits - 1) / splits;
+  splits = (k_tiles + per - 1) / per;
+  *bn_out = bn; *splits_out = splits; *live_y_out = live_y;
+  return 0;
+}
+
+// x [T, K] bf16 (row stride ldx elements), w [G or 1][N or 2N][K] bf16 contiguous, out [*, N].
+// partials: float32 scratch of at least tiles * splits * acc * bn * 128 elements (tiles = grid_x * grid_y);
+// tickets: int32 zeros, one per tile.  Both may be null when splits == 1.
+extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, int out_dtype, long ldo,
+                           const int* out_rows, const float* row_scale, const int* group_offsets, int n_groups,
+                           int T, int N, int K, int mode, int bn, int splits, float* partials, long partials_elems,
+                           int* tickets, long tickets_elems, int* error_flag, cudaStream_t stream) {
+  if (T == 0 || N == 0) return 0;
+  CPI_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
+  CPI_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K (%d) and the activation row stride (%ld) must be multiples of 8", K, ldx);
+  CPI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+              "gemm_tc: operands must be 16-byte aligned");
+  CPI_REQUIRE(mode != tc::kAdd || out_dtype == kF32, "gemm_tc: ADD mode needs a float32 output");
+  CPI_REQUIRE(mode != tc::kSwiglu || out_dtype == kBF16, "gemm_tc: SWIGLU mode writes bfloat16");
+  const int acc = mode == tc::kSwiglu ? 2 : 1;
+  const int rows_w = acc * N;
+  const int groups = n_groups > 0 ? n_groups : 1;
+  CUtensorMap mw, mx;
+  if (tc::get_map(w, (uint64_t)K, (uint64_t)rows_w, (uint64_t)groups, (uint64_t)K * 2, (uint64_t)K * 2 * rows_w,
+                  tc::BK, tc::BM, &mw)) return 1;
+  if (tc::get_map(x, (uint64_t)K, (uint64_t)T, 0, (uint64_t)ldx * 2, 0, tc::BK, (uint32_t)bn, &mx)) return 1;
+  const int k_tiles = (K + tc::BK - 1) / tc::BK;
+  const int per = (k_tiles + splits - 1) / splits;
+  CPI_REQUIRE(splits >= 1 && (long)(splits - 1) * per < k_tiles, "gemm_tc: %d splits leave an empty split (k tiles %d)", splits, k_tiles);
+  dim3 grid((N + tc::BM - 1) / tc::BM, n_groups > 0 ? (T + bn - 1) / bn + n_groups : (T + bn - 1) / bn, splits);
+  CPI_REQUIRE(grid.y <= 65535, "gemm_tc: too many token tiles (%u)", grid.y);
+  if (splits > 1) {
+    const long live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
+    const long tiles = (long)grid.x * live_y;
+    CPI_REQUIRE(partials && tickets && partials_elems >= tiles * splits * acc * bn * tc::BM && tickets_elems >= tiles,
+                "gemm_tc: split-K scratch is too small (tiles %ld, splits %d)", tiles, splits);
+  }
+  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, N, k_tiles, splits, per, partials, tickets, error_flag};
+  if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(bn, mw, mx, p, grid, stream);
+  if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(bn, mw, mx, p, grid, stream);
+  if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(bn, mw, mx, p, grid, stream);
+  if (mode == tc::kSwiglu) return tc::launch_bn<tc::kSwiglu, __nv_bfloat16>(bn, mw, mx, p, grid, stream);
+  set_error("gemm_tc: unsupported mode %d with output dtype %d", mode, out_dtype);
+  return 1;
+}

@@ -129,6 +129,89 @@ def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=Non
           _p(group_offsets), c_int(n_groups), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(hint), _stream())
 
 
+_tc_scratch = {}      # device index -> {"partials", "tickets", "error"}
+
+
+def tc_error_flag(device) -> torch.Tensor:
+    """int32[1] that a tensor-core kernel sets when one of its bounded waits ran out."""
+    return _tc_state(device)["error"]
+
+
+def _tc_state(device):
+    idx = torch.device(device).index or 0
+    st = _tc_scratch.get(idx)
+    if st is None:
+        st = {"partials": torch.empty(1 << 20, dtype=torch.float32, device=device),
+              "tickets": torch.zeros(1 << 14, dtype=torch.int32, device=device),
+              "error": torch.zeros(1, dtype=torch.int32, device=device)}
+        _tc_scratch[idx] = st
+    return st
+
+
+def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None, row_scale=None,
+            group_offsets=None, n_groups=0, rows_per_group_hint=None) -> bool:
+    """The tcgen05 kernel for out[m, n] (+)= sum_k a[m, k] w[g(m)][n, k] in bfloat16 (see gemm_tc.cu).
+
+    Returns False, having launched nothing, when the call is outside what the kernel takes (a row
+    gather, K or a row stride that is no multiple of 8, unaligned operands, an output dtype the
+    epilogue does not write); the caller then uses the FP32-pipe kernel."""
+    if a_rows is not None or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    if a.dim() != 2 or a.stride(1) != 1 or not w.is_contiguous() or out.stride(-1) != 1:
+        return False
+    K = a.shape[1]
+    if K % 8 or a.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16 or w.shape[-1] != K:
+        return False
+    if mode == MODE_SWIGLU and out.dtype != torch.bfloat16:
+        return False
+    if mode == MODE_ADD and out.dtype != torch.float32:
+        return False
+    _need_cuda(a, w, out, out_rows, row_scale, group_offsets)
+    grouped = group_offsets is not None
+    rows_w = w.shape[-2]
+    N = n_out if n_out is not None else (rows_w // 2 if mode == MODE_SWIGLU else rows_w)
+    if rows_w != (2 * N if mode == MODE_SWIGLU else N) or out.shape[1] != N:
+        raise KernelError(f"gemm_tc: weight rows {rows_w} do not match {N} outputs in mode {mode}")
+    if grouped and (w.dim() != 3 or w.shape[0] != n_groups):
+        raise KernelError("gemm_tc: grouped weights must be [groups, rows, K]")
+    T = m_rows if m_rows is not None else a.shape[0]
+    if T > a.shape[0]:
+        raise KernelError("gemm_tc: more logical rows than activation rows")
+    bn, splits, live_y = c_int(), c_int(), c_int()
+    load().cpi_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(n_groups if grouped else 0),
+                            c_int(int(mode == MODE_SWIGLU)), ctypes.byref(bn), ctypes.byref(splits),
+                            ctypes.byref(live_y))
+    st = _tc_state(a.device)
+    sp = splits.value
+    if sp > 1:
+        tiles = -(-N // 128) * live_y.value
+        need = tiles * sp * (2 if mode == MODE_SWIGLU else 1) * bn.value * 128
+        if need > (1 << 26):                 # keep the scratch modest: fewer splits instead
+            sp = 1
+        else:
+            if st["partials"].numel() < need:
+                st["partials"] = torch.empty(need, dtype=torch.float32, device=a.device)
+            if st["tickets"].numel() < tiles:
+                st["tickets"] = torch.zeros(tiles, dtype=torch.int32, device=a.device)
+    _call("cpi_gemm_tc", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
+          c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
+          c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn.value), c_int(sp), _p(st["partials"]),
+          c_long(st["partials"].numel()), _p(st["tickets"]), c_long(st["tickets"].numel()), _p(st["error"]),
+          _stream())
+    return True
+
+
+def gather_rows(src, rows, dst):
+    """dst[r] = src[rows[r]] for 2-D tensors whose rows are multiples of 16 bytes."""
+    _need_cuda(src, rows, dst)
+    _rowmajor(src, "gather_rows src")
+    assert dst.is_contiguous() and dst.dtype == src.dtype and dst.shape[1] == src.shape[1]
+    assert rows.dtype == torch.int32
+    n = dst.shape[0]
+    _call("cpi_gather_rows", _p(src), c_long(src.stride(0) * src.element_size()), _p(rows), _p(dst), c_int(n),
+          c_int(src.shape[1] * src.element_size()), _stream())
+
+
 def qkv_post(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
              n_heads, n_kv_heads, head_dim, inv_freq=None, interleaved=False, qk_norm=False,
              norm_before_rope=False, norm_eps=0.0, temperature=None, write_kv=True):

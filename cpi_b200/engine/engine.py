@@ -163,6 +163,9 @@ class Engine:
 
     def check_device_errors(self) -> None:
         """Raises if a kernel flagged a bad input since the last check (synchronises)."""
+        if int(K.tc_error_flag(self.device).item()):
+            K.tc_error_flag(self.device).zero_()
+            raise RuntimeError("a tensor-core kernel gave up waiting on one of its barriers; results are invalid")
         code = int(self.model.err_flag.item())
         if code:
             self.model.err_flag.zero_()

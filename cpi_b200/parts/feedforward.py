@@ -120,9 +120,16 @@ class MoESwiGLU(FeedForward):
         M = T * Kk
         hint = max(1, -(-M // E))
         act = ws.get("moe_act", (M, self.inter), h.dtype)
-        project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token,
-                row_scale=row_scale if self.gate_mode == "sigmoid_input" else None,
-                group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+        in_scale = row_scale if self.gate_mode == "sigmoid_input" else None
+        if (h.shape[1] * h.element_size()) % 16 == 0 and h.stride(0) * h.element_size() % 16 == 0:
+            # rows sorted by expert, so that each expert reads a contiguous block
+            sorted_h = ws.get("moe_in", (M, self.hidden), h.dtype)
+            K.gather_rows(h, row_token, sorted_h)
+            project(sorted_h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, row_scale=in_scale,
+                    group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+        else:
+            project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token, row_scale=in_scale,
+                    group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
         out_scale = row_scale if self.gate_mode == "sigmoid_output" else None
         if Kk == 1:
             project(act, self.w_down, residual, MODE_ADD, m_rows=M, out_rows=row_token, row_scale=out_scale,

@@ -1,0 +1,382 @@
+"""Each CUDA kernel alone against a plain torch float32 statement of the same operation, at sizes other
+than the engine's tiny configurations (odd widths, tails, empty groups, window edges)."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def K():
+    from cpi_b200.csrc import lib
+    return lib
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+# ------------------------------------------------------------------------------------------------ rows
+@pytest.mark.parametrize("H,tdt", [(70, torch.bfloat16), (1000, torch.float32)])
+def test_embedding(H, tdt):
+    V, T = 37, 9
+    table = rnd(V, H, dtype=tdt)
+    toks = torch.tensor([0, 36, 5, 5, 17, 1, 2, 3, 36], dtype=torch.int32, device=DEV)
+    out = torch.empty(T, H, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().embedding(toks, table, out, err)
+    assert torch.equal(out, table[toks.long()].float()) and int(err) == 0
+    toks[4] = 37
+    K().embedding(toks, table, out, err)
+    assert int(err) == 5 and float(out[4].abs().sum()) == 0
+
+
+@pytest.mark.parametrize("n,xdt,odt,wdt", [(5120, torch.float32, torch.bfloat16, torch.bfloat16),
+                                           (100, torch.float32, torch.float32, torch.float32),
+                                           (48, torch.bfloat16, torch.bfloat16, None)])
+def test_rmsnorm(n, xdt, odt, wdt):
+    x = rnd(7, n, dtype=xdt, scale=3.0)
+    w = None if wdt is None else rnd(n, dtype=wdt, seed=1)
+    out = torch.empty(7, n, dtype=odt, device=DEV)
+    K().rmsnorm(x, w, 1e-6, out)
+    xf = x.float()
+    ref = xf / torch.sqrt((xf * xf).mean(-1, keepdim=True) + 1e-6)
+    if w is not None:
+        ref = ref * w.float()
+    tol = 1e-5 if odt == torch.float32 else 1e-2
+    assert torch.allclose(out.float(), ref, atol=tol * float(ref.abs().max()))
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, n, dtype=odt, device=DEV)
+    K().rmsnorm(x, w, 1e-6, out2, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+def ref_gemm(a, w, mode, out0=None, row_scale=None):
+    acc = a.float() @ w.float().T
+    if row_scale is not None:
+        acc = acc * row_scale[:, None]
+    if mode == 2:
+        n = w.shape[0] // 2
+        g, u = acc[:, :n], acc[:, n:]
+        return g / (1 + torch.exp(-g)) * u
+    return acc if mode == 0 else out0 + acc
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 7, 5), (13, 70, 33), (64, 64, 16), (100, 200, 300)])
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                     (torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32)])
+def test_gemm_fp32_pipe_modes(M, N, Kd, adt, wdt):
+    a, scale = rnd(M, Kd, dtype=adt), rnd(M, seed=5).abs()
+    for mode in (0, 1, 2):
+        w = rnd(2 * N if mode == 2 else N, Kd, dtype=wdt, seed=2)
+        out = rnd(M, N, seed=3)
+        ref = ref_gemm(a, w, mode, out.clone(), scale)
+        K().gemm_simt(a, w, out, mode, row_scale=scale)
+        assert torch.allclose(out, ref, atol=2e-5 * max(1.0, float(ref.abs().max()))), (mode, float((out - ref).abs().max()))
+
+
+def test_gemm_fp32_pipe_grouped_gather_scatter():
+    G, N, Kd, M = 5, 40, 24, 37
+    w = rnd(G, N, Kd, dtype=torch.bfloat16)
+    a = rnd(50, Kd)
+    counts = [0, 11, 0, 25, 1]
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    a_rows = torch.randperm(50)[:M].to(torch.int32).to(DEV)
+    out_rows = torch.randperm(60)[:M].to(torch.int32).to(DEV)
+    out = torch.zeros(60, N, device=DEV)
+    K().gemm_simt(a, w, out, 1, m_rows=M, a_rows=a_rows, out_rows=out_rows, group_offsets=offs, n_groups=G,
+                  rows_per_group_hint=8)
+    ref = torch.zeros(60, N, device=DEV)
+    m = 0
+    for g, c in enumerate(counts):
+        for _ in range(c):
+            ref[out_rows[m]] += a[a_rows[m]] @ w[g].float().T
+            m += 1
+    assert torch.allclose(out, ref, atol=1e-5 * float(ref.abs().max()))
+
+
+TC_SHAPES = [(1, 128, 64), (8, 256, 512), (8, 7168, 5120), (17, 200, 200), (64, 5120, 8192), (100, 384, 1024),
+             (300, 640, 264), (2048, 1024, 512)]
+
+
+@pytest.mark.parametrize("T,N,Kd", TC_SHAPES)
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gemm_tensor_core_modes(T, N, Kd, mode):
+    a = rnd(T, Kd, dtype=torch.bfloat16)
+    w = rnd(2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=2, scale=Kd ** -0.5)
+    scale = rnd(T, seed=5).abs()
+    for odt in ([torch.float32] if mode == 1 else [torch.bfloat16] if mode == 2 else [torch.bfloat16, torch.float32]):
+        out = rnd(T, N, dtype=odt, seed=3)
+        ref = ref_gemm(a, w, mode, out.float().clone(), scale)
+        assert K().gemm_tc(a, w, out, mode, row_scale=scale)
+        torch.cuda.synchronize()
+        assert int(K().tc_error_flag(DEV)) == 0
+        tol = (2e-5 if odt == torch.float32 else 1e-2) * max(1.0, float(ref.abs().max()))
+        err = float((out.float() - ref).abs().max())
+        assert err <= tol, (odt, err, tol)
+
+
+def test_gemm_tensor_core_refuses_what_it_cannot_take():
+    a, w = rnd(4, 36, dtype=torch.bfloat16), rnd(128, 36, dtype=torch.bfloat16)
+    out = torch.empty(4, 128, dtype=torch.bfloat16, device=DEV)
+    assert not K().gemm_tc(a, w, out, 0)                                        # K is no multiple of 8
+    a, w = rnd(4, 64), rnd(128, 64)
+    assert not K().gemm_tc(a, w, torch.empty(4, 128, device=DEV), 0)            # float32 operands
+    from cpi_b200.parts.linear import project                                   # the dispatcher falls back
+    a, w = rnd(4, 36, dtype=torch.bfloat16), rnd(128, 36, dtype=torch.bfloat16)
+    project(a, w, out)
+    ref = a.float() @ w.float().T
+    assert float((out.float() - ref).abs().max()) <= 1e-2 * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("counts,bn_rows", [([0, 3, 0, 1, 4], 8), ([40, 0, 170, 1, 0, 29], 240), ([1], 1)])
+@pytest.mark.parametrize("mode", [1, 2])
+def test_gemm_tensor_core_grouped(counts, bn_rows, mode):
+    G, N, Kd = len(counts), 320, 256
+    M = sum(counts)
+    w = rnd(G, 2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=1, scale=Kd ** -0.5)
+    a = rnd(M + 3, Kd, dtype=torch.bfloat16)
+    scale = rnd(M, seed=4).abs()
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    if mode == 1:
+        out_rows = torch.randperm(M + 10)[:M].to(torch.int32).to(DEV)
+        out = rnd(M + 10, N, seed=7)
+        ref = out.clone()
+    else:
+        out_rows = None
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        ref = torch.zeros(M, N, device=DEV)
+    m = 0
+    for g, c in enumerate(counts):
+        for _ in range(c):
+            r = ref_gemm(a[m:m + 1], w[g], 2 if mode == 2 else 0, None, scale[m:m + 1])[0]
+            if mode == 1:
+                ref[out_rows[m]] += r
+            else:
+                ref[m] = r
+            m += 1
+    assert K().gemm_tc(a, w, out, mode, m_rows=M, out_rows=out_rows, row_scale=scale, group_offsets=offs, n_groups=G)
+    torch.cuda.synchronize()
+    assert int(K().tc_error_flag(DEV)) == 0
+    tol = (2e-5 if mode == 1 else 1e-2) * max(1.0, float(ref.abs().max()))
+    assert float((out.float() - ref).abs().max()) <= tol
+
+
+def test_gemm_tensor_core_split_k_is_deterministic():
+    a, w = rnd(8, 5120, dtype=torch.bfloat16), rnd(640, 5120, dtype=torch.bfloat16, scale=0.02)
+    outs = []
+    for _ in range(5):
+        out = torch.zeros(8, 640, device=DEV)
+        assert K().gemm_tc(a, w, out, 1)
+        outs.append(out)
+    assert all(torch.equal(outs[0], o) for o in outs[1:])
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def paged_cache(n_seq, lengths, NKV, D, page, dtype, seed=0):
+    """Random keys/values for sequences of the given lengths scattered over shuffled pages."""
+    blocks = [-(-l // page) for l in lengths]
+    n_pages = sum(blocks) + 3
+    perm = torch.randperm(n_pages, generator=torch.Generator().manual_seed(seed)).tolist()
+    table = torch.zeros(n_seq + 2, max(blocks) + 1, dtype=torch.int32)
+    k = rnd(n_pages, NKV, page, D, dtype=dtype, seed=seed + 1)
+    v = rnd(n_pages, NKV, page, D, dtype=dtype, seed=seed + 2)
+    it = iter(perm)
+    for s in range(n_seq):
+        for b in range(blocks[s]):
+            table[s + 1, b] = next(it)          # slot = s + 1
+    return k, v, table.to(DEV)
+
+
+def gather_kv(cache, table, slot, n, page):
+    rows = [cache[int(table[slot, t // page]), :, t % page, :] for t in range(n)]
+    return torch.stack(rows).float()            # [n, NKV, D]
+
+
+def ref_attention(q, k, v, pos, lo, scale):
+    """q [NH, D] at position pos over keys lo..pos; k, v [n, NKV, D]."""
+    NH, G = q.shape[0], q.shape[0] // k.shape[1]
+    out = torch.empty_like(q)
+    for h in range(NH):
+        s = (k[lo:pos + 1, h // G] @ q[h]) * scale
+        p = torch.softmax(s, 0)
+        out[h] = p @ v[lo:pos + 1, h // G]
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("NH,NKV,D,page,window", [(6, 2, 48, 16, ("full", 0)), (5, 5, 16, 64, ("chunk", 40)),
+                                                  (8, 1, 256, 32, ("sliding", 33)), (12, 4, 128, 64, ("chunk", 128))])
+def test_attention_general_over_pages(dtype, NH, NKV, D, page, window):
+    lengths = [1, 130, 77, 300]
+    k, v, table = paged_cache(len(lengths), lengths, NKV, D, page, dtype)
+    # queries: the last position of each sequence, plus window edges of the longest
+    qs = [(s, l - 1) for s, l in enumerate(lengths)]
+    wk, wsz = window
+    if wk != "full":
+        qs += [(3, wsz - 1), (3, wsz), (3, wsz + 1), (3, 2 * wsz - 1), (3, 2 * wsz)]
+    T = len(qs)
+    q = rnd(T, NH * D, dtype=dtype, seed=9)
+    out = torch.empty_like(q)
+    token_seq = torch.tensor([s for s, _ in qs], dtype=torch.int32, device=DEV)
+    token_pos = torch.tensor([p for _, p in qs], dtype=torch.int32, device=DEV)
+    seq_slot = torch.arange(1, len(lengths) + 1, dtype=torch.int32, device=DEV)
+    scale = 1.0 / math.sqrt(D)
+    K().attention_general(q, out, k, v, table, page, token_seq, token_pos, seq_slot, n_heads=NH, n_kv_heads=NKV,
+                          head_dim=D, window_kind=K().WINDOW_KINDS[wk], window_size=wsz, scale=scale)
+    for i, (s, pos) in enumerate(qs):
+        kk, vv = gather_kv(k, table, s + 1, lengths[s], page), gather_kv(v, table, s + 1, lengths[s], page)
+        lo = 0 if wk == "full" else ((pos // wsz) * wsz if wk == "chunk" else max(0, pos - wsz + 1))
+        ref = ref_attention(q[i].float().view(NH, D), kk, vv, pos, lo, scale).reshape(-1)
+        tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+        assert float((out[i].float() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max())), (i, s, pos)
+
+
+def test_attention_finds_one_far_key_among_hundreds():
+    """A key far back whose score stands out must take all the weight, wherever its page lies."""
+    NH, NKV, D, page = 4, 2, 64, 64
+    lengths = [700]
+    k, v, table = paged_cache(1, lengths, NKV, D, page, torch.float32, seed=3)
+    q = rnd(1, NH * D, seed=4)
+    far = 13
+    pg, off = int(table[1, far // page]), far % page
+    for kvh in range(NKV):
+        k[pg, kvh, off] = q.view(NH, D)[kvh * 2] * 40.0
+    out = torch.empty_like(q)
+    one = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().attention_general(q, out, k, v, table, page, one, torch.tensor([699], dtype=torch.int32, device=DEV),
+                          torch.ones(1, dtype=torch.int32, device=DEV), n_heads=NH, n_kv_heads=NKV, head_dim=D,
+                          window_kind=0, window_size=0, scale=1.0)
+    for kvh in range(NKV):
+        assert torch.allclose(out.view(NH, D)[kvh * 2], v[pg, kvh, off], atol=1e-4)
+    # with a chunk window the far key is outside: the result must change
+    out2 = torch.empty_like(q)
+    K().attention_general(q, out2, k, v, table, page, one, torch.tensor([699], dtype=torch.int32, device=DEV),
+                          torch.ones(1, dtype=torch.int32, device=DEV), n_heads=NH, n_kv_heads=NKV, head_dim=D,
+                          window_kind=1, window_size=100, scale=1.0)
+    assert float((out2 - out).abs().max()) > 0.1
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D,interleaved,norm,before,temp", [(16, False, True, False, None), (48, True, True, True, None),
+                                                            (128, False, False, False, (32.0, 0.1)),
+                                                            (256, True, True, False, (8.0, 0.5))])
+def test_qkv_post(dtype, D, interleaved, norm, before, temp):
+    NH, NKV, page, T = 3, 1, 16, 6
+    qkv = rnd(T, (NH + 2 * NKV) * D, dtype=dtype, seed=1)
+    pos = [0, 1, 31, 32, 1000, 17]
+    table = torch.tensor([[0] * 70, list(range(5, 75))], dtype=torch.int32, device=DEV)
+    kc = torch.zeros(80, NKV, page, D, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    q_out = torch.empty(T, NH * D, dtype=dtype, device=DEV)
+    inv_freq = (10000.0 ** (-torch.arange(D // 2).float() * 2 / D)).to(DEV)
+    K().qkv_post(qkv, q_out, kc, vc, table, page, torch.zeros(T, dtype=torch.int32, device=DEV),
+                 torch.tensor(pos, dtype=torch.int32, device=DEV), torch.ones(1, dtype=torch.int32, device=DEV),
+                 n_heads=NH, n_kv_heads=NKV, head_dim=D, inv_freq=inv_freq, interleaved=interleaved, qk_norm=norm,
+                 norm_before_rope=before, norm_eps=1e-5, temperature=temp)
+    x = qkv.float().view(T, NH + 2 * NKV, D)
+
+    def l2(t):
+        return t / torch.sqrt((t * t).mean(-1, keepdim=True) + 1e-5)
+
+    def rot(t):
+        ang = torch.tensor(pos, device=DEV).float()[:, None] * inv_freq[None, :]
+        c, s = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+        o = torch.empty_like(t)
+        if interleaved:
+            a, b = t[..., 0::2], t[..., 1::2]
+            o[..., 0::2], o[..., 1::2] = a * c - b * s, a * s + b * c
+        else:
+            a, b = t[..., :D // 2], t[..., D // 2:]
+            o[..., :D // 2], o[..., D // 2:] = a * c - b * s, a * s + b * c
+        return o
+
+    qk = x[:, :NH + NKV]
+    if norm and before:
+        qk = l2(qk)
+    qk = rot(qk)
+    if norm and not before:
+        qk = l2(qk)
+    qr, kr = qk[:, :NH].clone(), qk[:, NH:]
+    if temp is not None:
+        p = torch.tensor(pos, device=DEV).float()
+        qr = qr * (1 + temp[1] * torch.log(torch.floor((p + 1) / temp[0]) + 1))[:, None, None]
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    # position 1000 at high frequencies: sin/cos of a large float32 angle -- both sides use float32 angles
+    assert float((q_out.float().view(T, NH, D) - qr).abs().max()) <= tol * float(qr.abs().max())
+    for i, p_ in enumerate(pos):
+        pg = 5 + p_ // page
+        assert float((kc[pg, :, p_ % page].float() - kr[i]).abs().max()) <= tol * float(kr.abs().max())
+        assert torch.equal(vc[pg, :, p_ % page].float(), x[i, NH + NKV:])
+
+
+# ------------------------------------------------------------------------------------------------ routing
+@pytest.mark.parametrize("T,H,E,k", [(1, 40, 3, 1), (50, 96, 8, 2), (300, 128, 16, 4), (7, 64, 128, 1)])
+def test_router_and_lists(T, H, E, k):
+    h, w = rnd(T, H, dtype=torch.bfloat16), rnd(E, H, dtype=torch.bfloat16, seed=1)
+    w[1] = w[0]                                     # an exact tie: the lower index must win
+    idx = torch.empty(T, k, dtype=torch.int32, device=DEV)
+    gate = torch.empty(T, k, device=DEV)
+    logits = torch.empty(T, E, device=DEV)
+    K().router_topk(h, w, idx, gate, top_k=k, sigmoid_gate=True, logits_out=logits)
+    ref = h.float() @ w.float().T
+    assert torch.allclose(logits, ref, atol=1e-4 * float(ref.abs().max()))
+    for t in range(T):
+        row = logits[t].tolist()
+        order = sorted(range(E), key=lambda e: (-row[e], e))[:k]
+        assert idx[t].tolist() == order
+        assert torch.allclose(gate[t], torch.sigmoid(logits[t, idx[t].long()]), atol=1e-6)
+    M = T * k
+    offs = torch.empty(E + 1, dtype=torch.int32, device=DEV)
+    row_token = torch.empty(M, dtype=torch.int32, device=DEV)
+    row_scale = torch.empty(M, device=DEV)
+    row_of_slot = torch.empty(M, dtype=torch.int32, device=DEV)
+    K().moe_lists(idx, gate, offs, row_token, row_scale, row_of_slot, n_tokens=T, top_k=k, n_experts=E)
+    flat = idx.flatten().tolist()
+    counts = [flat.count(e) for e in range(E)]
+    assert offs.tolist() == [0] + list(torch.tensor(counts).cumsum(0).tolist())
+    assert sorted(row_of_slot.tolist()) == list(range(M))
+    for s in range(M):
+        m = int(row_of_slot[s])
+        assert offs[flat[s]] <= m < offs[flat[s] + 1]
+        assert int(row_token[m]) == s // k and float(row_scale[m]) == float(gate.flatten()[s])
+    for e in range(E):                               # stable: rows of an expert in token order
+        seg = row_token[int(offs[e]):int(offs[e + 1])].tolist()
+        assert seg == sorted(seg)
+
+
+def test_moe_combine_and_gather_and_swiglu():
+    T, k, H = 9, 3, 200
+    res = rnd(T, H)
+    y = rnd(T * k, H, seed=1)
+    ros = torch.randperm(T * k).to(torch.int32).to(DEV)
+    ref = res.clone()
+    for t in range(T):
+        for j in range(k):
+            ref[t] += y[ros[t * k + j]]
+    K().moe_combine(res, y, ros, top_k=k)
+    assert torch.allclose(res, ref, atol=1e-6)
+    src = rnd(11, 72, dtype=torch.bfloat16)
+    rows = torch.tensor([10, 0, 0, 5], dtype=torch.int32, device=DEV)
+    dst = torch.empty(4, 72, dtype=torch.bfloat16, device=DEV)
+    K().gather_rows(src, rows, dst)
+    assert torch.equal(dst, src[rows.long()])
+    gu = rnd(5, 2 * 33)
+    out = torch.empty(5, 33, device=DEV)
+    K().swiglu(gu, out)
+    g, u = gu[:, :33], gu[:, 33:]
+    assert torch.allclose(out, g / (1 + torch.exp(-g)) * u, atol=1e-6)
+
+
+def test_argmax_first_maximum_and_odd_vocabulary():
+    V = 202049
+    lg = rnd(3, V)
+    lg[0, 777] = lg[0, 200000] = 50.0
+    lg[2, V - 1] = 60.0
+    out = torch.empty(3, dtype=torch.int32, device=DEV)
+    K().argmax(lg, out)
+    assert out.tolist() == [777, int(lg[1].argmax()), V - 1]
