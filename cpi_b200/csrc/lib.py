@@ -242,6 +242,35 @@ def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq
           c_int(window_size), c_float(scale), _stream())
 
 
+_dec_scratch = {}
+
+
+def attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool:
+    return bool(load().cpi_attention_decode_supported(c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+                                                      c_int(page_size)))
+
+
+def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
+                     n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, n_splits):
+    """bfloat16 attention of independent tokens against the paged cache, keys split over `n_splits` blocks."""
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot)
+    assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
+    T = q.shape[0]
+    po = pml = None
+    if n_splits > 1:
+        idx = q.device.index or 0
+        need = T * n_heads * n_splits * (head_dim + 2)
+        buf = _dec_scratch.get(idx)
+        if buf is None or buf.numel() < need:
+            buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
+            _dec_scratch[idx] = buf
+        po, pml = buf, buf[T * n_heads * n_splits * head_dim:]
+    _call("cpi_attention_decode", _p(q), _p(out), _p(k_cache), _p(v_cache), _p(page_table),
+          c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(T),
+          c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale),
+          c_int(n_splits), _p(po), _p(pml), _stream())
+
+
 def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None):
     _need_cuda(h, w, topk_idx, topk_gate, logits_out)
     _rowmajor(h, "router h")

@@ -11,38 +11,41 @@ namespace cpi {
 
 constexpr int kMaxExperts = 256;
 
-// one warp per token
+// one block per token: the warps share the experts, thread 0 picks the top k
+constexpr int ROUTER_WARPS = 8;
+
 template <typename TH, typename TW>
-__global__ void router_topk_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
-                                   float* __restrict__ logits_out, int* __restrict__ topk_idx,
-                                   float* __restrict__ topk_gate, int n_tokens, int hidden, int n_experts,
-                                   int top_k, int gate_mode) {
-  __shared__ float lg[4][kMaxExperts];
+__global__ void __launch_bounds__(ROUTER_WARPS * 32)
+router_topk_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
+                   float* __restrict__ logits_out, int* __restrict__ topk_idx,
+                   float* __restrict__ topk_gate, int n_tokens, int hidden, int n_experts,
+                   int top_k, int gate_mode) {
+  __shared__ float lg[kMaxExperts];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x * 4 + warp;
-  if (t >= n_tokens) return;
+  const int t = blockIdx.x;
   const TH* x = h + (size_t)t * h_stride;
-  for (int e = 0; e < n_experts; ++e) {
+  for (int e = warp; e < n_experts; e += ROUTER_WARPS) {
     const TW* wr = w + (size_t)e * hidden;
-    float s = 0.f;
+    float s = 0.f;                                  // lane-strided partial sums, then a fixed warp tree
+#pragma unroll 4
     for (int i = lane; i < hidden; i += 32) s = fmaf(to_f32(x[i]), to_f32(wr[i]), s);
     s = warp_sum(s);
     if (lane == 0) {
-      lg[warp][e] = s;
+      lg[e] = s;
       if (logits_out) logits_out[(size_t)t * n_experts + e] = s;
     }
   }
-  __syncwarp();
-  if (lane == 0) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
     for (int k = 0; k < top_k; ++k) {
       int best = -1;
       for (int e = 0; e < n_experts; ++e) {
-        const float v = lg[warp][e];
+        const float v = lg[e];
         if (v != v) continue;                       // NaN never wins
         bool taken = false;
         for (int j = 0; j < k; ++j) taken |= (topk_idx[(size_t)t * top_k + j] == e);
         if (taken) continue;
-        if (best < 0 || v > lg[warp][best]) best = e;
+        if (best < 0 || v > lg[best]) best = e;
       }
       if (best < 0) {                               // all NaN: fall back to the lowest free index
         for (int e = 0; e < n_experts && best < 0; ++e) {
@@ -52,7 +55,7 @@ __global__ void router_topk_kernel(const TH* __restrict__ h, long h_stride, cons
         }
       }
       topk_idx[(size_t)t * top_k + k] = best;
-      const float r = lg[warp][best];
+      const float r = lg[best];
       topk_gate[(size_t)t * top_k + k] = gate_mode == 0 ? 1.0f : 1.0f / (1.0f + expf(-r));
     }
   }
@@ -108,7 +111,7 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
   CPI_REQUIRE(n_experts >= 1 && n_experts <= kMaxExperts, "router: %d experts (supported: 1..%d)", n_experts, kMaxExperts);
   CPI_REQUIRE(top_k >= 1 && top_k <= n_experts, "router: top-k %d of %d experts", top_k, n_experts);
   CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-      (router_topk_kernel<TH, TW><<<(n_tokens + 3) / 4, 128, 0, stream>>>(
+      (router_topk_kernel<TH, TW><<<n_tokens, ROUTER_WARPS * 32, 0, stream>>>(
           (const TH*)h, h_stride, (const TW*)w, logits_out, topk_idx, topk_gate, n_tokens, hidden,
           n_experts, top_k, gate_mode))));
   return check_launch("router_topk");

@@ -95,6 +95,20 @@ class AttentionMixer(Mixer):
         project(att, self.w_o, residual, MODE_ADD)
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
+        wk = K.WINDOW_KINDS[self.window_kind]
+        if (batch.is_decode and q.dtype == torch.bfloat16
+                and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
+            # keys per sequence that the window lets through, at most
+            longest = max(s + 1 for s in batch.starts)
+            if self.window_kind != "full":
+                longest = min(longest, self.window_size + page_size)
+            pages = -(-longest // page_size)
+            want = -(-444 // (batch.n_tokens * self.nkv))          # about three blocks per SM
+            n_splits = max(1, min(want, pages // 2))
+            K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                               batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+                               window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)
+            return
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                             window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,

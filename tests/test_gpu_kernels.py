@@ -380,3 +380,55 @@ def test_argmax_first_maximum_and_odd_vocabulary():
     out = torch.empty(3, dtype=torch.int32, device=DEV)
     K().argmax(lg, out)
     assert out.tolist() == [777, int(lg[1].argmax()), V - 1]
+
+
+@pytest.mark.parametrize("NH,NKV,D,window,splits", [(40, 8, 128, ("full", 0), 1), (40, 8, 128, ("full", 0), 7),
+                                                    (6, 2, 64, ("chunk", 100), 3), (16, 1, 128, ("sliding", 70), 2),
+                                                    (5, 5, 64, ("chunk", 64), 4)])
+def test_attention_decode_tensor_core_kernel(NH, NKV, D, window, splits):
+    page = 64
+    lengths = [1, 64, 65, 700, 333, 128]
+    k, v, table = paged_cache(len(lengths), lengths, NKV, D, page, torch.bfloat16, seed=5)
+    # stale contents beyond a sequence's length must not leak: poison the tail of every last page
+    for s, l in enumerate(lengths):
+        if l % page:
+            pg = int(table[s + 1, (l - 1) // page])
+            k[pg, :, l % page:] = float("nan")
+            v[pg, :, l % page:] = float("nan")
+    T = len(lengths)
+    q = rnd(T, NH * D, dtype=torch.bfloat16, seed=9)
+    out = torch.empty_like(q)
+    token_seq = torch.arange(T, dtype=torch.int32, device=DEV)
+    token_pos = torch.tensor([l - 1 for l in lengths], dtype=torch.int32, device=DEV)
+    seq_slot = torch.arange(1, T + 1, dtype=torch.int32, device=DEV)
+    wk, wsz = window
+    scale = 1.0 / math.sqrt(D)
+    assert K().attention_decode_supported(NH, NKV, D, page)
+    K().attention_decode(q, out, k, v, table, page, token_seq, token_pos, seq_slot, n_heads=NH, n_kv_heads=NKV,
+                         head_dim=D, window_kind=K().WINDOW_KINDS[wk], window_size=wsz, scale=scale, n_splits=splits)
+    for i, l in enumerate(lengths):
+        pos = l - 1
+        kk = gather_kv(torch.nan_to_num(k), table, i + 1, l, page)
+        vv = gather_kv(torch.nan_to_num(v), table, i + 1, l, page)
+        lo = 0 if wk == "full" else ((pos // wsz) * wsz if wk == "chunk" else max(0, pos - wsz + 1))
+        ref = ref_attention(q[i].float().view(NH, D), kk, vv, pos, lo, scale).reshape(-1)
+        err = float((out[i].float() - ref).abs().max())
+        assert err <= 1.5e-2 * max(1.0, float(ref.abs().max())), (i, l, err)
+    assert not K().attention_decode_supported(12, 4, 48, 64) and not K().attention_decode_supported(34, 2, 128, 64)
+
+
+def test_attention_decode_far_key():
+    NH, NKV, D, page = 10, 2, 128, 64
+    k, v, table = paged_cache(1, [2000], NKV, D, page, torch.bfloat16, seed=3)
+    q = rnd(1, NH * D, dtype=torch.bfloat16, seed=4)
+    far = 77
+    pg, off = int(table[1, far // page]), far % page
+    for kvh in range(NKV):
+        k[pg, kvh, off] = (q.view(NH, D)[kvh * 5 + 2].float() * 30.0).bfloat16()
+    out = torch.empty_like(q)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    K().attention_decode(q, out, k, v, table, page, z, torch.tensor([1999], dtype=torch.int32, device=DEV),
+                         torch.ones(1, dtype=torch.int32, device=DEV), n_heads=NH, n_kv_heads=NKV, head_dim=D,
+                         window_kind=0, window_size=0, scale=1.0, n_splits=5)
+    for kvh in range(NKV):
+        assert torch.allclose(out.view(NH, D)[kvh * 5 + 2].float(), v[pg, kvh, off].float(), atol=2e-2)
