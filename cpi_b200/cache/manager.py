@@ -94,8 +94,9 @@ class KVGroup:
         self.page_size, self.max_blocks = page_size, max_blocks
         self.pool = PagePool(n_pages)
         shape = (len(entries), n_pages, req.n_kv_heads, page_size, req.head_dim)
-        self.k = torch.empty(shape, dtype=dtype, device=device)
-        self.v = torch.empty(shape, dtype=dtype, device=device)
+        # zeroed once: a tensor-core kernel multiplies masked positions by zero, which needs finite values
+        self.k = torch.zeros(shape, dtype=dtype, device=device)
+        self.v = torch.zeros(shape, dtype=dtype, device=device)
         self.table_host = torch.zeros((max_slots, max_blocks), dtype=torch.int32)
         self.table = torch.zeros((max_slots, max_blocks), dtype=torch.int32, device=device)
         self.blocks: list[dict] = [dict() for _ in range(max_slots)]     # slot -> {block: page}

@@ -1,0 +1,371 @@
+// Prefill attention in bfloat16 on tcgen05: tiles of 128 queries of one head against the paged cache.
+//
+// A CTA owns 128 consecutive tokens of one sequence and one query head.  Warp 4 streams key/value tiles
+// (128 positions = two cache pages, through TMA with the 128-byte swizzle, two stages); one thread of
+// warp 5 issues the MMAs; warps 0-3 are the softmax: thread r owns query row r, so row maxima and sums
+// need no shuffles.  Per key tile:
+//     S = Q K^T            tcgen05.mma, both operands K-major from shared memory, S in tensor memory
+//     P = 2^(S*c - m)      read S with tcgen05.ld, mask by position, write P as bf16 into shared memory
+//     O_tile = P V         tcgen05.mma, V consumed MN-major straight from the page layout [position][dim]
+//     O = O * alpha + O_tile   in registers (thread r keeps its output row in float32)
+// Masks: key position <= query position, and >= the window's low end (chunk or sliding window).  The
+// last tile's value rows beyond the newest position are zeroed in shared memory, so stale page contents
+// cannot reach the product (0 * NaN).  Formulas: src/engine/llama4_cpu_engine.cpp:195-250; the
+// reference's own prefill is a loop of single-token forwards (src/engine/llama4_cuda_engine.cu:571-580).
+//
+// Every mbarrier wait is bounded; when one runs out the CTA sets *error_flag and leaves.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace cpi {
+namespace tc {
+// from gemm_tc.cu
+int get_map_2d_bf16(const void* ptr, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner,
+                    uint32_t box_rows, CUtensorMap* out);
+}
+namespace pre {
+
+constexpr int BQ = 128, BKV = 128, PAGE = 64;
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct Params {
+  __nv_bfloat16* out;                 // [T, NH * D]
+  const int* page_table; int max_blocks;
+  const int* token_pos; const int* token_seq; const int* seq_slot;
+  const int* tile_tok0; const int* tile_rows;     // per query tile: first packed token, valid rows
+  int n_heads, n_kv_heads;
+  int window_kind, window_size;
+  float scale_log2;
+  int* error_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && *abort_flag) return false;
+  }
+  *abort_flag = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+               ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// shared-memory matrix descriptor, 128-byte swizzle; lbo/sbo in bytes
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFF) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFF) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+__host__ __device__ constexpr uint32_t instr_desc(int m, int n, int b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+         ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ int window_low(int kind, int size, int pos) {
+  if (kind == 1) return (pos / size) * size;
+  if (kind == 2) return max(0, pos - size + 1);
+  return 0;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D>
+__global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                const __grid_constant__ CUtensorMap map_k,
+                                                                const __grid_constant__ CUtensorMap map_v, Params p) {
+  constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a row
+  constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows x 128 bytes
+  constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES;
+  constexpr uint32_t KV_BYTES = HALVES * HALF_BYTES;   // one of K or V, 128 positions
+  constexpr uint32_t P_BYTES = 2 * HALF_BYTES;         // 128 rows x 128 keys
+  constexpr uint32_t TMEM_COLS = 256;                  // S: 128 columns, O tile: D columns
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* kv_s = q_s + Q_BYTES;                       // [stage][K | V]
+  uint8_t* p_s = kv_s + 2 * 2 * KV_BYTES;
+
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int kvh = head / (p.n_heads / p.n_kv_heads);
+  const int tok0 = p.tile_tok0[tile], rows = p.tile_rows[tile];
+  const int slot = p.seq_slot[p.token_seq[tok0]];
+  const int pos_first = p.token_pos[tok0], pos_last = pos_first + rows - 1;
+  const int lo_first = window_low(p.window_kind, p.window_size, pos_first);
+  const int kt_begin = lo_first / BKV, kt_end = pos_last / BKV + 1;
+  const int n_kt = kt_end - kt_begin;
+
+  if (tid == 0) {
+    mbar_init(&q_full, 1);
+    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
+    mbar_init(&s_full, 1); mbar_init(&p_full, 128); mbar_init(&o_full, 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+  volatile int* abort_flag = &abort_s;
+  bool ok = true;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- TMA producer ----
+      mbar_expect_tx(&q_full, Q_BYTES);
+      for (int h = 0; h < HALVES; ++h) tma_load_2d(q_s + h * HALF_BYTES, &map_q, &q_full, head * D + h * 64, tok0);
+      const int* table = p.page_table + (size_t)slot * p.max_blocks;
+      const int last_block = pos_last / PAGE;
+      for (int i = 0; i < n_kt; ++i) {
+        const int s = i & 1;
+        if (i >= 2 && !mbar_wait(&kv_empty[s], ((i >> 1) - 1) & 1, abort_flag)) break;
+        uint8_t* ks = kv_s + (size_t)s * 2 * KV_BYTES;
+        uint8_t* vs = ks + KV_BYTES;
+        const int blk0 = (kt_begin + i) * (BKV / PAGE);
+        const int n_pages = min(BKV / PAGE, last_block - blk0 + 1);
+        mbar_expect_tx(&kv_full[s], (uint32_t)n_pages * 2u * HALVES * (PAGE * 128));
+        for (int pg = 0; pg < n_pages; ++pg) {
+          const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
+          for (int h = 0; h < HALVES; ++h) {
+            tma_load_2d(ks + h * HALF_BYTES + pg * (PAGE * 128), &map_k, &kv_full[s], h * 64, row);
+            tma_load_2d(vs + h * HALF_BYTES + pg * (PAGE * 128), &map_v, &kv_full[s], h * 64, row);
+          }
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0);
+      constexpr uint32_t idesc_o = instr_desc(BQ, D, 1);
+      ok = mbar_wait(&q_full, 0, abort_flag);
+      for (int i = 0; i < n_kt && ok; ++i) {
+        const int s = i & 1;
+        ok = mbar_wait(&kv_full[s], (i >> 1) & 1, abort_flag);
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t qa = smem_u32(q_s), ka = smem_u32(kv_s + (size_t)s * 2 * KV_BYTES), va = ka + KV_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
+          umma_bf16(tmem_s, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, ks > 0);
+        }
+        umma_commit(&s_full);
+        ok = mbar_wait(&p_full, i & 1, abort_flag);
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t pa = smem_u32(p_s);
+#pragma unroll
+        for (int j = 0; j < BKV / 16; ++j) {
+          const uint32_t poff = (j >> 2) * HALF_BYTES + (j & 3) * 32;
+          umma_bf16(tmem_o, smem_desc(pa + poff, 16, 1024), smem_desc(va + j * 2048, HALF_BYTES, 1024), idesc_o, j > 0);
+        }
+        umma_commit(&o_full);
+        umma_commit(&kv_empty[s]);
+      }
+    }
+  } else {
+    // ---- softmax: thread `row` owns one query row ----
+    const int row = tid;
+    const bool live = row < rows;
+    const int qp = live ? p.token_pos[tok0 + row] : -1;
+    const int lo = live ? window_low(p.window_kind, p.window_size, qp) : 0;
+    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
+    float m_run = -1e30f, l_run = 0.f;
+    float o[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o[i] = 0.f;
+
+    for (int i = 0; i < n_kt && ok; ++i) {
+      const int key0 = (kt_begin + i) * BKV;
+      ok = mbar_wait(&s_full, i & 1, abort_flag);
+      if (!ok) break;
+      fence_after_sync();
+      // pass 1: row maximum
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + lane_addr + c, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kp = key0 + c + e;
+          if (kp <= qp && kp >= lo) mx = fmaxf(mx, v[e] * p.scale_log2);
+        }
+      }
+      const float m_new = fmaxf(m_run, mx);
+      const float alpha = exp2f(m_run - m_new);
+      m_run = m_new;
+      // the last tile: zero the value rows beyond the newest position (this thread: key row `row`)
+      if (i == n_kt - 1) {
+        ok = mbar_wait(&kv_full[i & 1], (i >> 1) & 1, abort_flag);
+        if (ok && key0 + row > pos_last) {
+          uint8_t* vs = kv_s + (size_t)(i & 1) * 2 * KV_BYTES + KV_BYTES;
+#pragma unroll
+          for (int h = 0; h < HALVES; ++h) {
+            uint4* r4 = reinterpret_cast<uint4*>(vs + h * HALF_BYTES + row * 128);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) r4[q] = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+      // pass 2: P = 2^(s - m) as bf16 into shared memory (K-major, swizzled), row sum
+      float ls = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < BKV; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_s + lane_addr + c, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int kp = key0 + c + e;
+          const float pe = (kp <= qp && kp >= lo) ? exp2f(v[e] * p.scale_log2 - m_new) : 0.f;
+          v[e] = pe;
+          ls += pe;
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int col = c + g * 8;
+          const int chunk = (col & 63) >> 3;
+          uint4 w = make_uint4(pack_bf16(v[g * 8], v[g * 8 + 1]), pack_bf16(v[g * 8 + 2], v[g * 8 + 3]),
+                               pack_bf16(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16(v[g * 8 + 6], v[g * 8 + 7]));
+          *reinterpret_cast<uint4*>(p_s + (col >> 6) * HALF_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = w;
+        }
+      }
+      l_run = l_run * alpha + ls;
+      fence_async_proxy();
+      fence_before_sync();
+      mbar_arrive(&p_full);
+      // O = O * alpha + P V
+      ok = ok && mbar_wait(&o_full, i & 1, abort_flag);
+      if (!ok) break;
+      fence_after_sync();
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        float v[32];
+        tmem_ld32(tmem_o + lane_addr + c, v);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) o[c + e] = o[c + e] * alpha + v[e];
+      }
+      fence_before_sync();
+    }
+    if (ok && live) {
+      const float inv = 1.0f / fmaxf(l_run, 1e-20f);
+      __nv_bfloat16* dst = p.out + ((size_t)(tok0 + row) * p.n_heads + head) * D;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        uint4 w = make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
+                             pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
+        *reinterpret_cast<uint4*>(dst + c) = w;
+      }
+    }
+  }
+  if (abort_s) {
+    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(TMEM_COLS));
+}
+
+}  // namespace pre
+}  // namespace cpi
+
+using namespace cpi;
+
+extern "C" int cpi_attention_prefill_supported(int n_heads, int n_kv_heads, int head_dim, int page_size) {
+  if (n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
+  return (head_dim == 64 || head_dim == 128) && page_size == pre::PAGE;
+}
+
+// q, out [T, NH*D] bfloat16; k_cache, v_cache [n_pages, NKV, 64, D] bfloat16 of one layer.
+// tile_tok0 / tile_rows (device, int32 [n_tiles]): first packed token and valid rows (1..128) of each query
+// tile; the tokens of a tile belong to one sequence and have consecutive positions.
+extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, long n_pages,
+                                     const int* page_table, int max_blocks, int page_size, const int* token_seq,
+                                     const int* token_pos, const int* seq_slot, const int* tile_tok0,
+                                     const int* tile_rows, int n_tiles, int n_tokens, int n_heads, int n_kv_heads,
+                                     int head_dim, int window_kind, int window_size, float scale, int* error_flag,
+                                     cudaStream_t stream) {
+  if (n_tiles == 0) return 0;
+  CPI_REQUIRE(cpi_attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size),
+              "attention_prefill: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
+  CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention_prefill: window kind %d needs a size > 0", window_kind);
+  CPI_REQUIRE(n_heads <= 65535, "attention_prefill: too many heads");
+  CUtensorMap mq, mk, mv;
+  const uint64_t q_width = (uint64_t)n_heads * head_dim;
+  if (tc::get_map_2d_bf16(q, q_width, (uint64_t)n_tokens, q_width * 2, 64, pre::BQ, &mq)) return 1;
+  const uint64_t kv_rows = (uint64_t)n_pages * n_kv_heads * pre::PAGE;
+  if (tc::get_map_2d_bf16(k_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mk)) return 1;
+  if (tc::get_map_2d_bf16(v_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mv)) return 1;
+  pre::Params p{(__nv_bfloat16*)out, page_table, max_blocks, token_pos, token_seq, seq_slot, tile_tok0, tile_rows,
+                n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag};
+  dim3 grid(n_tiles, n_heads);
+  const int halves = head_dim / 64;
+  const int smem = halves * 128 * 128 * (1 + 4) + 2 * 128 * 128 + 1024;
+  if (head_dim == 128) {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
+    pre::attention_prefill_kernel<128><<<grid, 192, smem, stream>>>(mq, mk, mv, p);
+  } else {
+    static bool set = false;
+    if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
+    pre::attention_prefill_kernel<64><<<grid, 192, smem, stream>>>(mq, mk, mv, p);
+  }
+  return check_launch("attention_prefill");
+}

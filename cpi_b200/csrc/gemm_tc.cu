@@ -365,6 +365,12 @@ static int get_map(const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint6
   return 0;
 }
 
+// 2-D bf16 tensor [rows][inner] with a row stride in bytes; box box_inner x box_rows (other kernels use it too)
+int get_map_2d_bf16(const void* ptr, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner,
+                    uint32_t box_rows, CUtensorMap* out) {
+  return get_map(ptr, inner, rows, 0, row_stride_bytes, 0, box_inner, box_rows, out);
+}
+
 template <int BN, int MODE, typename TO>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
   constexpr int ACC = MODE == kSwiglu ? 2 : 1;

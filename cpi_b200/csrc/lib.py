@@ -271,6 +271,24 @@ def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq,
           c_int(n_splits), _p(po), _p(pml), _stream())
 
 
+def attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool:
+    return bool(load().cpi_attention_prefill_supported(c_int(n_heads), c_int(n_kv_heads), c_int(head_dim),
+                                                       c_int(page_size)))
+
+
+def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, tile_tok0,
+                      tile_rows, *, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale):
+    """bfloat16 attention of query tiles (<= 128 consecutive tokens of one sequence each) on tcgen05."""
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, tile_tok0, tile_rows)
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
+    _call("cpi_attention_prefill", _p(q), _p(out), _p(k_cache), _p(v_cache), c_long(k_cache.shape[0]), _p(page_table),
+          c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), _p(tile_tok0),
+          _p(tile_rows), c_int(tile_tok0.numel()), c_int(q.shape[0]), c_int(n_heads), c_int(n_kv_heads),
+          c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale), _p(tc_error_flag(q.device)),
+          _stream())
+
+
 def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=None):
     _need_cuda(h, w, topk_idx, topk_gate, logits_out)
     _rowmajor(h, "router h")

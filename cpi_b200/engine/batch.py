@@ -13,6 +13,9 @@ from dataclasses import dataclass
 import torch
 
 
+Q_TILE = 128      # query rows per tile of the prefill attention kernel
+
+
 @dataclass
 class StepBatch:
     n_tokens: int
@@ -30,6 +33,9 @@ class StepBatch:
     slots: list
     starts: list
     n_new: list
+    n_q_tiles: int = 0                 # prefill only: tiles of up to 128 consecutive tokens of one sequence,
+    tile_tok0: torch.Tensor = None     # first packed token of each tile, longest context first
+    tile_rows: torch.Tensor = None     # tokens in each tile
 
     @property
     def is_decode(self) -> bool:
@@ -66,7 +72,16 @@ class BatchStager:
         n_new = [len(t) for t in token_lists]
         T = sum(n_new)
         R = sum(len(w) for w in wants)
-        total = 3 * T + 3 * B + R
+        tiles = []
+        if max(n_new) > 1:
+            base = 0
+            for n, st in zip(n_new, starts):
+                for off in range(0, n, Q_TILE):
+                    rows = min(Q_TILE, n - off)
+                    tiles.append((st + off + rows, base + off, rows))
+                base += n
+            tiles.sort(key=lambda x: -x[0])          # most keys first: the long tiles start early
+        total = 3 * T + 3 * B + R + 2 * len(tiles)
         self._reserve(total)
         entry = self._ring[self._next]
         self._next = (self._next + 1) % self.RING
@@ -82,7 +97,8 @@ class BatchStager:
             token_pos += range(st, st + n)
             want_rows += [base + i for i in w]
             base += n
-        flat = tokens + token_seq + token_pos + list(slots) + list(starts) + n_new + want_rows
+        flat = (tokens + token_seq + token_pos + list(slots) + list(starts) + n_new + want_rows
+                + [t[1] for t in tiles] + [t[2] for t in tiles])
         h[:total] = torch.tensor(flat, dtype=torch.int32)
         d[:total].copy_(h[:total], non_blocking=True)
         self.bytes_staged = total * 4
@@ -100,4 +116,5 @@ class BatchStager:
         return StepBatch(n_tokens=T, n_seqs=B, n_want=R, max_new=max(n_new), dtype=dtype,
                          tokens=take(T), token_seq=take(T), token_pos=take(T), seq_slot=take(B),
                          seq_start=take(B), seq_new=take(B), want_rows=take(R),
-                         slots=list(slots), starts=list(starts), n_new=n_new)
+                         slots=list(slots), starts=list(starts), n_new=n_new,
+                         n_q_tiles=len(tiles), tile_tok0=take(len(tiles)), tile_rows=take(len(tiles)))

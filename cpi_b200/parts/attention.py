@@ -109,6 +109,13 @@ class AttentionMixer(Mixer):
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                                window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)
             return
+        if (not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
+                and K.attention_prefill_supported(self.nh, self.nkv, self.d, page_size)):
+            K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                                batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=self.nh,
+                                n_kv_heads=self.nkv, head_dim=self.d, window_kind=wk, window_size=self.window_size,
+                                scale=self.scale)
+            return
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                             window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,

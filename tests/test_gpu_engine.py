@@ -31,13 +31,14 @@ def vocab(name):
     return c.get("text_config", c)["vocab_size"]
 
 
-CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")]
+CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")] + [("C", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_whole_prompts_each_alone(name, dtype):
     e = engine(name, dtype)
-    reqs = {f"r{n}": tiny.random_tokens(n, vocab(name), 100 + n) for n in (1, 5, 33, 70, 150)}
+    lengths = (1, 64, 129, 400) if name == "C" else (1, 5, 33, 70, 150)
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab(name), 100 + n) for n in lengths}
     rp = Replay(e)
     for rid, toks in reqs.items():
         rp.step([(rid, toks, list(range(len(toks))))])
@@ -50,7 +51,7 @@ def test_whole_prompts_each_alone(name, dtype):
 @pytest.mark.parametrize("name,dtype", CASES)
 def test_last_32_tokens_one_by_one(name, dtype):
     e = engine(name, dtype)
-    reqs = {f"r{n}": tiny.random_tokens(n, vocab(name), 200 + n) for n in (33, 70, 131)}
+    reqs = {f"r{n}": tiny.random_tokens(n, vocab(name), 200 + n) for n in ((33, 170, 340) if name == "C" else (33, 70, 131))}
     rp = Replay(e)
     for rid, toks in reqs.items():
         n = len(toks)
@@ -68,7 +69,8 @@ def test_last_32_tokens_one_by_one(name, dtype):
 def test_unequal_batches_one_after_another(name, dtype):
     """Batches of unequal prompts whose shorter requests end earlier; the cache is sized for one batch,
     so the second and third batch run in slots and pages that the first one gave back."""
-    shapes = {"A": [(5, 24), (17, 9), (40, 24)], "B": [(1, 16), (9, 3), (33, 16), (70, 7)]}[name]
+    shapes = {"A": [(5, 24), (17, 9), (40, 24)], "B": [(1, 16), (9, 3), (33, 16), (70, 7)],
+              "C": [(150, 20), (3, 8), (260, 20), (64, 1)]}[name]
     need = sum(-(-(p + d) // 64) * 64 for p, d in shapes)
     e = engine(name, dtype, max_tokens=need)
     all_reqs = {}

@@ -432,3 +432,73 @@ def test_attention_decode_far_key():
                          window_kind=0, window_size=0, scale=1.0, n_splits=5)
     for kvh in range(NKV):
         assert torch.allclose(out.view(NH, D)[kvh * 5 + 2].float(), v[pg, kvh, off].float(), atol=2e-2)
+
+
+def _prefill_case(NH, NKV, D, window, seqs, seed=0):
+    """seqs: list of (cached positions before the step, new tokens).  Returns everything a launch needs."""
+    page = 64
+    lengths = [s + n for s, n in seqs]
+    k, v, table = paged_cache(len(seqs), lengths, NKV, D, page, torch.bfloat16, seed=seed)
+    for i, l in enumerate(lengths):                  # poison what lies beyond each sequence
+        if l % page:
+            pg = int(table[i + 1, (l - 1) // page])
+            k[pg, :, l % page:] = float("nan")
+            v[pg, :, l % page:] = float("nan")
+    token_seq, token_pos, tiles = [], [], []
+    base = 0
+    for i, (s, n) in enumerate(seqs):
+        token_seq += [i] * n
+        token_pos += list(range(s, s + n))
+        for off in range(0, n, 128):
+            tiles.append((base + off, min(128, n - off)))
+        base += n
+    T = base
+    q = rnd(T, NH * D, dtype=torch.bfloat16, seed=seed + 7)
+    dev = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return dict(q=q, k=k, v=v, table=table, token_seq=dev(token_seq), token_pos=dev(token_pos),
+                seq_slot=torch.arange(1, len(seqs) + 1, dtype=torch.int32, device=DEV),
+                tile_tok0=dev([t[0] for t in tiles]), tile_rows=dev([t[1] for t in tiles]),
+                lengths=lengths, pos=token_pos, seq=token_seq)
+
+
+@pytest.mark.parametrize("NH,NKV,D,window", [(4, 2, 128, ("full", 0)), (6, 6, 64, ("chunk", 200)),
+                                             (5, 1, 128, ("sliding", 130)), (8, 2, 64, ("chunk", 128))])
+def test_attention_prefill_tensor_core_kernel(NH, NKV, D, window):
+    page = 64
+    c = _prefill_case(NH, NKV, D, window, [(0, 1), (0, 129), (0, 300), (70, 200), (256, 64), (0, 64)])
+    out = torch.full_like(c["q"], float("nan"))
+    wk, wsz = window
+    scale = 1.0 / math.sqrt(D)
+    assert K().attention_prefill_supported(NH, NKV, D, page)
+    K().attention_prefill(c["q"], out, c["k"], c["v"], c["table"], page, c["token_seq"], c["token_pos"], c["seq_slot"],
+                          c["tile_tok0"], c["tile_rows"], n_heads=NH, n_kv_heads=NKV, head_dim=D,
+                          window_kind=K().WINDOW_KINDS[wk], window_size=wsz, scale=scale)
+    torch.cuda.synchronize()
+    assert int(K().tc_error_flag(DEV)) == 0
+    kk = [gather_kv(torch.nan_to_num(c["k"]), c["table"], i + 1, l, page) for i, l in enumerate(c["lengths"])]
+    vv = [gather_kv(torch.nan_to_num(c["v"]), c["table"], i + 1, l, page) for i, l in enumerate(c["lengths"])]
+    worst = 0.0
+    for t, (s, pos) in enumerate(zip(c["seq"], c["pos"])):
+        lo = 0 if wk == "full" else ((pos // wsz) * wsz if wk == "chunk" else max(0, pos - wsz + 1))
+        ref = ref_attention(c["q"][t].float().view(NH, D), kk[s], vv[s], pos, lo, scale).reshape(-1)
+        err = float((out[t].float() - ref).abs().max()) / max(1.0, float(ref.abs().max()))
+        worst = max(worst, err)
+        assert err <= 1.5e-2, (t, s, pos, err)
+    print("prefill attention worst error", worst)
+
+
+def test_attention_prefill_far_key_and_general_kernel_agree():
+    NH, NKV, D, page = 4, 1, 128, 64
+    c = _prefill_case(NH, NKV, D, ("full", 0), [(0, 900)], seed=3)
+    far = 5
+    pg, off = int(c["table"][1, far // page]), far % page
+    c["k"][pg, 0, off] = (c["q"][899].view(NH, D)[1].float() * 30.0).bfloat16()
+    out = torch.empty_like(c["q"])
+    args = (c["k"], c["v"], c["table"], page, c["token_seq"], c["token_pos"], c["seq_slot"])
+    K().attention_prefill(c["q"], out, *args, c["tile_tok0"], c["tile_rows"], n_heads=NH, n_kv_heads=NKV, head_dim=D,
+                          window_kind=0, window_size=0, scale=1.0)
+    assert torch.allclose(out[899].view(NH, D)[1].float(), c["v"][pg, 0, off].float(), atol=2e-2)
+    gen = torch.empty_like(c["q"])
+    K().attention_general(c["q"], gen, *args, n_heads=NH, n_kv_heads=NKV, head_dim=D, window_kind=0, window_size=0,
+                          scale=1.0)
+    assert float((out.float() - gen.float()).abs().max()) <= 2e-2 * float(gen.float().abs().max())

@@ -58,7 +58,22 @@ TINY_R = {
     "tie_word_embeddings": False,
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "R": (TINY_R, 2)}
+# C: head size 64 and widths that are multiples of 8, so that the bfloat16 path runs on the tensor-core
+# kernels (GEMM, prefill and decode attention); chunk and temperature floor inside a few hundred tokens.
+TINY_C = {
+    "architectures": ["Llama4ForCausalLM"],
+    "num_hidden_layers": 4, "hidden_size": 136, "num_attention_heads": 6, "num_key_value_heads": 2,
+    "head_dim": 64, "intermediate_size": 200, "intermediate_size_mlp": 264,
+    "num_local_experts": 5, "num_experts_per_tok": 2, "interleave_moe_layer_step": 2,
+    "vocab_size": 777, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "nope_layer_interval": 2, "attention_chunk_size": 160, "use_qk_norm": True,
+    "attn_temperature_tuning": True, "floor_scale": 100, "attn_scale": 0.2,
+    "tie_word_embeddings": False, "max_position_embeddings": 4096, "initializer_range": 0.03,
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "R": (TINY_R, 2), "C": (TINY_C, 3)}
 
 
 def config(name: str) -> dict:
