@@ -311,3 +311,67 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
   }
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that may not allocate device memory (declared in
+// attention_decode_noalloc.h; it has no counterpart in the reference).
+//
+// Same kernels as cpi_attention_decode, but the float32 partials of the key splits live in a fixed
+// array inside this library instead of a buffer the caller allocates.  See the header for who needs
+// this and for the rules of use.
+namespace cpi {
+namespace dec {
+
+constexpr long kStaticScratchFloats = 2l << 20;             // 8 MiB per GPU that loads the library
+static __device__ __align__(256) float g_split_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_scratch_ptr[kMaxDevices] = {};              // device address of the array, per device
+
+// In host code `g_split_scratch` is only a handle for the runtime, not an address a kernel can use:
+// ask the runtime for the array's device address once per device, with that device current.
+static int static_scratch(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    set_error("attention_decode_noalloc: cannot identify the current device (%s)", cudaGetErrorString(e));
+    return 1;
+  }
+  if (!g_scratch_ptr[dev]) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_split_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_error("attention_decode_noalloc: cudaGetSymbolAddress failed on device %d (%s)", dev, cudaGetErrorString(e));
+      return 1;
+    }
+    g_scratch_ptr[dev] = static_cast<float*>(ptr);
+  }
+  *out = g_scratch_ptr[dev];
+  return 0;
+}
+
+}  // namespace dec
+}  // namespace cpi
+
+extern "C" long cpi_attention_decode_noalloc_capacity() { return cpi::dec::kStaticScratchFloats; }
+
+extern "C" int cpi_attention_decode_noalloc(const void* q, void* out, const void* k_cache, const void* v_cache,
+                                            const int* page_table, int max_blocks, int page_size,
+                                            const int* token_seq, const int* token_pos, const int* seq_slot,
+                                            int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window_kind,
+                                            int window_size, float scale, int n_splits, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  CPI_REQUIRE(n_splits >= 1, "attention_decode_noalloc: n_splits must be >= 1, got %d", n_splits);
+  const long need = (long)n_tokens * n_heads * n_splits * (head_dim + 2);
+  CPI_REQUIRE(n_splits == 1 || need <= dec::kStaticScratchFloats,
+              "attention_decode_noalloc: %d tokens x %d heads x %d splits need %ld floats of scratch; the built-in "
+              "array holds %ld (use fewer splits, or the allocating entry point)",
+              n_tokens, n_heads, n_splits, need, dec::kStaticScratchFloats);
+  float* scratch = nullptr;
+  if (dec::static_scratch(&scratch)) return 1;
+  float* part_o = scratch;
+  float* part_ml = scratch + (long)n_tokens * n_heads * n_splits * head_dim;
+  return cpi_attention_decode(q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos,
+                              seq_slot, n_tokens, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale,
+                              n_splits, part_o, part_ml, stream);
+}
