@@ -25,6 +25,7 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const TT* __res
 
 // One block per row.  The sum of squares is taken in a fixed order (thread-strided, then a warp
 // tree, then warps in order), so a row's result does not depend on the other rows of the launch.
+// Rows of up to 16 elements per thread stay in registers between the two passes.
 template <typename TX, typename TO>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
                                const void* __restrict__ w, int w_dtype, TO* __restrict__ out,
@@ -32,6 +33,31 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const TX* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
+  TO* o = out + (size_t)r * out_stride;
+  constexpr int PER = 16;
+  if (n <= PER * (int)blockDim.x) {
+    float v[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      v[j] = i < n ? to_f32(xr[i]) : 0.f;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) ss += v[j] * v[j];
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)n + eps);
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * blockDim.x;
+      if (i < n) {
+        float y = v[j] * inv;
+        if (w) y *= load_any(w, w_dtype, i);
+        o[i] = from_f32<TO>(y);
+      }
+    }
+    return;
+  }
   float ss = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = to_f32(xr[i]);
@@ -39,7 +65,6 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
   }
   ss = block_sum(ss, scratch);
   const float inv = 1.0f / sqrtf(ss / (float)n + eps);
-  TO* o = out + (size_t)r * out_stride;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float v = to_f32(xr[i]) * inv;
     if (w) v *= load_any(w, w_dtype, i);

@@ -424,12 +424,17 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
   const int live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
   const int k_tiles = (K + tc::BK - 1) / tc::BK;
   int splits = 1;
-  const long ctas = (long)n_tiles * (live_y > 0 ? live_y : 1);
-  if (ctas < 256) {
-    splits = (int)((296 + ctas - 1) / ctas);
-    const int max_by_k = k_tiles / 8 > 0 ? k_tiles / 8 : 1;      // at least 8 k-tiles per split
+  // CTAs that will really run: one per token tile; with groups at most one more per group that has rows
+  const int run_y = n_groups > 0 ? (T <= n_groups ? T : (T + bn - 1) / bn + n_groups / 2) : (T + bn - 1) / bn;
+  const long ctas = (long)n_tiles * (run_y > 0 ? run_y : 1);
+  const long slots = bn <= 32 ? 2 * 148 : 148;              // resident CTAs: narrow token tiles fit two per SM
+  if (ctas < slots) {
+    // fill one wave and no more: a launch of 1.1 waves takes as long as one of 2
+    splits = (int)(slots / ctas);
+    const int max_by_k = k_tiles / 4 > 0 ? k_tiles / 4 : 1;     // at least 4 k-tiles per split
     if (splits > max_by_k) splits = max_by_k;
     if (splits > 16) splits = 16;
+    if (splits < 1) splits = 1;
   }
   const int per = (k_tiles + splits - 1) / splits;
   splits = (k_tiles + per - 1) / per;

@@ -296,9 +296,14 @@ def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=No
     E = w.shape[0]
     assert w.is_contiguous() and w.shape[1] == H
     assert topk_idx.dtype == torch.int32 and topk_gate.dtype == torch.float32
-    _call("cpi_router_topk", _p(h), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
-          c_int(dtype_code(w.dtype)), _p(logits_out), _p(topk_idx), _p(topk_gate), c_int(T), c_int(H),
-          c_int(E), c_int(top_k), c_int(int(sigmoid_gate)), _stream())
+    if logits_out is None:
+        raise KernelError("router_topk: a float32 [tokens, experts] logits buffer is required")
+    assert logits_out.dtype == torch.float32 and logits_out.is_contiguous() and logits_out.numel() >= T * E
+    for t0 in range(0, T, 65535):            # the token axis is the grid's y dimension
+        n = min(65535, T - t0)
+        _call("cpi_router_topk", _p(h[t0:t0 + n]), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
+              c_int(dtype_code(w.dtype)), _p(logits_out[t0:t0 + n]), _p(topk_idx[t0:t0 + n]), _p(topk_gate[t0:t0 + n]),
+              c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(int(sigmoid_gate)), _stream())
 
 
 def moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot, *, n_tokens, top_k,

@@ -103,8 +103,12 @@ class AttentionMixer(Mixer):
             if self.window_kind != "full":
                 longest = min(longest, self.window_size + page_size)
             pages = -(-longest // page_size)
-            want = -(-444 // (batch.n_tokens * self.nkv))          # about three blocks per SM
-            n_splits = max(1, min(want, pages // 2))
+            base, slots = batch.n_tokens * self.nkv, 3 * 148       # three blocks fit an SM
+            if base <= slots:
+                want = slots // base                                # one full wave and no more
+            else:
+                want = -(-4 * slots // base)                        # several waves of smaller blocks
+            n_splits = max(1, min(want, pages // 4 if base > slots else pages // 2))
             K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                                window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)

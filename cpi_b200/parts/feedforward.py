@@ -109,7 +109,8 @@ class MoESwiGLU(FeedForward):
         ws, i32, f32 = self.ws, torch.int32, torch.float32
         idx = ws.get("moe_topk_idx", (T, Kk), i32)
         gate = ws.get("moe_topk_gate", (T, Kk), f32)
-        K.router_topk(h, self.w_router, idx, gate, top_k=Kk, sigmoid_gate=self.gate_mode != "none")
+        logits = ws.get("moe_router_logits", (T, E), f32)
+        K.router_topk(h, self.w_router, idx, gate, top_k=Kk, sigmoid_gate=self.gate_mode != "none", logits_out=logits)
         offsets = ws.get("moe_offsets", (E + 1,), i32)
         row_token = ws.get("moe_row_token", (T * Kk,), i32)
         row_scale = ws.get("moe_row_scale", (T * Kk,), f32)
