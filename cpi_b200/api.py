@@ -70,7 +70,7 @@ class Model:
         src/engine/llama4_cuda_engine.cu:623-674, without its top-k cut)."""
         s = self.engine.acquire_slot()
         try:
-            return self.engine.step([StepEntry(s, list(prompt), [len(prompt) - 1])])[0]
+            return self.engine.step([StepEntry(s, list(prompt), [len(prompt) - 1])])[0].clone()
         finally:
             self.engine.release_slot(s)
 

@@ -255,13 +255,48 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   };
 
   if (ok && p.splits == 1) {
-#pragma unroll 1
-    for (int c = 0; c < BN; c += 16) {
-      float v[16], u[16];
-      tmem_ld16(lane_addr + c, v);
-      if (ACC == 2) tmem_ld16(lane_addr + BN + c, u);
+    if (MODE == kAdd) {
+      // read-modify-write of the residual: the old values of chunk c+1 are fetched while chunk c is added,
+      // so that their latency hides behind the tensor-memory load
+      const bool row_ok = n < p.N;
+      float* outf = reinterpret_cast<float*>(p.out);
+      float old[2][16];
+      auto fetch = [&](int c, float* dst) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j) emit(c + j, v[j], ACC == 2 ? u[j] : 0.f);
+        for (int j = 0; j < 16; ++j) {
+          const int col = c + j, lr = t0 + col;
+          dst[j] = (row_ok && col < n_valid_t) ? outf[(size_t)(p.out_rows ? p.out_rows[lr] : lr) * p.ldo + n] : 0.f;
+        }
+      };
+      fetch(0, old[0]);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int cc = c + 16 * h;
+          if (cc >= BN) break;
+          if (cc + 16 < BN) fetch(cc + 16, old[h ^ 1]);
+          float v[16];
+          tmem_ld16(lane_addr + cc, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int col = cc + j, lr = t0 + col;
+            if (row_ok && col < n_valid_t) {
+              const float s = p.row_scale ? p.row_scale[lr] : 1.0f;
+              outf[(size_t)(p.out_rows ? p.out_rows[lr] : lr) * p.ldo + n] = old[h][j] + v[j] * s;
+            }
+          }
+        }
+      }
+    } else {
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 16) {
+        float v[16], u[16];
+        tmem_ld16(lane_addr + c, v);
+        if (ACC == 2) tmem_ld16(lane_addr + BN + c, u);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) emit(c + j, v[j], ACC == 2 ? u[j] : 0.f);
+      }
     }
   } else if (ok) {
     // raw accumulators -> partials[tile][split][acc][col][row]
@@ -414,7 +449,9 @@ using namespace cpi;
 // tiles_hint = expected token tiles per group (rows per group / bn, rounded up), groups_hint = groups in use.
 extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, int* bn_out, int* splits_out,
                                 int* live_y_out) {
-  const int rows_per_group = n_groups > 0 ? (T + n_groups - 1) / n_groups : T;
+  // groups: rows are spread unevenly, and a group that needs a second token tile reads its weights twice;
+  // size the tile for one and a half times the mean
+  const int rows_per_group = n_groups > 0 ? (3 * ((T + n_groups - 1) / n_groups) + 1) / 2 : T;
   int bn = 16;
   while (bn < 256 && bn < rows_per_group) bn *= 2;
   if (swiglu && bn > 256) bn = 256;

@@ -18,6 +18,7 @@ WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
 
 _lib = None
+scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
 launch_count = 0          # kernels launched through this module since import (bench reports it)
 
 
@@ -189,10 +190,13 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
         if need > (1 << 26):                 # keep the scratch modest: fewer splits instead
             sp = 1
         else:
+            global scratch_generation
             if st["partials"].numel() < need:
                 st["partials"] = torch.empty(need, dtype=torch.float32, device=a.device)
+                scratch_generation += 1
             if st["tickets"].numel() < tiles:
                 st["tickets"] = torch.zeros(tiles, dtype=torch.int32, device=a.device)
+                scratch_generation += 1
     _call("cpi_gemm_tc", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
           c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
           c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn.value), c_int(sp), _p(st["partials"]),
@@ -262,8 +266,10 @@ def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq,
         need = T * n_heads * n_splits * (head_dim + 2)
         buf = _dec_scratch.get(idx)
         if buf is None or buf.numel() < need:
+            global scratch_generation
             buf = torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device)
             _dec_scratch[idx] = buf
+            scratch_generation += 1
         po, pml = buf, buf[T * n_heads * n_splits * head_dim:]
     _call("cpi_attention_decode", _p(q), _p(out), _p(k_cache), _p(v_cache), _p(page_table),
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(T),

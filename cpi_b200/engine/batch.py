@@ -33,6 +33,7 @@ class StepBatch:
     slots: list
     starts: list
     n_new: list
+    ctx_bucket: int = 0                # an upper bound of the longest context, a power of two (sizes key splits)
     n_q_tiles: int = 0                 # prefill only: tiles of up to 128 consecutive tokens of one sequence,
     tile_tok0: torch.Tensor = None     # first packed token of each tile, longest context first
     tile_rows: torch.Tensor = None     # tokens in each tile
@@ -56,6 +57,11 @@ class BatchStager:
         self._next = 0
         self.bytes_staged = 0          # host-to-device bytes of the latest step
 
+    @staticmethod
+    def words_needed(n_tokens: int, n_seqs: int, n_want: int) -> int:
+        """int32 words a decode step (one token per sequence, no query tiles) stages."""
+        return 3 * n_tokens + 3 * n_seqs + n_want
+
     def _reserve(self, n: int) -> None:
         if n <= self._cap:
             return
@@ -67,7 +73,9 @@ class BatchStager:
             dev = torch.empty(self._cap, dtype=torch.int32, device=self.device)
             self._ring.append([host, dev, None])
 
-    def stage(self, slots, starts, token_lists, wants, dtype) -> StepBatch:
+    def stage(self, slots, starts, token_lists, wants, dtype, static_dev=None) -> StepBatch:
+        """`static_dev`: an int32 device buffer to fill instead of the ring's (its address then stays the
+        same from step to step, which a captured CUDA graph needs)."""
         B = len(slots)
         n_new = [len(t) for t in token_lists]
         T = sum(n_new)
@@ -86,6 +94,8 @@ class BatchStager:
         entry = self._ring[self._next]
         self._next = (self._next + 1) % self.RING
         h, d, ev = entry
+        if static_dev is not None:
+            d = static_dev
         if ev is not None:
             ev.synchronize()
         tokens, token_seq, token_pos, want_rows = [], [], [], []
@@ -113,7 +123,11 @@ class BatchStager:
             o += n
             return v
 
-        return StepBatch(n_tokens=T, n_seqs=B, n_want=R, max_new=max(n_new), dtype=dtype,
+        longest = max(st + n for st, n in zip(starts, n_new))
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        return StepBatch(n_tokens=T, n_seqs=B, n_want=R, max_new=max(n_new), dtype=dtype, ctx_bucket=bucket,
                          tokens=take(T), token_seq=take(T), token_pos=take(T), seq_slot=take(B),
                          seq_start=take(B), seq_new=take(B), want_rows=take(R),
                          slots=list(slots), starts=list(starts), n_new=n_new,

@@ -61,6 +61,13 @@ class Engine:
         self.stager = BatchStager(self.device)
         self.max_step_tokens = max(1, int(max_step_tokens))
         self.steps_run = 0
+        # Decode steps (one token per sequence) are captured into CUDA graphs, one per (sequences, wanted
+        # rows, context bucket): the first step of a kind runs eagerly, the second is captured, later ones
+        # replay.  What changes from step to step -- tokens, positions, slots, page tables -- lives in
+        # device buffers with fixed addresses that are refilled before each replay.
+        self.use_graphs = True
+        self._graphs = {}
+        self._routing_capture = False
 
     # ---- construction ----------------------------------------------------------------------------
     @classmethod
@@ -136,23 +143,59 @@ class Engine:
             pieces.append(cur)
         if any(sorted(w) != w for w in wants):
             raise ValueError("a step larger than max_step_tokens needs each entry's `want` in ascending order")
-        outs = [self._run([c[0] for c in piece], [c[1] for c in piece], [c[2] for c in piece]) for piece in pieces]
+        outs = [self._run([c[0] for c in piece], [c[1] for c in piece], [c[2] for c in piece]).clone()
+                for piece in pieces]
         return torch.cat(outs, dim=0)
 
     def _run(self, slots, toks, wants) -> torch.Tensor:
+        """Runs one piece; the returned logits live in a buffer that the next step overwrites."""
         n_new = [len(t) for t in toks]
         starts = self.cache.prepare_step(slots, n_new)
-        batch = self.stager.stage(slots, starts, toks, wants, self.dtype)
-        logits = self.model.run(batch, self.cache)
+        decode = max(n_new) == 1
+        if decode and self.use_graphs and not self._routing_capture:
+            logits = self._run_decode_graph(slots, starts, toks, wants)
+        else:
+            batch = self.stager.stage(slots, starts, toks, wants, self.dtype)
+            logits = self.model.run(batch, self.cache)
         self.cache.commit_step(slots, n_new)
         self.steps_run += 1
         return logits
+
+    def _run_decode_graph(self, slots, starts, toks, wants) -> torch.Tensor:
+        B = len(slots)
+        R = sum(len(w) for w in wants)
+        longest = max(s + 1 for s in starts)
+        bucket = 256
+        while bucket < longest:
+            bucket *= 2
+        key = (B, R, bucket)
+        st = self._graphs.get(key)
+        gen = (self.ws.generation, K.scratch_generation)
+        if st is not None and st["graph"] is not None and st["gen"] != gen:
+            st = None                       # a buffer moved since the capture: the graph holds stale addresses
+        if st is None:
+            # first step of this kind: eager (it also sizes every workspace buffer and sets kernel attributes)
+            dev = torch.empty(self.stager.words_needed(B, B, R), dtype=torch.int32, device=self.device)
+            self._graphs[key] = {"dev": dev, "graph": None, "logits": None, "gen": None}
+            batch = self.stager.stage(slots, starts, toks, wants, self.dtype, static_dev=dev)
+            return self.model.run(batch, self.cache)
+        batch = self.stager.stage(slots, starts, toks, wants, self.dtype, static_dev=st["dev"])
+        if st["graph"] is None:
+            torch.cuda.synchronize(self.device)
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                st["logits"] = self.model.run(batch, self.cache)
+            st["graph"] = g
+            st["gen"] = (self.ws.generation, K.scratch_generation)
+        st["graph"].replay()
+        return st["logits"]
 
     # ---- inspection ------------------------------------------------------------------------------
     def capture_routing(self, on: bool = True) -> dict:
         """Starts (or stops) recording the experts chosen in every step.  Returns {layer index: list}
         whose lists grow by one int32 tensor [tokens, k] per step while recording is on."""
         out = {}
+        self._routing_capture = bool(on)          # recording copies tensors every step: not inside a graph
         for i, layer in enumerate(self.model.layers):
             ff = layer.feed_forward
             if hasattr(ff, "capture"):

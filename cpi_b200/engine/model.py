@@ -106,7 +106,7 @@ class DecoderModel:
             view = parts_base.CacheView(cache_manager, owner, owns=e.cache_of is None)
             layer.block.run(layer, x, batch, view)
         R = batch.n_want
-        logits = torch.empty((R, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        logits = self.ws.get("logits", (R, self.spec.vocab_size), torch.float32)   # valid until the next step
         if R:
             xn = self.final_norm(x, self.dtype, rows=batch.want_rows)
             project(xn, self.head, logits)

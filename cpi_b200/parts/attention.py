@@ -98,8 +98,9 @@ class AttentionMixer(Mixer):
         wk = K.WINDOW_KINDS[self.window_kind]
         if (batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
-            # keys per sequence that the window lets through, at most
-            longest = max(s + 1 for s in batch.starts)
+            # keys per sequence that the window lets through, at most (a bucketed bound: the split count
+            # then stays the same from step to step, which a captured graph needs)
+            longest = batch.ctx_bucket
             if self.window_kind != "full":
                 longest = min(longest, self.window_size + page_size)
             pages = -(-longest // page_size)

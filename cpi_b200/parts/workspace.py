@@ -8,6 +8,7 @@ class Workspace:
     def __init__(self, device):
         self.device = device
         self._buffers: dict = {}
+        self.generation = 0        # grows whenever a buffer is (re)allocated: captured graphs then hold stale addresses
 
     def get(self, name: str, shape, dtype: torch.dtype) -> torch.Tensor:
         n = 1
@@ -21,6 +22,7 @@ class Workspace:
                 cap = max(cap, int(buf.numel() * 1.5))
             buf = torch.empty(cap, dtype=dtype, device=self.device)
             self._buffers[key] = buf
+            self.generation += 1
         return buf[:n].view(*shape)
 
     def bytes_held(self) -> int:
