@@ -74,6 +74,8 @@ template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
 
 template <int D>
 __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int CH = D / 8;                 // 16-byte chunks per row
   constexpr int KS = D / 16;                // k-steps of Q K^T
   constexpr int NO = D / 8;                 // n-tiles of the output
@@ -249,6 +251,8 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
 // out[t, h, :] = sum_s w_s O_s / sum_s w_s l_s,  w_s = 2^(m_s - max m)
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int n_splits, int D) {
+  pdl_launch_dependents();
+  pdl_wait();
   const size_t th = blockIdx.x;
   float M = -1e30f;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(th * n_splits + s) * 2]);
@@ -297,15 +301,15 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
   if (head_dim == 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(dec::attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    dec::attention_decode_kernel<128><<<grid, dec::NT, smem, stream>>>(p);
+    cpi::launch_pdl(dec::attention_decode_kernel<128>, grid, dec::NT, smem, stream, p);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(dec::attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    dec::attention_decode_kernel<64><<<grid, dec::NT, smem, stream>>>(p);
+    cpi::launch_pdl(dec::attention_decode_kernel<64>, grid, dec::NT, smem, stream, p);
   }
   if (check_launch("attention_decode")) return 2;
   if (n_splits > 1) {
-    dec::attention_combine_kernel<<<n_tokens * n_heads, head_dim <= 64 ? 64 : 128, 0, stream>>>(
+    cpi::launch_pdl(dec::attention_combine_kernel, n_tokens * n_heads, head_dim <= 64 ? 64 : 128, 0, stream, 
         part_o, part_ml, (__nv_bfloat16*)out, n_splits, head_dim);
     return check_launch("attention_combine");
   }

@@ -137,6 +137,8 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
   uint8_t* kv_s = q_s + Q_BYTES;                       // [stage][K | V]
   uint8_t* p_s = kv_s + 2 * 2 * KV_BYTES;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int tile = blockIdx.x, head = blockIdx.y;
   const int kvh = head / (p.n_heads / p.n_kv_heads);
   const int tok0 = p.tile_tok0[tile], rows = p.tile_rows[tile];
@@ -361,11 +363,11 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
   if (head_dim == 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    pre::attention_prefill_kernel<128><<<grid, 192, smem, stream>>>(mq, mk, mv, p);
+    cpi::launch_pdl(pre::attention_prefill_kernel<128>, grid, 192, smem, stream, mq, mk, mv, p);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    pre::attention_prefill_kernel<64><<<grid, 192, smem, stream>>>(mq, mk, mv, p);
+    cpi::launch_pdl(pre::attention_prefill_kernel<64>, grid, 192, smem, stream, mq, mk, mv, p);
   }
   return check_launch("attention_prefill");
 }

@@ -32,6 +32,8 @@ struct QkvPostParams {
 
 template <typename T>
 __global__ void qkv_post_kernel(QkvPostParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = p.n_heads + (p.write_kv ? 2 * p.n_kv_heads : 0);
   const int hs = blockIdx.y * (blockDim.x >> 5) + warp;       // head slot
@@ -130,6 +132,8 @@ constexpr int ATT_NT = 128;
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float q_s[256];
   __shared__ float p_s[ATT_NT];
   __shared__ size_t off_s[ATT_NT];
@@ -210,7 +214,7 @@ extern "C" int cpi_qkv_post(const void* qkv, long qkv_stride, void* q_out, void*
                   norm_eps, temperature, floor_scale, attn_scale, n_heads, n_kv_heads, head_dim, write_kv};
   const int heads_total = n_heads + (write_kv ? 2 * n_kv_heads : 0);
   dim3 grid(n_tokens, (heads_total + 3) / 4);
-  CPI_DISPATCH_DTYPE(dtype, T, qkv_post_kernel<T><<<grid, 128, 0, stream>>>(p));
+  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(qkv_post_kernel<T>, grid, 128, 0, stream, p));
   return check_launch("qkv_post");
 }
 
@@ -226,6 +230,6 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
   AttnParams p{q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos, seq_slot,
                n_heads, n_kv_heads, head_dim, window_kind, window_size, scale};
   dim3 grid(n_tokens, n_heads);
-  CPI_DISPATCH_DTYPE(dtype, T, attention_general_kernel<T><<<grid, ATT_NT, 0, stream>>>(p));
+  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(attention_general_kernel<T>, grid, ATT_NT, 0, stream, p));
   return check_launch("attention_general");
 }

@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <cstdarg>
+#include <utility>
 
 namespace cpi {
 
@@ -60,6 +61,31 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   float r = scratch[0];
   for (int i = 1; i < nw; ++i) r = fmaxf(r, scratch[i]);
   return r;
+}
+
+// Programmatic dependent launch: a kernel launched with launch_pdl may start while the kernel before it
+// in the stream is still running.  Every such kernel calls pdl_launch_dependents() early (so that its
+// own successor may be scheduled) and pdl_wait() before it first reads or writes global memory that
+// another kernel of the stream produces or reads; pdl_wait() returns once the preceding kernel has
+// finished and its writes are visible.  What precedes the wait (barrier set-up, tensor-memory
+// allocation, loads of weights, which no kernel writes) overlaps the predecessor's tail.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 }  // namespace cpi

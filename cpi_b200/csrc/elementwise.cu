@@ -12,6 +12,8 @@ namespace cpi {
 template <typename TT>
 __global__ void embedding_kernel(const int* __restrict__ tokens, const TT* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab, int* __restrict__ err) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const int tok = tokens[t];
   if (tok < 0 || tok >= vocab) {              // never read out of range: flag it and write zeros
@@ -30,6 +32,8 @@ template <typename TX, typename TO>
 __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const int* __restrict__ rows,
                                const void* __restrict__ w, int w_dtype, TO* __restrict__ out,
                                long out_stride, int n, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int r = blockIdx.x;
   const TX* xr = x + (size_t)(rows ? rows[r] : r) * x_stride;
@@ -76,6 +80,8 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
 template <typename TY>
 __global__ void moe_combine_kernel(float* __restrict__ residual, const TY* __restrict__ y,
                                    const int* __restrict__ row_of_slot, int top_k, int hidden) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float acc = residual[(size_t)t * hidden + i];
@@ -89,6 +95,8 @@ __global__ void moe_combine_kernel(float* __restrict__ residual, const TY* __res
 
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   const T* g = gu + (size_t)t * 2 * inter;
   for (int i = threadIdx.x; i < inter; i += blockDim.x) {
@@ -100,6 +108,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 // dst[r, :] = src[rows[r], :]  (16-byte chunks; width * sizeof(T) must be a multiple of 16)
 __global__ void gather_rows_kernel(const uint4* __restrict__ src, long src_stride16, const int* __restrict__ rows,
                                    uint4* __restrict__ dst, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int r = blockIdx.x;
   const uint4* s = src + (size_t)rows[r] * src_stride16;
   uint4* d = dst + (size_t)r * chunks;
@@ -114,7 +124,7 @@ extern "C" int cpi_gather_rows(const void* src, long src_stride_bytes, const int
                                int row_bytes, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CPI_REQUIRE(row_bytes % 16 == 0 && src_stride_bytes % 16 == 0, "gather_rows: rows of %d bytes (stride %ld) are not 16-byte multiples", row_bytes, src_stride_bytes);
-  gather_rows_kernel<<<n_rows, 128, 0, stream>>>((const uint4*)src, src_stride_bytes / 16, rows, (uint4*)dst, row_bytes / 16);
+  cpi::launch_pdl(gather_rows_kernel, n_rows, 128, 0, stream, (const uint4*)src, src_stride_bytes / 16, rows, (uint4*)dst, row_bytes / 16);
   return check_launch("gather_rows");
 }
 
@@ -123,7 +133,7 @@ extern "C" int cpi_embedding(const int* tokens, const void* table, int table_dty
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes T=%d H=%d V=%d", n_tokens, hidden, vocab);
   CPI_DISPATCH_DTYPE(table_dtype, TT,
-      embedding_kernel<TT><<<n_tokens, 256, 0, stream>>>(tokens, (const TT*)table, out, hidden, vocab, err_flag));
+      cpi::launch_pdl(embedding_kernel<TT>, n_tokens, 256, 0, stream, tokens, (const TT*)table, out, hidden, vocab, err_flag));
   return check_launch("embedding");
 }
 
@@ -134,7 +144,7 @@ extern "C" int cpi_rmsnorm(const void* x, int x_dtype, long x_stride, const int*
   CPI_REQUIRE(n_rows > 0 && n > 0, "rmsnorm: bad sizes rows=%d n=%d", n_rows, n);
   const int threads = n <= 256 ? 64 : (n <= 2048 ? 256 : 512);
   CPI_DISPATCH_DTYPE(x_dtype, TX, CPI_DISPATCH_DTYPE(out_dtype, TO,
-      (rmsnorm_kernel<TX, TO><<<n_rows, threads, 0, stream>>>((const TX*)x, x_stride, rows, w, w_dtype,
+      (cpi::launch_pdl(rmsnorm_kernel<TX, TO>, n_rows, threads, 0, stream, (const TX*)x, x_stride, rows, w, w_dtype,
                                                               (TO*)out, out_stride, n, eps))));
   return check_launch("rmsnorm");
 }
@@ -143,12 +153,12 @@ extern "C" int cpi_moe_combine(float* residual, const void* y, int y_dtype, cons
                                int n_tokens, int top_k, int hidden, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_DISPATCH_DTYPE(y_dtype, TY,
-      moe_combine_kernel<TY><<<n_tokens, 256, 0, stream>>>(residual, (const TY*)y, row_of_slot, top_k, hidden));
+      cpi::launch_pdl(moe_combine_kernel<TY>, n_tokens, 256, 0, stream, residual, (const TY*)y, row_of_slot, top_k, hidden));
   return check_launch("moe_combine");
 }
 
 extern "C" int cpi_swiglu(const void* gate_up, void* out, int dtype, int n_rows, int inter, cudaStream_t stream) {
   if (n_rows == 0) return 0;
-  CPI_DISPATCH_DTYPE(dtype, T, swiglu_kernel<T><<<n_rows, 256, 0, stream>>>((const T*)gate_up, (T*)out, inter));
+  CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(swiglu_kernel<T>, n_rows, 256, 0, stream, (const T*)gate_up, (T*)out, inter));
   return check_launch("swiglu");
 }

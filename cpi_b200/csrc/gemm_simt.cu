@@ -31,6 +31,8 @@ constexpr int BN = 64, BK = 16, NT = 256;
 
 template <typename TA, typename TW, typename TO, int MODE, int TM>
 __global__ void __launch_bounds__(NT) gemm_simt_kernel(GemmParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int BM = 16 * TM;
   constexpr bool GLU = MODE == kSwiglu;
   __shared__ float As[BK][BM + 4];
@@ -144,8 +146,8 @@ int launch_simt(const GemmParams& p, int m_tiles_hint, cudaStream_t stream) {
   if (p.group_offsets) m_tiles += p.n_groups;
   dim3 grid((p.N + BN - 1) / BN, m_tiles);
   if (grid.y > 65535) { set_error("gemm: too many row tiles (%u)", grid.y); return 1; }
-  if (small) gemm_simt_kernel<TA, TW, TO, MODE, 1><<<grid, NT, 0, stream>>>(p);
-  else       gemm_simt_kernel<TA, TW, TO, MODE, 4><<<grid, NT, 0, stream>>>(p);
+  if (small) cpi::launch_pdl(gemm_simt_kernel<TA, TW, TO, MODE, 1>, grid, NT, 0, stream, p);
+  else       cpi::launch_pdl(gemm_simt_kernel<TA, TW, TO, MODE, 4>, grid, NT, 0, stream, p);
   return check_launch("gemm_simt");
 }
 

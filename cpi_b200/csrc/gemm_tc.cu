@@ -159,9 +159,11 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
+  pdl_launch_dependents();
   // ---- which tile ----
   int group = 0, t_begin = 0, t_end = p.T, tile_t = blockIdx.y;
   if (p.group_offsets) {
+    pdl_wait();                                  // the row lists come from the kernel before this one
     bool found = false;
     for (int g = 0; g < p.n_groups; ++g) {
       const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
@@ -194,7 +196,20 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   if (warp == 0 && lane == 0) {
     // ---- TMA producer ----
-    for (int i = 0; i < n_kt; ++i) {
+    // Weights are written by no kernel, so their tiles for the first stages are requested before the
+    // wait on the preceding kernel; the activation tiles follow it.
+    const int n_early = p.group_offsets ? 0 : min(n_kt, STAGES);
+    for (int i = 0; i < n_early; ++i) {
+      uint8_t* st = smem + (size_t)i * STAGE_BYTES;
+      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      const int k = (kt_begin + i) * BK;
+      tma_load_3d(st, &map_w, &full_bar[i], k, n0, group);
+      if (ACC == 2) tma_load_3d(st + A_BYTES, &map_w, &full_bar[i], k, p.N + n0, group);
+    }
+    pdl_wait();
+    for (int i = 0; i < n_early; ++i)
+      tma_load_2d(smem + (size_t)i * STAGE_BYTES + ACC * A_BYTES, &map_x, &full_bar[i], (kt_begin + i) * BK, t0);
+    for (int i = n_early; i < n_kt; ++i) {
       const int s = i % STAGES;
       if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
       uint8_t* st = smem + (size_t)s * STAGE_BYTES;
@@ -228,6 +243,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __syncwarp();
 
   // ---- epilogue: all four warps ----
+  pdl_wait();                                    // before any global read or write of this thread
   bool ok = mbar_wait(&accum_bar, 0, abort_flag);
   fence_after_sync();
   ok = ok && !abort_s;
@@ -318,15 +334,33 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     if (ticket_s == p.splits - 1) {
       __threadfence();
       const float* base = p.partials + (tile_id * p.splits * ACC) * (size_t)(BN * BM);
+      // Sum the parts in split order.  Eight columns and four splits are fetched at a time, so that up to
+      // 32 (64 with two accumulators) loads are in flight per thread instead of one.
 #pragma unroll 1
-      for (int c = 0; c < n_valid_t; ++c) {
-        float v = 0.f, u = 0.f;
-        for (int z = 0; z < p.splits; ++z) {
-          const float* pz = base + ((size_t)z * ACC) * (size_t)(BN * BM);
-          v += __ldcg(pz + (size_t)c * BM + row);
-          if (ACC == 2) u += __ldcg(pz + ((size_t)BN + c) * BM + row);
+      for (int c0 = 0; c0 < n_valid_t; c0 += 8) {
+        float v[8], u[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) { v[j] = 0.f; u[j] = 0.f; }
+#pragma unroll 1
+        for (int z0 = 0; z0 < p.splits; z0 += 4) {
+          float tv[4][8], tu[4][8];
+#pragma unroll
+          for (int zz = 0; zz < 4; ++zz) {
+            const bool live = z0 + zz < p.splits;
+            const float* pz = base + ((size_t)(z0 + zz) * ACC) * (size_t)(BN * BM);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              tv[zz][j] = live ? __ldcg(pz + (size_t)(c0 + j) * BM + row) : 0.f;
+              if (ACC == 2) tu[zz][j] = live ? __ldcg(pz + ((size_t)BN + c0 + j) * BM + row) : 0.f;
+            }
+          }
+#pragma unroll
+          for (int zz = 0; zz < 4; ++zz)
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { v[j] += tv[zz][j]; if (ACC == 2) u[j] += tu[zz][j]; }
         }
-        emit(c, v, u);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) emit(c0 + j, v[j], u[j]);
       }
       if (tid == 0) p.tickets[tile_id] = 0;
     }
@@ -423,7 +457,7 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
     }
     attr_set = true;
   }
-  kern<<<grid, 128, SMEM, stream>>>(mw, mx, p);
+  cpi::launch_pdl(kern, grid, 128, SMEM, stream, mw, mx, p);
   return check_launch("gemm_tc");
 }
 
@@ -470,7 +504,8 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
     splits = (int)(slots / ctas);
     const int max_by_k = k_tiles / 4 > 0 ? k_tiles / 4 : 1;     // at least 4 k-tiles per split
     if (splits > max_by_k) splits = max_by_k;
-    if (splits > 16) splits = 16;
+    if (splits > 8) splits = 8;
+    if (bn >= 64 && splits > 1) splits = 1;                     // wide token tiles: the merge of parts costs more than it saves
     if (splits < 1) splits = 1;
   }
   const int per = (k_tiles + splits - 1) / splits;

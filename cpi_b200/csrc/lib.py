@@ -150,7 +150,7 @@ def _tc_state(device):
 
 
 def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None, row_scale=None,
-            group_offsets=None, n_groups=0, rows_per_group_hint=None) -> bool:
+            group_offsets=None, n_groups=0, rows_per_group_hint=None, force_splits=None, force_bn=None) -> bool:
     """The tcgen05 kernel for out[m, n] (+)= sum_k a[m, k] w[g(m)][n, k] in bfloat16 (see gemm_tc.cu).
 
     Returns False, having launched nothing, when the call is outside what the kernel takes (a row
@@ -183,7 +183,10 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
                             c_int(int(mode == MODE_SWIGLU)), ctypes.byref(bn), ctypes.byref(splits),
                             ctypes.byref(live_y))
     st = _tc_state(a.device)
-    sp = splits.value
+    if force_bn is not None:                 # tuning aid: override the planner
+        bn.value = force_bn
+        live_y.value = -(-T // force_bn) + (min(T, n_groups) if grouped else 0)
+    sp = splits.value if force_splits is None else force_splits
     if sp > 1:
         tiles = -(-N // 128) * live_y.value
         need = tiles * sp * (2 if mode == MODE_SWIGLU else 1) * bn.value * 128

@@ -16,6 +16,8 @@ template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
                      float* __restrict__ logits, int hidden, int n_experts) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[32];
   const int e = blockIdx.x, t = blockIdx.y;
   const TH* x = h + (size_t)t * h_stride;
@@ -31,6 +33,8 @@ router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restri
 __global__ void router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx,
                                      float* __restrict__ topk_gate, int n_tokens, int n_experts, int top_k,
                                      int gate_mode) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= n_tokens) return;
   const float* lg = logits + (size_t)t * n_experts;
@@ -71,6 +75,8 @@ moe_lists_kernel(const int* __restrict__ topk_idx, const float* __restrict__ top
                  int* __restrict__ group_offsets, int* __restrict__ row_token,
                  float* __restrict__ row_scale, int* __restrict__ row_of_slot,
                  int n_slots, int top_k, int n_experts) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ int counts[kMaxExperts];
   __shared__ int offsets[kMaxExperts + 1];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -125,9 +131,9 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
   CPI_REQUIRE(n_tokens <= 65535, "router: too many tokens in one launch (%d)", n_tokens);
   dim3 grid(n_experts, n_tokens);
   CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-      (router_logits_kernel<TH, TW><<<grid, 128, 0, stream>>>((const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
+      (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
   if (check_launch("router_logits")) return 2;
-  router_select_kernel<<<(n_tokens + 127) / 128, 128, 0, stream>>>(logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
+  cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
   return check_launch("router_select");
 }
 
@@ -136,7 +142,7 @@ extern "C" int cpi_moe_lists(const int* topk_idx, const float* topk_gate, int* g
                              cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(n_experts >= 1 && n_experts <= kMaxExperts, "moe_lists: %d experts (supported: 1..%d)", n_experts, kMaxExperts);
-  moe_lists_kernel<<<1, 1024, 0, stream>>>(topk_idx, topk_gate, group_offsets, row_token, row_scale,
+  cpi::launch_pdl(moe_lists_kernel, 1, 1024, 0, stream, topk_idx, topk_gate, group_offsets, row_token, row_scale,
                                               row_of_slot, n_tokens * top_k, top_k, n_experts);
   return check_launch("moe_lists");
 }
