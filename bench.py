@@ -160,7 +160,7 @@ def run(args) -> dict:
         plen = ctx - (n_steps + n_warm) - 1
         slots = [eng.acquire_slot() for _ in range(batch)]
         eng.step([StepEntry(s, toks(plen), []) for s in slots])
-        feed = [[toks(batch) for _ in range(n_steps + n_warm + 1)]][0]
+        feed = [toks(batch) for _ in range(n_steps + n_warm + 1)]
 
         def one(i):
             lg = eng.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
@@ -169,7 +169,7 @@ def run(args) -> dict:
         for i in range(n_warm):
             one(i)
         torch.cuda.synchronize()
-        l0 = K.launch_count
+        l0 = K.kernel_launches() + eng.graph_kernel_launches
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(n_warm, n_warm + n_steps):
@@ -177,7 +177,7 @@ def run(args) -> dict:
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
-        launches = K.launch_count - l0
+        launches = K.kernel_launches() + eng.graph_kernel_launches - l0
         cap = eng.capture_routing(True)          # one more, untimed, step: how many experts a step touches
         one(n_warm + n_steps)
         torch.cuda.synchronize()

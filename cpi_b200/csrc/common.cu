@@ -12,6 +12,9 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
+static long g_launches = 0;
+void count_launch() { ++g_launches; }
+
 int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
@@ -21,6 +24,10 @@ int check_launch(const char* what) {
   return 0;
 }
 }  // namespace cpi
+
+// Kernels launched by this library from host code since it was loaded (replays of a captured graph are
+// not host launches and are not counted here).
+extern "C" long cpi_launch_count() { return cpi::g_launches; }
 
 extern "C" const char* cpi_last_error() { return cpi::g_error; }
 

@@ -16,6 +16,7 @@ namespace cpi {
 enum DType : int { kF32 = 0, kBF16 = 1 };
 
 void set_error(const char* fmt, ...);
+void count_launch();                 // every kernel launch of the library is counted (cpi_launch_count)
 int check_launch(const char* what);
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
@@ -85,6 +86,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  count_launch();
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

@@ -38,6 +38,12 @@ def load():
     return _lib
 
 
+def kernel_launches() -> int:
+    """Kernels this library has launched from host code (graph replays are counted by the engine)."""
+    load().cpi_launch_count.restype = c_long
+    return int(load().cpi_launch_count())
+
+
 def library_file() -> str:
     return _build.library_path(build_if_missing=False)
 
@@ -130,22 +136,27 @@ def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=Non
           _p(group_offsets), c_int(n_groups), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(hint), _stream())
 
 
-_tc_scratch = {}      # device index -> {"partials", "tickets", "error"}
+_tc_scratch = {}      # (device index, stream) -> {"partials", "tickets"}: kernels on different streams may overlap
+_tc_error = {}        # device index -> int32[1]
 
 
 def tc_error_flag(device) -> torch.Tensor:
     """int32[1] that a tensor-core kernel sets when one of its bounded waits ran out."""
-    return _tc_state(device)["error"]
+    idx = torch.device(device).index or 0
+    if idx not in _tc_error:
+        _tc_error[idx] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_error[idx]
 
 
 def _tc_state(device):
     idx = torch.device(device).index or 0
-    st = _tc_scratch.get(idx)
+    key = (idx, torch.cuda.current_stream(device).cuda_stream)
+    st = _tc_scratch.get(key)
     if st is None:
         st = {"partials": torch.empty(1 << 20, dtype=torch.float32, device=device),
               "tickets": torch.zeros(1 << 14, dtype=torch.int32, device=device),
-              "error": torch.zeros(1, dtype=torch.int32, device=device)}
-        _tc_scratch[idx] = st
+              "error": tc_error_flag(device)}
+        _tc_scratch[key] = st
     return st
 
 

@@ -161,6 +161,7 @@ using namespace cpi;
 extern "C" int cpi_argmax(const float* logits, long stride, int n_rows, int vocab, int* out, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CPI_REQUIRE(vocab > 0, "argmax: empty vocabulary");
+  count_launch();
   argmax_kernel<<<n_rows, SAMP_NT, 0, stream>>>(logits, stride, vocab, out);
   return check_launch("argmax");
 }
@@ -170,6 +171,7 @@ extern "C" int cpi_sample(const float* logits, long stride, float* work, int n_r
                           const float* uniform, int* out, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CPI_REQUIRE(vocab > 0, "sample: empty vocabulary");
+  count_launch();
   sample_kernel<<<n_rows, SAMP_NT, 0, stream>>>(logits, stride, work, vocab, temperature, top_k, top_p, uniform, out);
   return check_launch("sample");
 }
@@ -177,6 +179,7 @@ extern "C" int cpi_sample(const float* logits, long stride, float* work, int n_r
 extern "C" int cpi_repetition_penalty(float* logits, long stride, int n_rows, int vocab, const int* ids,
                                       const int* id_offsets, const float* penalty, cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  count_launch();
   repetition_penalty_kernel<<<n_rows, 256, 0, stream>>>(logits, stride, vocab, ids, id_offsets, penalty);
   return check_launch("repetition_penalty");
 }
@@ -184,6 +187,7 @@ extern "C" int cpi_repetition_penalty(float* logits, long stride, int n_rows, in
 extern "C" int cpi_ban_tokens(float* logits, long stride, int n_rows, int vocab, const int* ids,
                               const int* id_offsets, cudaStream_t stream) {
   if (n_rows == 0) return 0;
+  count_launch();
   ban_tokens_kernel<<<n_rows, 256, 0, stream>>>(logits, stride, vocab, ids, id_offsets);
   return check_launch("ban_tokens");
 }

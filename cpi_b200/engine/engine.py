@@ -67,6 +67,7 @@ class Engine:
         # device buffers with fixed addresses that are refilled before each replay.
         self.use_graphs = True
         self._graphs = {}
+        self.graph_kernel_launches = 0       # kernels run by graph replays (they are not host launches)
         self._routing_capture = False
 
     # ---- construction ----------------------------------------------------------------------------
@@ -176,18 +177,21 @@ class Engine:
         if st is None:
             # first step of this kind: eager (it also sizes every workspace buffer and sets kernel attributes)
             dev = torch.empty(self.stager.words_needed(B, B, R), dtype=torch.int32, device=self.device)
-            self._graphs[key] = {"dev": dev, "graph": None, "logits": None, "gen": None}
+            self._graphs[key] = {"dev": dev, "graph": None, "logits": None, "gen": None, "kernels": 0}
             batch = self.stager.stage(slots, starts, toks, wants, self.dtype, static_dev=dev)
             return self.model.run(batch, self.cache)
         batch = self.stager.stage(slots, starts, toks, wants, self.dtype, static_dev=st["dev"])
         if st["graph"] is None:
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()
+            before = K.kernel_launches()
             with torch.cuda.graph(g):
                 st["logits"] = self.model.run(batch, self.cache)
+            st["kernels"] = K.kernel_launches() - before
             st["graph"] = g
             st["gen"] = (self.ws.generation, K.scratch_generation)
         st["graph"].replay()
+        self.graph_kernel_launches += st["kernels"]
         return st["logits"]
 
     # ---- inspection ------------------------------------------------------------------------------

@@ -83,6 +83,12 @@ class MoESwiGLU(FeedForward):
                                           "feed_forward.shared_expert.up_proj.weight",
                                           "feed_forward.shared_expert.down_proj.weight"))
         self.w_router = self.w_gate_up = self.w_down = None
+        # The shared expert does not depend on the routing, so it runs on a second stream beside the routed
+        # experts (fork after the norm, join before the outputs are combined).  To keep the two from adding
+        # into the same residual rows at the same time, the routed outputs are then stored and combined
+        # after the join.
+        self.overlap_shared = True
+        self._side_stream = None
         self.capture = None        # a list: every forward appends a copy of its expert choices [T, k]
 
     def requirements(self):
@@ -107,6 +113,17 @@ class MoESwiGLU(FeedForward):
     def forward(self, h, residual, batch):
         T, E, Kk = h.shape[0], self.n_experts, self.top_k
         ws, i32, f32 = self.ws, torch.int32, torch.float32
+        forked = None
+        if self.shared is not None and self.overlap_shared and h.is_cuda:
+            if self._side_stream is None:
+                self._side_stream = torch.cuda.Stream(device=h.device)
+            fork = torch.cuda.Event()
+            fork.record(torch.cuda.current_stream())
+            self._side_stream.wait_event(fork)
+            with torch.cuda.stream(self._side_stream):
+                self.shared.forward(h, residual, batch)
+                forked = torch.cuda.Event()
+                forked.record(self._side_stream)
         idx = ws.get("moe_topk_idx", (T, Kk), i32)
         gate = ws.get("moe_topk_gate", (T, Kk), f32)
         logits = ws.get("moe_router_logits", (T, E), f32)
@@ -132,13 +149,17 @@ class MoESwiGLU(FeedForward):
             project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token, row_scale=in_scale,
                     group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
         out_scale = row_scale if self.gate_mode == "sigmoid_output" else None
-        if Kk == 1:
+        if Kk == 1 and forked is None:
             project(act, self.w_down, residual, MODE_ADD, m_rows=M, out_rows=row_token, row_scale=out_scale,
                     group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
         else:
             y = ws.get("moe_y", (M, self.hidden), f32)
             project(act, self.w_down, y, MODE_STORE, m_rows=M, row_scale=out_scale,
                     group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+            if forked is not None:
+                torch.cuda.current_stream().wait_event(forked)
             K.moe_combine(residual, y, row_of_slot, top_k=Kk)
+        if forked is not None:
+            return
         if self.shared is not None:
             self.shared.forward(h, residual, batch)
