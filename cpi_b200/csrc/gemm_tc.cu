@@ -221,7 +221,10 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
-    constexpr uint32_t idesc = instr_desc_bf16(BN);
+    // The MMA's N is a run-time field of the instruction descriptor: a tile with few rows (the tail of a
+    // group, or a group with few tokens) multiplies only those columns, rounded up to 16.
+    const int n_rows_here = min(BN, (p.group_offsets ? t_end : p.T) - t0);
+    const uint32_t idesc = instr_desc_bf16(min(BN, (n_rows_here + 15) & ~15));
     bool ok = true;
     for (int i = 0; i < n_kt && ok; ++i) {
       const int s = i % STAGES;
@@ -252,6 +255,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int n = n0 + row;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int n_valid_t = min(BN, t_end - t0);
+  const int n_cols = min(BN, (n_valid_t + 15) & ~15);          // columns the MMAs wrote
   TO* out = reinterpret_cast<TO*>(p.out);
 
   auto emit = [&](int col, float v, float u) {
@@ -286,12 +290,12 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       };
       fetch(0, old[0]);
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
+      for (int c = 0; c < n_cols; c += 32) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int cc = c + 16 * h;
-          if (cc >= BN) break;
-          if (cc + 16 < BN) fetch(cc + 16, old[h ^ 1]);
+          if (cc >= n_cols) break;
+          if (cc + 16 < n_cols) fetch(cc + 16, old[h ^ 1]);
           float v[16];
           tmem_ld16(lane_addr + cc, v);
 #pragma unroll
@@ -306,7 +310,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
       }
     } else {
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
+      for (int c = 0; c < n_cols; c += 16) {
         float v[16], u[16];
         tmem_ld16(lane_addr + c, v);
         if (ACC == 2) tmem_ld16(lane_addr + BN + c, u);
@@ -321,7 +325,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll 1
     for (int a = 0; a < ACC; ++a)
 #pragma unroll 1
-      for (int c = 0; c < BN; c += 16) {
+      for (int c = 0; c < n_cols; c += 16) {
         float v[16];
         tmem_ld16(lane_addr + a * BN + c, v);
 #pragma unroll

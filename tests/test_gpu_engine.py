@@ -120,3 +120,60 @@ def test_cuts_agree_bitwise_in_float32(name):
     scale = float(w.abs().max())
     assert float((w - c).abs().max()) <= 2e-6 * scale
     assert float((w - bt).abs().max()) <= 2e-6 * scale
+
+
+@pytest.mark.parametrize("name,dtype,prompt,steps", [("A", "float32", 7, 300), ("C", "bfloat16", 100, 420),
+                                                      ("B", "bfloat16", 3, 150)])
+def test_long_decoding(name, dtype, prompt, steps):
+    """Hundreds of single-token steps (through the captured decode graph), across page, chunk and
+    temperature-floor boundaries, in a batch with a second, shorter request that ends on the way."""
+    n = prompt + steps
+    e = engine(name, dtype, max_tokens=1024)
+    a, b = tiny.random_tokens(n, vocab(name), 31), tiny.random_tokens(prompt + 40, vocab(name), 32)
+    rp = Replay(e)
+    rp.step([("a", a[:prompt], [prompt - 1]), ("b", b[:prompt], [prompt - 1])])
+    for i in range(prompt, n):
+        items = [("a", [a[i]], [0])]
+        if i < len(b):
+            items.append(("b", [b[i]], [0]))
+        rp.step(items)
+        if i == len(b) - 1:
+            rp.end("b")
+    rp.end("a")
+    checks = sorted(set(range(prompt - 1, n, 7)) | {n - 1, n - 2})
+    worst = compare_with_plain(model_dir(name), {"a": a, "b": b}, rp, dtype,
+                               {"a": checks, "b": list(range(prompt - 1, len(b), 5))})
+    print(f"long decoding {name} {dtype}: worst relative error {worst:.3e}")
+    # the same steps once more without the recording: decode now replays captured graphs, and must give
+    # the very same bits as the eager launches above
+    from cpi_b200.engine import StepEntry
+    e.capture_routing(False)
+    assert e.use_graphs
+    sa, sb = e.acquire_slot(), e.acquire_slot()
+    replays_before = e.graph_kernel_launches
+    e.step([StepEntry(sa, a[:prompt], []), StepEntry(sb, b[:prompt], [])])
+    for i in range(prompt, n):
+        entries = [StepEntry(sa, [a[i]], [0])]
+        if i < len(b):
+            entries.append(StepEntry(sb, [b[i]], [0]))
+        out = e.step(entries).cpu()
+        if i in checks:
+            assert torch.equal(out[0], rp.logits["a"][i]), f"graph replay differs from eager at position {i}"
+        if i == len(b) - 1:
+            e.release_slot(sb)
+    e.release_slot(sa)
+    e.check_device_errors()
+    assert e.graph_kernel_launches > replays_before
+
+
+@pytest.mark.parametrize("name,dtype", CASES)
+def test_first_tokens_of_a_sequence(name, dtype):
+    """Positions 0, 1, 2: as a three-token prompt, and one by one from an empty cache."""
+    e = engine(name, dtype)
+    t = tiny.random_tokens(3, vocab(name), 77)
+    rp = Replay(e)
+    rp.step([("whole", t, [0, 1, 2])]); rp.end("whole")
+    for i in range(3):
+        rp.step([("single", [t[i]], [0])])
+    rp.end("single")
+    compare_with_plain(model_dir(name), {"whole": t, "single": t}, rp, dtype)
