@@ -219,7 +219,8 @@ def run(args) -> dict:
     # ---- end to end through the Python entry point --------------------------------------------------
     plen = ctx - (steps + warm) - 1
     prompts = [toks(plen) for _ in range(B)]
-    model.generate(prompts[:1], max_new=2, temperature=0.0, stop_ids=[])      # warm the path
+    # warm-up: the same batch for `warm` steps (it also captures this batch size's decode graph), then the timed run
+    model.generate(prompts, max_new=warm + 1, temperature=0.0, stop_ids=[])
     model.generate(prompts, max_new=steps + 1, temperature=0.0, stop_ids=[])
     st = model.stats()
     e2e_value = B * st.decode_steps / (st.decode_ms / 1e3)

@@ -3,6 +3,7 @@
     python -m cpi_b200.csrc.cases gemm --tokens 8 --out 8192 --in 5120 --mode swiglu --groups 16
     python -m cpi_b200.csrc.cases attention_decode --batch 8 --context 4096
     python -m cpi_b200.csrc.cases attention_prefill --tokens 2048
+    python -m cpi_b200.csrc.cases step --layers 4 --batch 8 --context 4000 --decode
 
 Each case holds a few GB at most, flushes the L2 between launches (a 256 MB write), times `--reps`
 launches with CUDA events and prints the median with the bytes or flops the launch has to move.
@@ -116,6 +117,57 @@ def case_attention_prefill(a) -> None:
     print(f"attention_prefill tokens={T} heads={NH}/{NKV} D={D}: {us:.1f} us, {flops / us / 1e6:.1f} TFLOP/s (causal)")
 
 
+SCOUT_LAYER = {
+    "architectures": ["Llama4ForCausalLM"], "hidden_size": 5120, "num_attention_heads": 40,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192, "intermediate_size_mlp": 16384,
+    "num_local_experts": 16, "num_experts_per_tok": 1, "interleave_moe_layer_step": 1, "vocab_size": 202048,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "nope_layer_interval": 4, "attention_chunk_size": 8192, "use_qk_norm": True, "attn_temperature_tuning": True,
+    "floor_scale": 8192, "attn_scale": 0.1, "tie_word_embeddings": False, "max_position_embeddings": 131072,
+}
+
+
+def case_step(a) -> None:
+    """One whole engine step of a model with Scout-sized layers and random weights, bracketed by
+    cudaProfilerStart/Stop (use `ncu --profile-from-start off`); graphs off, so every kernel is a launch."""
+    from ..api import Model
+    from ..engine import StepEntry
+    cfg = dict(SCOUT_LAYER, num_hidden_layers=a.layers)
+    m = Model.random(cfg, 0, dtype="bfloat16", max_batch=a.batch, max_context=a.context + 64)
+    eng = m.engine
+    eng.use_graphs = False
+    g = torch.Generator().manual_seed(1)
+    toks = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist()
+    out = torch.empty(a.batch, dtype=torch.int32, device=DEV)
+    slots = [eng.acquire_slot() for _ in range(a.batch)]
+    if a.decode:
+        eng.step([StepEntry(s, toks(a.context), []) for s in slots])
+
+        def one():
+            K.argmax(eng.step([StepEntry(s, toks(1), [0]) for s in slots]), out)
+        for _ in range(3):
+            one()
+    else:
+        def one():
+            eng.step([StepEntry(s, toks(a.context), [a.context - 1]) for s in slots])
+            for s in slots:
+                eng.release_slot(s)
+            slots[:] = [eng.acquire_slot() for _ in range(a.batch)]
+        one()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.profiler.start()
+    e0.record()
+    one()
+    e1.record()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    print(f"step layers={a.layers} batch={a.batch} context={a.context} {'decode' if a.decode else 'prefill'}: "
+          f"{e0.elapsed_time(e1):.3f} ms")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(prog="python -m cpi_b200.csrc.cases")
     sub = ap.add_subparsers(dest="case", required=True)
@@ -131,6 +183,11 @@ def main() -> int:
     d.add_argument("--splits", type=int, default=0)
     p = sub.add_parser("attention_prefill")
     p.add_argument("--tokens", type=int, default=2048)
+    st = sub.add_parser("step")
+    st.add_argument("--layers", type=int, default=4)
+    st.add_argument("--batch", type=int, default=8)
+    st.add_argument("--context", type=int, default=4000)
+    st.add_argument("--decode", action="store_true", help="time a decode step after a prefill of --context tokens")
     for s in (g, d, p):
         s.add_argument("--reps", type=int, default=5)
     for s in (d, p):
@@ -138,7 +195,8 @@ def main() -> int:
         s.add_argument("--kv-heads", type=int, default=8)
         s.add_argument("--head-dim", type=int, default=128)
     a = ap.parse_args()
-    {"gemm": case_gemm, "attention_decode": case_attention_decode, "attention_prefill": case_attention_prefill}[a.case](a)
+    {"gemm": case_gemm, "attention_decode": case_attention_decode, "attention_prefill": case_attention_prefill,
+     "step": case_step}[a.case](a)
     return 0
 
 

@@ -150,6 +150,8 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   constexpr int ACC = MODE == kSwiglu ? 2 : 1;
   constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2;
   constexpr uint32_t STAGE_BYTES = ACC * A_BYTES + B_BYTES;
+  constexpr int BOX_ROWS = BN < 64 ? BN : 64;           // token rows per TMA box of the activation tile
+  constexpr uint32_t BOX_BYTES = BOX_ROWS * BK * 2;
   constexpr uint32_t TMEM_COLS = ACC * BN < 32 ? 32 : ACC * BN;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
@@ -180,6 +182,9 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int kt_begin = split * p.k_tiles_per_split;
   const int kt_end = min(p.k_tiles, kt_begin + p.k_tiles_per_split);
   const int n_kt = kt_end - kt_begin;
+  // only the boxes that hold rows of this tile are fetched (a group's tail tile may hold few)
+  const int n_boxes = (min(BN, t_end - t0) + BOX_ROWS - 1) / BOX_ROWS;
+  const uint32_t stage_tx = ACC * A_BYTES + (uint32_t)n_boxes * BOX_BYTES;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -201,23 +206,26 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     const int n_early = p.group_offsets ? 0 : min(n_kt, STAGES);
     for (int i = 0; i < n_early; ++i) {
       uint8_t* st = smem + (size_t)i * STAGE_BYTES;
-      mbar_expect_tx(&full_bar[i], STAGE_BYTES);
+      mbar_expect_tx(&full_bar[i], stage_tx);
       const int k = (kt_begin + i) * BK;
       tma_load_3d(st, &map_w, &full_bar[i], k, n0, group);
       if (ACC == 2) tma_load_3d(st + A_BYTES, &map_w, &full_bar[i], k, p.N + n0, group);
     }
     pdl_wait();
     for (int i = 0; i < n_early; ++i)
-      tma_load_2d(smem + (size_t)i * STAGE_BYTES + ACC * A_BYTES, &map_x, &full_bar[i], (kt_begin + i) * BK, t0);
+      for (int b = 0; b < n_boxes; ++b)
+        tma_load_2d(smem + (size_t)i * STAGE_BYTES + ACC * A_BYTES + b * BOX_BYTES, &map_x, &full_bar[i],
+                    (kt_begin + i) * BK, t0 + b * BOX_ROWS);
     for (int i = n_early; i < n_kt; ++i) {
       const int s = i % STAGES;
       if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
       uint8_t* st = smem + (size_t)s * STAGE_BYTES;
-      mbar_expect_tx(&full_bar[s], STAGE_BYTES);
+      mbar_expect_tx(&full_bar[s], stage_tx);
       const int k = (kt_begin + i) * BK;
       tma_load_3d(st, &map_w, &full_bar[s], k, n0, group);
       if (ACC == 2) tma_load_3d(st + A_BYTES, &map_w, &full_bar[s], k, p.N + n0, group);
-      tma_load_2d(st + ACC * A_BYTES, &map_x, &full_bar[s], k, t0);
+      for (int b = 0; b < n_boxes; ++b)
+        tma_load_2d(st + ACC * A_BYTES + b * BOX_BYTES, &map_x, &full_bar[s], k, t0 + b * BOX_ROWS);
     }
   } else if (warp == 1 && lane == 0) {
     // ---- MMA issuer ----
@@ -538,7 +546,7 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   CUtensorMap mw, mx;
   if (tc::get_map(w, (uint64_t)K, (uint64_t)rows_w, (uint64_t)groups, (uint64_t)K * 2, (uint64_t)K * 2 * rows_w,
                   tc::BK, tc::BM, &mw)) return 1;
-  if (tc::get_map(x, (uint64_t)K, (uint64_t)T, 0, (uint64_t)ldx * 2, 0, tc::BK, (uint32_t)bn, &mx)) return 1;
+  if (tc::get_map(x, (uint64_t)K, (uint64_t)T, 0, (uint64_t)ldx * 2, 0, tc::BK, (uint32_t)(bn < 64 ? bn : 64), &mx)) return 1;
   const int k_tiles = (K + tc::BK - 1) / tc::BK;
   const int per = (k_tiles + splits - 1) / splits;
   CPI_REQUIRE(splits >= 1 && (long)(splits - 1) * per < k_tiles, "gemm_tc: %d splits leave an empty split (k tiles %d)", splits, k_tiles);

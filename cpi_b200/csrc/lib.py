@@ -153,8 +153,8 @@ def _tc_state(device):
     key = (idx, torch.cuda.current_stream(device).cuda_stream)
     st = _tc_scratch.get(key)
     if st is None:
-        st = {"partials": torch.empty(1 << 20, dtype=torch.float32, device=device),
-              "tickets": torch.zeros(1 << 14, dtype=torch.int32, device=device),
+        st = {"partials": torch.empty(1 << 22, dtype=torch.float32, device=device),
+              "tickets": torch.zeros(1 << 16, dtype=torch.int32, device=device),
               "error": tc_error_flag(device)}
         _tc_scratch[key] = st
     return st

@@ -29,6 +29,38 @@ router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restri
   if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = s;
 }
 
+// The same sums for many tokens: one block per token keeps the token's row in registers and visits the
+// experts one after the other.  Thread i again sums elements i, i + 128, ... and the block sum is the
+// same, so a logit has the same bits whichever of the two kernels computed it.
+template <typename TH, typename TW>
+__global__ void __launch_bounds__(128)
+router_logits_rows_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
+                          float* __restrict__ logits, int hidden, int n_experts) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float scratch[32];
+  constexpr int PER = 64;                             // up to 8192 hidden elements in registers
+  const int t = blockIdx.x;
+  const TH* x = h + (size_t)t * h_stride;
+  float xv[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = threadIdx.x + j * 128;
+    xv[j] = i < hidden ? to_f32(x[i]) : 0.f;
+  }
+  for (int e = 0; e < n_experts; ++e) {
+    const TW* wr = w + (size_t)e * hidden;
+    float s = 0.f;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int i = threadIdx.x + j * 128;
+      if (i < hidden) s = fmaf(xv[j], to_f32(wr[i]), s);
+    }
+    s = block_sum(s, scratch);
+    if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = s;
+  }
+}
+
 // One thread per token: the k best logits, ties to the lowest index; gate = sigmoid of the chosen logit.
 __global__ void router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx,
                                      float* __restrict__ topk_gate, int n_tokens, int n_experts, int top_k,
@@ -129,9 +161,14 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
   CPI_REQUIRE(top_k >= 1 && top_k <= n_experts, "router: top-k %d of %d experts", top_k, n_experts);
   CPI_REQUIRE(logits != nullptr, "router: the logits buffer is missing");
   CPI_REQUIRE(n_tokens <= 65535, "router: too many tokens in one launch (%d)", n_tokens);
-  dim3 grid(n_experts, n_tokens);
-  CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-      (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
+  if (n_tokens >= 128 && hidden <= 64 * 128) {
+    CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
+        (cpi::launch_pdl(router_logits_rows_kernel<TH, TW>, n_tokens, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
+  } else {
+    dim3 grid(n_experts, n_tokens);
+    CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
+        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
+  }
   if (check_launch("router_logits")) return 2;
   cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
   return check_launch("router_select");

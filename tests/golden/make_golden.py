@@ -1,7 +1,7 @@
 """Makes tests/golden/tiny_r_reference.npz: logits of kurulav1/cpi's own, unmodified Llama4 CPU engine
 on the tiny configuration "R" (tests/tiny.py), for comparison with tests/plain_llama4.py.
 
-    python tests/golden/make_golden.py [REFERENCE_ROOT]        (default /root/reference)
+    python tests/golden/make_golden.py REFERENCE_ROOT        (a checkout of kurulav1/cpi)
 
 It compiles src/engine/llama4_cpu_engine.cpp, src/model/safetensors_loader.cpp and
 src/platform/mmap_file.cpp of the reference with ref_harness.cpp (g++, CUDA headers only, no CUDA
@@ -30,7 +30,9 @@ def weights_digest(model_dir):
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py REFERENCE_ROOT")
+    ref = sys.argv[1]
     work = tempfile.mkdtemp(prefix="cpi_golden_")
     exe = os.path.join(work, "ref_harness")
     srcs = [os.path.join(ref, p) for p in ("src/engine/llama4_cpu_engine.cpp", "src/model/safetensors_loader.cpp",
