@@ -213,6 +213,15 @@ class Llama4TextConfig:
         nrl = d.get("no_rope_layers")
         if nrl is not None and len(nrl) == 0:
             nrl = None
+        lt = d.get("layer_types")
+        if nrl is None and lt:
+            # per-layer attention kinds: "chunked_attention" layers rotate and see their chunk,
+            # "full_attention" layers have no position encoding and see every key
+            known = {"chunked_attention": 1, "full_attention": 0}
+            for i, kind in enumerate(lt):
+                if kind not in known:
+                    raise ConfigError(f"config.json: 'layer_types'[{i}] is '{kind}', expected one of {sorted(known)}")
+            nrl = [known[kind] for kind in lt]
         ml = d.get("moe_layers")
         cfg = Llama4TextConfig(
             rope_scaling=scaling,

@@ -60,6 +60,10 @@ def case_gemm(a) -> None:
         offs[1:] = counts.cumsum(0)
         kw = dict(m_rows=T, group_offsets=offs.to(DEV), n_groups=G)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    if a.bn:
+        kw["force_bn"] = a.bn
+    if a.splits:
+        kw["force_splits"] = a.splits
     if not K.gemm_tc(x, w, out, mode, **kw):
         sys.exit("this shape is outside what the tensor-core kernel takes")
     us = _timed(lambda: K.gemm_tc(x, w, out, mode, **kw), a.reps, flush)
@@ -177,6 +181,8 @@ def main() -> int:
     g.add_argument("--in", dest="inp", type=int, default=5120)
     g.add_argument("--mode", choices=["store", "add", "swiglu"], default="store")
     g.add_argument("--groups", type=int, default=0)
+    g.add_argument("--bn", type=int, default=0, help="force the token-tile width (tuning)")
+    g.add_argument("--splits", type=int, default=0, help="force the split-K count (tuning)")
     d = sub.add_parser("attention_decode")
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=4096)

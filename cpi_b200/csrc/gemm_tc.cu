@@ -47,6 +47,7 @@ struct Params {
   const float* row_scale;
   const int* group_offsets; int n_groups;
   int T;               // logical token rows (all groups)
+  int bn;              // token rows per tile: a multiple of 16, at most the kernel's BN
   int N;               // output features
   int k_tiles;         // ceil(K / 64)
   int splits, k_tiles_per_split;
@@ -169,13 +170,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     bool found = false;
     for (int g = 0; g < p.n_groups; ++g) {
       const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
-      const int tiles = (e - b + BN - 1) / BN;
+      const int tiles = (e - b + p.bn - 1) / p.bn;
       if (tile_t < tiles) { group = g; t_begin = b; t_end = e; found = true; break; }
       tile_t -= tiles;
     }
     if (!found) return;
   }
-  const int t0 = t_begin + tile_t * BN;
+  const int t0 = t_begin + tile_t * p.bn;
   if (t0 >= t_end) return;
   const int n0 = blockIdx.x * BM;
   const int split = blockIdx.z;
@@ -183,7 +184,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int kt_end = min(p.k_tiles, kt_begin + p.k_tiles_per_split);
   const int n_kt = kt_end - kt_begin;
   // only the boxes that hold rows of this tile are fetched (a group's tail tile may hold few)
-  const int n_boxes = (min(BN, t_end - t0) + BOX_ROWS - 1) / BOX_ROWS;
+  const int n_boxes = (min(p.bn, t_end - t0) + BOX_ROWS - 1) / BOX_ROWS;
   const uint32_t stage_tx = ACC * A_BYTES + (uint32_t)n_boxes * BOX_BYTES;
 
   if (tid == 0) {
@@ -231,7 +232,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     // ---- MMA issuer ----
     // The MMA's N is a run-time field of the instruction descriptor: a tile with few rows (the tail of a
     // group, or a group with few tokens) multiplies only those columns, rounded up to 16.
-    const int n_rows_here = min(BN, (p.group_offsets ? t_end : p.T) - t0);
+    const int n_rows_here = min(p.bn, (p.group_offsets ? t_end : p.T) - t0);
     const uint32_t idesc = instr_desc_bf16(min(BN, (n_rows_here + 15) & ~15));
     bool ok = true;
     for (int i = 0; i < n_kt && ok; ++i) {
@@ -262,7 +263,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int row = warp * 32 + lane;                       // accumulator lane = output feature n0 + row
   const int n = n0 + row;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-  const int n_valid_t = min(BN, t_end - t0);
+  const int n_valid_t = min(p.bn, t_end - t0);
   const int n_cols = min(BN, (n_valid_t + 15) & ~15);          // columns the MMAs wrote
   TO* out = reinterpret_cast<TO*>(p.out);
 
@@ -502,6 +503,19 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
   while (bn < 256 && bn < rows_per_group) bn *= 2;
   if (swiglu && bn > 256) bn = 256;
   const int n_tiles = (N + tc::BM - 1) / tc::BM;
+  if (n_groups == 0 && T > 256) {
+    // many tokens: one CTA per SM at a time, and a tile's time follows the operand bytes it pulls through
+    // the L2 per k-step (128 or 256 weight rows + the token rows), so time ~ waves x (weight rows + width);
+    // a somewhat narrower tile can turn "3.03 waves" into 3
+    long best_cost = -1;
+    const int w_rows = swiglu ? 256 : 128;
+    for (int cand = 256; cand >= 128; cand -= 16) {
+      const long ctas = (long)n_tiles * ((T + cand - 1) / cand);
+      const long waves = (ctas + 147) / 148;
+      const long cost = waves * (cand + w_rows);
+      if (best_cost < 0 || cost < best_cost) { best_cost = cost; bn = cand; }
+    }
+  }
   // token tiles that can hold rows: sum_g ceil(rows_g / bn) <= ceil(T / bn) + min(T, groups); they are
   // the first values of blockIdx.y, so scratch is only needed for those
   const int live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
@@ -546,7 +560,10 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   CUtensorMap mw, mx;
   if (tc::get_map(w, (uint64_t)K, (uint64_t)rows_w, (uint64_t)groups, (uint64_t)K * 2, (uint64_t)K * 2 * rows_w,
                   tc::BK, tc::BM, &mw)) return 1;
-  if (tc::get_map(x, (uint64_t)K, (uint64_t)T, 0, (uint64_t)ldx * 2, 0, tc::BK, (uint32_t)(bn < 64 ? bn : 64), &mx)) return 1;
+  if (tc::get_map(x, (uint64_t)K, (uint64_t)T, 0, (uint64_t)ldx * 2, 0, tc::BK, (uint32_t)(bn < 64 ? bn : 64), &mx)) return 1;   // bn < 64 is a power of two
+  CPI_REQUIRE(bn >= 16 && bn <= 256 && bn % 16 == 0, "gemm_tc: token tile %d (multiples of 16 up to 256)", bn);
+  int cap = 16;                                   // the compiled tile that holds bn rows
+  while (cap < bn) cap *= 2;
   const int k_tiles = (K + tc::BK - 1) / tc::BK;
   const int per = (k_tiles + splits - 1) / splits;
   CPI_REQUIRE(splits >= 1 && (long)(splits - 1) * per < k_tiles, "gemm_tc: %d splits leave an empty split (k tiles %d)", splits, k_tiles);
@@ -555,14 +572,15 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   if (splits > 1) {
     const long live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
     const long tiles = (long)grid.x * live_y;
+    CPI_REQUIRE(bn == cap, "gemm_tc: split-K needs a power-of-two token tile, got %d", bn);
     CPI_REQUIRE(partials && tickets && partials_elems >= tiles * splits * acc * bn * tc::BM && tickets_elems >= tiles,
                 "gemm_tc: split-K scratch is too small (tiles %ld, splits %d)", tiles, splits);
   }
-  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, N, k_tiles, splits, per, partials, tickets, error_flag};
-  if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(bn, mw, mx, p, grid, stream);
-  if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(bn, mw, mx, p, grid, stream);
-  if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(bn, mw, mx, p, grid, stream);
-  if (mode == tc::kSwiglu) return tc::launch_bn<tc::kSwiglu, __nv_bfloat16>(bn, mw, mx, p, grid, stream);
+  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, partials, tickets, error_flag};
+  if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(cap, mw, mx, p, grid, stream);
+  if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(cap, mw, mx, p, grid, stream);
+  if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(cap, mw, mx, p, grid, stream);
+  if (mode == tc::kSwiglu) return tc::launch_bn<tc::kSwiglu, __nv_bfloat16>(cap, mw, mx, p, grid, stream);
   set_error("gemm_tc: unsupported mode %d with output dtype %d", mode, out_dtype);
   return 1;
 }

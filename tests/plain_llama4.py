@@ -78,6 +78,8 @@ def layer_is_moe(c: dict, i: int) -> bool:
 def layer_uses_rope(c: dict, i: int) -> bool:
     if c.get("no_rope_layers"):
         return bool(c["no_rope_layers"][i])
+    if c.get("layer_types"):
+        return c["layer_types"][i] == "chunked_attention"
     n = c["nope_layer_interval"]
     return True if n <= 0 else (i + 1) % n != 0
 

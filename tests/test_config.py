@@ -37,6 +37,16 @@ def test_layer_kinds():
     assert [x.layer_is_moe(i) for i in range(4)] == [False, False, True, False]
 
 
+def test_layer_types_list():
+    c = tiny.config("A")
+    c["layer_types"] = ["full_attention", "chunked_attention", "chunked_attention", "full_attention"]
+    x = Llama4TextConfig.from_json_dict(c)
+    assert [x.layer_uses_rope(i) for i in range(4)] == [False, True, True, False]
+    c["layer_types"][1] = "sliding"
+    with pytest.raises(ConfigError, match="layer_types"):
+        Llama4TextConfig.from_json_dict(c)
+
+
 def test_defaults_and_derived():
     c = tiny.config("A")
     for k in ("head_dim", "intermediate_size_mlp", "rms_norm_eps", "rope_theta", "num_experts_per_tok"):

@@ -177,3 +177,21 @@ def test_first_tokens_of_a_sequence(name, dtype):
         rp.step([("single", [t[i]], [0])])
     rp.end("single")
     compare_with_plain(model_dir(name), {"whole": t, "single": t}, rp, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_weights_stored_in_float32_stay_float32(dtype):
+    """A model folder whose tensors are F32: they are kept in 32-bit, and both precisions still match."""
+    from cpi_b200.engine import Engine
+    d = tiny.make_model_dir("B", seed=5, dtype=torch.float32)
+    e = Engine.from_model_dir(d, dtype=dtype, max_tokens=256)
+    assert e.model.layers[1].mixer.w_qkv.dtype == torch.float32 and e.model.embedding.dtype == torch.float32
+    reqs = {"x": tiny.random_tokens(50, 1000, 8), "y": tiny.random_tokens(9, 1000, 9)}
+    rp = Replay(e)
+    rp.step([("x", reqs["x"][:40], [39]), ("y", reqs["y"][:8], [7])])
+    rp.step([("x", [reqs["x"][40]], [0]), ("y", [reqs["y"][8]], [0])])
+    rp.end("y")
+    for t in reqs["x"][41:]:
+        rp.step([("x", [t], [0])])
+    rp.end("x")
+    compare_with_plain(d, reqs, rp, dtype, {"x": list(range(39, 50)), "y": [7, 8]})
