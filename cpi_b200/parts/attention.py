@@ -23,6 +23,10 @@ from .base import Mixer, build_part, register_mixer
 from .linear import MODE_ADD, project
 
 
+# set to False to run every attention through the general kernel (tests compare the two families)
+use_tensor_core_kernels = True
+
+
 @register_mixer("attention")
 class AttentionMixer(Mixer):
     def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
@@ -96,7 +100,7 @@ class AttentionMixer(Mixer):
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]
-        if (batch.is_decode and q.dtype == torch.bfloat16
+        if (use_tensor_core_kernels and batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
             # keys per sequence that the window lets through, at most (a bucketed bound: the split count
             # then stays the same from step to step, which a captured graph needs)
@@ -114,7 +118,7 @@ class AttentionMixer(Mixer):
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                                window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)
             return
-        if (not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
+        if (use_tensor_core_kernels and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
                 and K.attention_prefill_supported(self.nh, self.nkv, self.d, page_size)):
             K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                 batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=self.nh,

@@ -195,3 +195,50 @@ def test_weights_stored_in_float32_stay_float32(dtype):
         rp.step([("x", [t], [0])])
     rp.end("x")
     compare_with_plain(d, reqs, rp, dtype, {"x": list(range(39, 50)), "y": [7, 8]})
+
+
+def test_long_context_across_the_chunk_boundary_both_kernel_families_agree():
+    """Head size 128, chunk 8192, temperature floor 8192: a 9,000-token prompt (its tiles straddle the
+    chunk boundary and run as two pieces) and decoding from 8,150 across position 8,192, once on the
+    tensor-core kernels and once on the general ones."""
+    from cpi_b200.engine import Engine, StepEntry
+    from cpi_b200.parts import attention, linear
+    cfg = {
+        "architectures": ["Llama4ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 512,
+        "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 512,
+        "num_local_experts": 4, "num_experts_per_tok": 1, "vocab_size": 1024, "nope_layer_interval": 2,
+        "attention_chunk_size": 8192, "floor_scale": 8192, "attn_scale": 0.1, "initializer_range": 0.05,
+        "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+    }
+    d = tiny.make_model_dir(cfg, seed=4)
+    long_prompt = tiny.random_tokens(9000, 1024, 1)
+    dec = tiny.random_tokens(8150 + 120, 1024, 2)
+    outs = {}
+    for fast in (True, False):
+        attention.use_tensor_core_kernels = fast
+        linear.use_tensor_cores = fast
+        try:
+            e = Engine.from_model_dir(d, dtype="bfloat16", max_tokens=9216 + 8320, max_seqs=2, max_seq_len=9216)
+            e.use_graphs = fast
+            s = e.acquire_slot()
+            rows = [e.step([StepEntry(s, long_prompt, [8191, 8192, 8999])]).float().cpu()]
+            e.release_slot(s)
+            s = e.acquire_slot()
+            e.step([StepEntry(s, dec[:8150], [])])
+            for t in dec[8150:]:
+                rows.append(e.step([StepEntry(s, [t], [0])]).float().cpu())
+            e.release_slot(s)
+            e.check_device_errors()
+            e.cache.check_consistency()
+            outs[fast] = torch.cat(rows)
+            del e
+        finally:
+            attention.use_tensor_core_kernels = True
+            linear.use_tensor_cores = True
+    a, b = outs[True], outs[False]
+    scale = float(b.abs().max())
+    err = float((a - b).abs().max()) / scale
+    print(f"long context: tensor-core vs general kernels, worst relative difference {err:.3e}")
+    assert err <= 3e-2
+    assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.9
