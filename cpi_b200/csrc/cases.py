@@ -64,12 +64,13 @@ def case_gemm(a) -> None:
         kw["force_bn"] = a.bn
     if a.splits:
         kw["force_splits"] = a.splits
-    if not K.gemm_tc(x, w, out, mode, **kw):
+    fn = K.gemm_tc_pair if a.pair else K.gemm_tc
+    if not fn(x, w, out, mode, **kw):
         sys.exit("this shape is outside what the tensor-core kernel takes")
-    us = _timed(lambda: K.gemm_tc(x, w, out, mode, **kw), a.reps, flush)
+    us = _timed(lambda: fn(x, w, out, mode, **kw), a.reps, flush)
     wbytes = touched * rows * Kd * 2
     flops = 2.0 * T * rows * Kd
-    print(f"gemm tokens={T} out={N} in={Kd} mode={a.mode} groups={G} (touched {touched}): {us:.1f} us, "
+    print(f"gemm{' (pair)' if a.pair else ''} tokens={T} out={N} in={Kd} mode={a.mode} groups={G} (touched {touched}): {us:.1f} us, "
           f"weights {wbytes / 1e6:.0f} MB -> {wbytes / us / 1e6:.2f} TB/s, {flops / us / 1e6:.1f} TFLOP/s")
 
 
@@ -181,6 +182,7 @@ def main() -> int:
     g.add_argument("--in", dest="inp", type=int, default=5120)
     g.add_argument("--mode", choices=["store", "add", "swiglu"], default="store")
     g.add_argument("--groups", type=int, default=0)
+    g.add_argument("--pair", action="store_true", help="use the paired (two-SM) kernel")
     g.add_argument("--bn", type=int, default=0, help="force the token-tile width (tuning)")
     g.add_argument("--splits", type=int, default=0, help="force the split-K count (tuning)")
     d = sub.add_parser("attention_decode")

@@ -453,6 +453,12 @@ int get_map_2d_bf16(const void* ptr, uint64_t inner, uint64_t rows, uint64_t row
   return get_map(ptr, inner, rows, 0, row_stride_bytes, 0, box_inner, box_rows, out);
 }
 
+// 3-D bf16 tensor [groups][rows][inner], contiguous; box box_inner x box_rows x 1 (the paired kernel uses it too)
+int get_map_3d_bf16(const void* ptr, uint64_t inner, uint64_t rows, uint64_t groups, uint32_t box_inner,
+                    uint32_t box_rows, CUtensorMap* out) {
+  return get_map(ptr, inner, rows, groups, inner * 2, inner * 2 * rows, box_inner, box_rows, out);
+}
+
 template <int BN, int MODE, typename TO>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
   constexpr int ACC = MODE == kSwiglu ? 2 : 1;

@@ -14,12 +14,16 @@ MODE_STORE, MODE_ADD, MODE_SWIGLU = K.MODE_STORE, K.MODE_ADD, K.MODE_SWIGLU
 
 # set to False to force the FP32-pipe kernel everywhere (tests compare the two)
 use_tensor_cores = True
+# set to False to keep dense products with many tokens on the single-CTA kernel
+use_paired_kernel = True
 
 
 def project(a, w, out, mode=MODE_STORE, **kw):
     """Dense or grouped projection; see csrc/lib.py: gemm_simt for the keyword arguments."""
     if use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        fast = getattr(K, "gemm_tc", None)
-        if fast is not None and fast(a, w, out, mode, **kw):
+        plain = not (set(kw) - {"row_scale"})          # no groups, gather or scatter
+        if use_paired_kernel and plain and a.shape[0] >= 512 and K.gemm_tc_pair(a, w, out, mode, **kw):
+            return
+        if K.gemm_tc(a, w, out, mode, **kw):
             return
     K.gemm_simt(a, w, out, mode, **kw)

@@ -120,6 +120,28 @@ def test_gemm_tensor_core_modes(T, N, Kd, mode):
         assert err <= tol, (odt, err, tol)
 
 
+@pytest.mark.parametrize("T,N,Kd", [(512, 256, 64), (2048, 1024, 512), (700, 512, 200), (1000, 768, 1032), (4096, 5120, 256)])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gemm_tensor_core_pair_kernel(T, N, Kd, mode):
+    """Two CTAs on one tile: every mode, token tails that are no multiple of 32, k tails."""
+    a = rnd(T, Kd, dtype=torch.bfloat16)
+    w = rnd(2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=2, scale=Kd ** -0.5)
+    scale = rnd(T, seed=5).abs()
+    for odt in ([torch.float32] if mode == 1 else [torch.bfloat16] if mode == 2 else [torch.bfloat16, torch.float32]):
+        out = rnd(T, N, dtype=odt, seed=3)
+        ref = ref_gemm(a, w, mode, out.float().clone(), scale)
+        assert K().gemm_tc_pair(a, w, out, mode, row_scale=scale)
+        torch.cuda.synchronize()
+        assert int(K().tc_error_flag(DEV)) == 0
+        tol = (2e-5 if odt == torch.float32 else 1e-2) * max(1.0, float(ref.abs().max()))
+        err = float((out.float() - ref).abs().max())
+        assert err <= tol, (odt, err, tol)
+    assert not K().gemm_tc_pair(a[:100], w, out[:100], mode)                # too few tokens
+    if N % 256 == 0:
+        wn = w[: (2 * (N - 128) if mode == 2 else N - 128)].contiguous()
+        assert not K().gemm_tc_pair(a, wn, out[:, : N - 128], mode)         # features no multiple of 256
+
+
 def test_gemm_tensor_core_refuses_what_it_cannot_take():
     a, w = rnd(4, 36, dtype=torch.bfloat16), rnd(128, 36, dtype=torch.bfloat16)
     out = torch.empty(4, 128, dtype=torch.bfloat16, device=DEV)
