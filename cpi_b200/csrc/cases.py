@@ -21,24 +21,33 @@ from . import lib as K
 DEV = "cuda:0"
 
 
-def _timed(fn, reps: int, flush: torch.Tensor):
-    fn()
+def _graph_ms(body, reps: int) -> float:
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for _ in range(reps):
+            body()
+    g.replay()
     torch.cuda.synchronize()
     times = []
-    for _ in range(reps):
-        flush.zero_()
+    for _ in range(3):
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g = torch.cuda.CUDAGraph()          # a one-kernel graph: the launch latency of Python stays outside
-        with torch.cuda.graph(g):
-            fn()
-        flush.zero_()
         e0.record()
         g.replay()
         e1.record()
         torch.cuda.synchronize()
-        times.append(e0.elapsed_time(e1) * 1e3)
-    times.sort()
-    return times[len(times) // 2]
+        times.append(e0.elapsed_time(e1))
+    return sorted(times)[1]
+
+
+def _timed(fn, reps: int, flush: torch.Tensor) -> float:
+    """Microseconds per launch: a graph of `reps` x (L2 flush, kernel) minus a graph of `reps` flushes, so
+    that neither the launch latency of Python nor the flush is counted."""
+    fn()
+    torch.cuda.synchronize()
+    reps = max(reps, 5)
+    both = _graph_ms(lambda: (flush.zero_(), fn()), reps)
+    only = _graph_ms(lambda: flush.zero_(), reps)
+    return (both - only) * 1e3 / reps
 
 
 def case_gemm(a) -> None:

@@ -158,6 +158,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s, ticket_s;
+  __shared__ int offs_s[257], tiles_s[256], found_s[2];   // group offsets and tile counts (at most 256 groups)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -167,13 +168,27 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   int group = 0, t_begin = 0, t_end = p.T, tile_t = blockIdx.y;
   if (p.group_offsets) {
     pdl_wait();                                  // the row lists come from the kernel before this one
-    bool found = false;
-    for (int g = 0; g < p.n_groups; ++g) {
+    // One division per group, done by one thread each; thread 0 then walks the counts.  (Every CTA of the
+    // launch does this, also the many that find no tile, so it has to be cheap.)
+    for (int g = tid; g < p.n_groups; g += 128) {
       const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
-      const int tiles = (e - b + p.bn - 1) / p.bn;
-      if (tile_t < tiles) { group = g; t_begin = b; t_end = e; found = true; break; }
-      tile_t -= tiles;
+      offs_s[g] = b;
+      tiles_s[g] = (e - b + p.bn - 1) / p.bn;
+      if (g == p.n_groups - 1) offs_s[g + 1] = e;
     }
+    __syncthreads();
+    if (tid == 0) {
+      int rest = tile_t, hit = -1;
+      for (int g = 0; g < p.n_groups; ++g) {
+        if (rest < tiles_s[g]) { hit = g; break; }
+        rest -= tiles_s[g];
+      }
+      found_s[0] = hit;
+      found_s[1] = rest;
+    }
+    __syncthreads();
+    const bool found = found_s[0] >= 0;
+    if (found) { group = found_s[0]; tile_t = found_s[1]; t_begin = offs_s[group]; t_end = offs_s[group + 1]; }
     if (!found) return;
   }
   const int t0 = t_begin + tile_t * p.bn;
@@ -558,6 +573,7 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   CPI_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K (%d) and the activation row stride (%ld) must be multiples of 8", K, ldx);
   CPI_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
               "gemm_tc: operands must be 16-byte aligned");
+  CPI_REQUIRE(n_groups <= 256, "gemm_tc: %d groups (at most 256)", n_groups);
   CPI_REQUIRE(mode != tc::kAdd || out_dtype == kF32, "gemm_tc: ADD mode needs a float32 output");
   CPI_REQUIRE(mode != tc::kSwiglu || out_dtype == kBF16, "gemm_tc: SWIGLU mode writes bfloat16");
   const int acc = mode == tc::kSwiglu ? 2 : 1;
@@ -573,7 +589,8 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   const int k_tiles = (K + tc::BK - 1) / tc::BK;
   const int per = (k_tiles + splits - 1) / splits;
   CPI_REQUIRE(splits >= 1 && (long)(splits - 1) * per < k_tiles, "gemm_tc: %d splits leave an empty split (k tiles %d)", splits, k_tiles);
-  dim3 grid((N + tc::BM - 1) / tc::BM, n_groups > 0 ? (T + bn - 1) / bn + n_groups : (T + bn - 1) / bn, splits);
+  // token tiles: sum_g ceil(rows_g / bn) <= ceil(T / bn) + min(T, groups)
+  dim3 grid((N + tc::BM - 1) / tc::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), splits);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc: too many token tiles (%u)", grid.y);
   if (splits > 1) {
     const long live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
