@@ -74,6 +74,8 @@ def case_gemm(a) -> None:
     if a.splits:
         kw["force_splits"] = a.splits
     fn = K.gemm_tc_pair if a.pair else K.gemm_tc
+    if a.pair:
+        kw.pop("force_bn", None); kw.pop("force_splits", None)
     if not fn(x, w, out, mode, **kw):
         sys.exit("this shape is outside what the tensor-core kernel takes")
     us = _timed(lambda: fn(x, w, out, mode, **kw), a.reps, flush)

@@ -11,7 +11,8 @@
 // signal the peer's barrier; no multicast load is used); the leader's `tcgen05.commit` with
 // `multicast::cluster` frees the stage in both CTAs and, at the end, tells both that the accumulators
 // are complete.  Every wait is bounded; a CTA that gives up raises the error flag and leaves.
-// Epilogues as in gemm_tc.cu: STORE, ADD (float32 residual), SWIGLU; no groups and no split-K here.
+// Epilogues as in gemm_tc.cu: STORE, ADD (float32 residual), SWIGLU, with groups (routed experts), a
+// per-token scale and output row scatter; no split-K here.
 // The reference has no tensor-core kernel of its own (src/kernels/kernels_ops_matvec.cu:343-418 are
 // SIMT GEMVs); this file has no counterpart there.
 #include "common.cuh"
@@ -34,7 +35,9 @@ enum Mode : int { kStore = 0, kAdd = 1, kSwiglu = 2 };
 
 struct Params {
   void* out; long ldo;
+  const int* out_rows;
   const float* row_scale;
+  const int* group_offsets; int n_groups;      // routed experts: tokens [offsets[g], offsets[g+1]) use W[g]
   int T, bn, N, k_tiles;
   int* error_flag;
 };
@@ -132,15 +135,40 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ int offs_s[257], tiles_s[256], found_s[2];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t rank = cluster_rank();                          // 0: leader (issues the MMAs), 1: peer
   pdl_launch_dependents();
 
+  // ---- which tile (both CTAs of a pair share blockIdx.y, so they find the same one) ----
+  int group = 0, t_begin = 0, t_end = p.T, tile_t = blockIdx.y;
+  if (p.group_offsets) {
+    pdl_wait();
+    for (int g = tid; g < p.n_groups; g += 128) {
+      const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
+      offs_s[g] = b;
+      tiles_s[g] = (e - b + p.bn - 1) / p.bn;
+      if (g == p.n_groups - 1) offs_s[g + 1] = e;
+    }
+    __syncthreads();
+    if (tid == 0) {
+      int rest = tile_t, hit = -1;
+      for (int g = 0; g < p.n_groups; ++g) {
+        if (rest < tiles_s[g]) { hit = g; break; }
+        rest -= tiles_s[g];
+      }
+      found_s[0] = hit;
+      found_s[1] = rest;
+    }
+    __syncthreads();
+    if (found_s[0] < 0) return;                                  // both CTAs of the pair leave together
+    group = found_s[0]; tile_t = found_s[1]; t_begin = offs_s[group]; t_end = offs_s[group + 1];
+  }
   const int n0 = blockIdx.x * BM;                                // this CTA's output features
-  const int t0 = blockIdx.y * p.bn;
-  const int n_valid_t = min(p.bn, p.T - t0);
+  const int t0 = t_begin + tile_t * p.bn;
+  const int n_valid_t = min(p.bn, t_end - t0);
   const int n_mma = min(BN, (n_valid_t + 31) & ~31);             // MMA width: both halves stay multiples of 16
   const int half = n_mma / 2;                                    // token rows of the tile staged by each CTA
   const int n_boxes = (half + BOX_ROWS - 1) / BOX_ROWS;
@@ -166,13 +194,13 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
 
   if (warp == 0 && lane == 0) {
     // ---- TMA producer (both CTAs): weights before the wait on the preceding kernel, tokens after ----
-    const int n_early = min(n_kt, STAGES);
+    const int n_early = p.group_offsets ? 0 : min(n_kt, STAGES);
     for (int i = 0; i < n_early; ++i) {
       uint8_t* st = smem + (size_t)i * STAGE_BYTES;
       const uint32_t bar = map_to_cta(smem_u32(&full_bar[i]), 0);
       if (rank == 0) mbar_expect_tx(&full_bar[i], 2 * cta_tx);
-      tma2_load_3d(st, &map_w, bar, i * BK, n0, 0);
-      if (ACC == 2) tma2_load_3d(st + A_BYTES, &map_w, bar, i * BK, p.N + n0, 0);
+      tma2_load_3d(st, &map_w, bar, i * BK, n0, group);
+      if (ACC == 2) tma2_load_3d(st + A_BYTES, &map_w, bar, i * BK, p.N + n0, group);
     }
     pdl_wait();
     for (int i = 0; i < n_early; ++i) {
@@ -183,12 +211,12 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
     }
     for (int i = n_early; i < n_kt; ++i) {
       const int s = i % STAGES;
-      if (!mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
+      if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
       uint8_t* st = smem + (size_t)s * STAGE_BYTES;
       const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
       if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * cta_tx);
-      tma2_load_3d(st, &map_w, bar, i * BK, n0, 0);
-      if (ACC == 2) tma2_load_3d(st + A_BYTES, &map_w, bar, i * BK, p.N + n0, 0);
+      tma2_load_3d(st, &map_w, bar, i * BK, n0, group);
+      if (ACC == 2) tma2_load_3d(st + A_BYTES, &map_w, bar, i * BK, p.N + n0, group);
       for (int b = 0; b < n_boxes; ++b)
         tma2_load_2d(st + ACC * A_BYTES + b * BOX_BYTES, &map_x, bar, i * BK, t0 + (int)rank * half + b * BOX_ROWS);
     }
@@ -233,7 +261,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         const int col = c + j;
-        dst[j] = (row_ok && col < n_valid_t) ? outf[(size_t)(t0 + col) * p.ldo + n] : 0.f;
+        dst[j] = (row_ok && col < n_valid_t) ? outf[(size_t)(p.out_rows ? p.out_rows[t0 + col] : t0 + col) * p.ldo + n] : 0.f;
       }
     };
     fetch(0, old[0]);
@@ -251,7 +279,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
           const int col = cc + j;
           if (row_ok && col < n_valid_t) {
             const float s = p.row_scale ? p.row_scale[t0 + col] : 1.0f;
-            outf[(size_t)(t0 + col) * p.ldo + n] = old[h][j] + v[j] * s;
+            outf[(size_t)(p.out_rows ? p.out_rows[t0 + col] : t0 + col) * p.ldo + n] = old[h][j] + v[j] * s;
           }
         }
       }
@@ -269,7 +297,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
         const float s = p.row_scale ? p.row_scale[t0 + col] : 1.0f;
         float x = v[j] * s;
         if (MODE == kSwiglu) x = x / (1.0f + __expf(-x)) * (u[j] * s);
-        store_out<TO>(out + (size_t)(t0 + col) * p.ldo + n, x);
+        store_out<TO>(out + (size_t)(p.out_rows ? p.out_rows[t0 + col] : t0 + col) * p.ldo + n, x);
       }
     }
   }
@@ -322,8 +350,15 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 using namespace cpi;
 
 // Whether the paired kernel takes this product, and the token-tile width it would use (0: not taken).
-extern "C" int cpi_gemm_tc_pair_plan(int T, int N, int K, int swiglu) {
-  if (T < 512 || N % 256 != 0 || K % 8 != 0) return 0;
+extern "C" int cpi_gemm_tc_pair_plan(int T, int N, int K, int swiglu, int n_groups) {
+  if (N % 256 != 0 || K % 8 != 0) return 0;
+  if (n_groups > 0) {
+    // experts: one token tile per expert (its weights are then read once), sized for 1.5 x the mean rows
+    if (n_groups > 256 || T < 64 * n_groups) return 0;
+    const int want = (3 * ((T + n_groups - 1) / n_groups) + 1) / 2;
+    return want > 128 ? 256 : 128;
+  }
+  if (T < 512) return 0;
   // one pair per two SMs at a time: time ~ waves x (weight rows + half the tile width) per SM
   long best_cost = -1;
   int bn = 0;
@@ -340,8 +375,8 @@ extern "C" int cpi_gemm_tc_pair_plan(int T, int N, int K, int swiglu) {
 
 // x [T, K] bf16 (row stride ldx), w [N or 2N][K] bf16 contiguous, out [T, N]; bn from cpi_gemm_tc_pair_plan.
 extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* out, int out_dtype, long ldo,
-                                const float* row_scale, int T, int N, int K, int mode, int bn, int* error_flag,
-                                cudaStream_t stream) {
+                                const int* out_rows, const float* row_scale, const int* group_offsets, int n_groups,
+                                int T, int N, int K, int mode, int bn, int* error_flag, cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
   CPI_REQUIRE(N % 256 == 0 && K % 8 == 0 && ldx % 8 == 0, "gemm_tc_pair: N (%d) must be a multiple of 256, K (%d) and the row stride of 8", N, K);
   CPI_REQUIRE(bn >= 32 && bn <= 256 && bn % 32 == 0, "gemm_tc_pair: token tile %d (multiples of 32 up to 256)", bn);
@@ -350,10 +385,11 @@ extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* ou
   CPI_REQUIRE(mode != tc2::kSwiglu || out_dtype == kBF16, "gemm_tc_pair: SWIGLU mode writes bfloat16");
   const int acc = mode == tc2::kSwiglu ? 2 : 1;
   CUtensorMap mw, mx;
-  if (tc::get_map_3d_bf16(w, (uint64_t)K, (uint64_t)acc * N, 1, tc2::BK, tc2::BM, &mw)) return 1;
+  CPI_REQUIRE(n_groups <= 256, "gemm_tc_pair: %d groups (at most 256)", n_groups);
+  if (tc::get_map_3d_bf16(w, (uint64_t)K, (uint64_t)acc * N, (uint64_t)(n_groups > 0 ? n_groups : 1), tc2::BK, tc2::BM, &mw)) return 1;
   if (tc::get_map_2d_bf16(x, (uint64_t)K, (uint64_t)T, (uint64_t)ldx * 2, tc2::BK, 64, &mx)) return 1;
-  tc2::Params p{out, ldo, row_scale, T, bn, N, (K + tc2::BK - 1) / tc2::BK, error_flag};
-  dim3 grid(N / tc2::BM, (T + bn - 1) / bn, 1);
+  tc2::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, (K + tc2::BK - 1) / tc2::BK, error_flag};
+  dim3 grid(N / tc2::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), 1);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc_pair: too many token tiles (%u)", grid.y);
   const int cap = bn <= 128 ? 128 : 256;
 #define CPI_PAIR(CAP)                                                                                         \

@@ -219,27 +219,33 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
     return True
 
 
-def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, row_scale=None) -> bool:
-    """The paired (two-SM) tcgen05 kernel for dense products with many tokens (see gemm_tc_pair.cu).
-    Returns False, having launched nothing, when the product is outside what it takes."""
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != 2:
+def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_scale=None, group_offsets=None,
+                 n_groups=0, rows_per_group_hint=None) -> bool:
+    """The paired (two-SM) tcgen05 kernel for products with many tokens, dense or grouped (see
+    gemm_tc_pair.cu).  Returns False, having launched nothing, when the product is outside what it takes."""
+    grouped = group_offsets is not None
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.dim() != 2 or w.dim() != (3 if grouped else 2):
         return False
     if a.stride(1) != 1 or not w.is_contiguous() or out.stride(-1) != 1:
         return False
-    T, K = a.shape
-    rows_w = w.shape[0]
+    K = a.shape[1]
+    T = m_rows if m_rows is not None else a.shape[0]
+    rows_w = w.shape[-2]
     N = rows_w // 2 if mode == MODE_SWIGLU else rows_w
-    if w.shape[1] != K or out.shape[1] != N or a.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+    if w.shape[-1] != K or out.shape[1] != N or a.stride(0) % 8 or a.data_ptr() % 16 or w.data_ptr() % 16:
+        return False
+    if grouped and w.shape[0] != n_groups:
         return False
     if (mode == MODE_SWIGLU and out.dtype != torch.bfloat16) or (mode == MODE_ADD and out.dtype != torch.float32):
         return False
-    bn = load().cpi_gemm_tc_pair_plan(c_int(T), c_int(N), c_int(K), c_int(int(mode == MODE_SWIGLU)))
+    bn = load().cpi_gemm_tc_pair_plan(c_int(T), c_int(N), c_int(K), c_int(int(mode == MODE_SWIGLU)),
+                                      c_int(n_groups if grouped else 0))
     if bn <= 0:
         return False
-    _need_cuda(a, w, out, row_scale)
+    _need_cuda(a, w, out, out_rows, row_scale, group_offsets)
     _call("cpi_gemm_tc_pair", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
-          c_long(out.stride(0)), _p(row_scale), c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn),
-          _p(tc_error_flag(a.device)), _stream())
+          c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
+          c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn), _p(tc_error_flag(a.device)), _stream())
     return True
 
 

@@ -21,8 +21,10 @@ use_paired_kernel = True
 def project(a, w, out, mode=MODE_STORE, **kw):
     """Dense or grouped projection; see csrc/lib.py: gemm_simt for the keyword arguments."""
     if use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        plain = not (set(kw) - {"row_scale"})          # no groups, gather or scatter
-        if use_paired_kernel and plain and a.shape[0] >= 512 and K.gemm_tc_pair(a, w, out, mode, **kw):
+        # dense products with many tokens go to the two-SM kernel; for the routed experts it measured no
+        # faster than the single-CTA kernel (both wait on memory latency there), so they stay on that one
+        dense = "a_rows" not in kw and "group_offsets" not in kw
+        if use_paired_kernel and dense and a.shape[0] >= 512 and K.gemm_tc_pair(a, w, out, mode, **kw):
             return
         if K.gemm_tc(a, w, out, mode, **kw):
             return

@@ -142,6 +142,35 @@ def test_gemm_tensor_core_pair_kernel(T, N, Kd, mode):
         assert not K().gemm_tc_pair(a, wn, out[:, : N - 128], mode)         # features no multiple of 256
 
 
+@pytest.mark.parametrize("counts", [[300, 0, 129, 83], [128, 128, 128, 128, 1, 255, 256, 0]])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gemm_tensor_core_pair_kernel_grouped(counts, mode):
+    G, N, Kd = len(counts), 512, 320
+    M = sum(counts)
+    w = rnd(G, 2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=1, scale=Kd ** -0.5)
+    a = rnd(M, Kd, dtype=torch.bfloat16)
+    scale = rnd(M, seed=4).abs()
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    grp = torch.repeat_interleave(torch.arange(G), torch.tensor(counts)).to(DEV)
+    acc = torch.einsum("mk,mnk->mn", a.float(), w.float()[grp]) * scale[:, None]
+    if mode == 1:
+        out_rows = torch.randperm(M + 10)[:M].to(torch.int32).to(DEV)
+        out = rnd(M + 10, N, seed=7)
+        ref = out.clone()
+        ref[out_rows.long()] += acc
+    elif mode == 2:
+        out_rows, out = None, torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        g_, u_ = acc[:, :N], acc[:, N:]
+        ref = g_ / (1 + torch.exp(-g_)) * u_
+    else:
+        out_rows, out, ref = None, torch.zeros(M, N, device=DEV), acc
+    assert K().gemm_tc_pair(a, w, out, mode, m_rows=M, out_rows=out_rows, row_scale=scale, group_offsets=offs, n_groups=G)
+    torch.cuda.synchronize()
+    assert int(K().tc_error_flag(DEV)) == 0
+    tol = (1e-2 if mode == 2 else 2e-5) * max(1.0, float(ref.abs().max()))
+    assert float((out.float() - ref).abs().max()) <= tol
+
+
 def test_gemm_tensor_core_refuses_what_it_cannot_take():
     a, w = rnd(4, 36, dtype=torch.bfloat16), rnd(128, 36, dtype=torch.bfloat16)
     out = torch.empty(4, 128, dtype=torch.bfloat16, device=DEV)
