@@ -5,9 +5,12 @@
 // warp 5 issues the MMAs; warps 0-3 are the softmax: thread r owns query row r, so row maxima and sums
 // need no shuffles.  Per key tile:
 //     S = Q K^T            tcgen05.mma, both operands K-major from shared memory, S in tensor memory
+//                          (two S buffers: the MMAs run two tiles ahead of the softmax)
 //     P = 2^(S*c - m)      read S with tcgen05.ld, mask by position, write P as bf16 into shared memory
-//     O_tile = P V         tcgen05.mma, V consumed MN-major straight from the page layout [position][dim]
-//     O = O * alpha + O_tile   in registers (thread r keeps its output row in float32)
+//     O += P V             tcgen05.mma accumulating in tensor memory, V consumed MN-major straight from
+//                          the page layout [position][dim]
+// m is a reference maximum that is raised, and O rescaled in tensor memory, only when the row maximum
+// has outgrown it by 2^8; the division by the row sum comes once, at the end.
 // Masks: key position <= query position, and >= the window's low end (chunk or sliding window).  The
 // last tile's value rows beyond the newest position are zeroed in shared memory, so stale page contents
 // cannot reach the product (0 * NaN).  Formulas: src/engine/llama4_cpu_engine.cpp:195-250; the
@@ -116,6 +119,28 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// Exponentials are taken against a reference maximum that is only raised when the true row maximum has
+// outgrown it by more than this many powers of two; the accumulated output then needs rescaling only
+// then (rarely after the first tiles), and intermediate values stay below 2^kRescaleSlack.
+constexpr float kRescaleSlack = 8.0f;
+
 template <int D>
 __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                 const __grid_constant__ CUtensorMap map_k,
@@ -124,18 +149,18 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
   constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows x 128 bytes
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES;
   constexpr uint32_t KV_BYTES = HALVES * HALF_BYTES;   // one of K or V, 128 positions
-  constexpr uint32_t P_BYTES = 2 * HALF_BYTES;         // 128 rows x 128 keys
-  constexpr uint32_t TMEM_COLS = 256;                  // S: 128 columns, O tile: D columns
+  constexpr uint32_t TMEM_COLS = 512;                  // S twice (128 columns each), then O (D columns)
   extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full, p_full, o_full;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_full;
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
-  uint8_t* kv_s = q_s + Q_BYTES;                       // [stage][K | V]
-  uint8_t* p_s = kv_s + 2 * 2 * KV_BYTES;
+  uint8_t* k_s = q_s + Q_BYTES;                        // [2 stages]
+  uint8_t* v_s = k_s + 2 * KV_BYTES;                   // [2 stages]
+  uint8_t* p_s = v_s + 2 * KV_BYTES;
 
   pdl_launch_dependents();
   pdl_wait();
@@ -150,8 +175,12 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
 
   if (tid == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(&s_full, 1); mbar_init(&p_full, 128); mbar_init(&o_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+    }
+    mbar_init(&p_full, 128); mbar_init(&o_full, 1);
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -162,102 +191,107 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
-  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256;
   volatile int* abort_flag = &abort_s;
   bool ok = true;
 
   if (warp == 4) {
     if (lane == 0) {
-      // ---- TMA producer ----
+      // ---- TMA producer: keys and values have barriers of their own, so that the keys of tile i+2 can
+      //      come as soon as Q K^T of tile i is done, long before its P V ----
       mbar_expect_tx(&q_full, Q_BYTES);
       for (int h = 0; h < HALVES; ++h) tma_load_2d(q_s + h * HALF_BYTES, &map_q, &q_full, head * D + h * 64, tok0);
       const int* table = p.page_table + (size_t)slot * p.max_blocks;
       const int last_block = pos_last / PAGE;
       for (int i = 0; i < n_kt; ++i) {
         const int s = i & 1;
-        if (i >= 2 && !mbar_wait(&kv_empty[s], ((i >> 1) - 1) & 1, abort_flag)) break;
-        uint8_t* ks = kv_s + (size_t)s * 2 * KV_BYTES;
-        uint8_t* vs = ks + KV_BYTES;
         const int blk0 = (kt_begin + i) * (BKV / PAGE);
         const int n_pages = min(BKV / PAGE, last_block - blk0 + 1);
-        mbar_expect_tx(&kv_full[s], (uint32_t)n_pages * 2u * HALVES * (PAGE * 128));
+        const uint32_t bytes = (uint32_t)n_pages * HALVES * (PAGE * 128);
+        if (i >= 2 && !mbar_wait(&k_empty[s], ((i >> 1) - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(&k_full[s], bytes);
         for (int pg = 0; pg < n_pages; ++pg) {
           const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
-          for (int h = 0; h < HALVES; ++h) {
-            tma_load_2d(ks + h * HALF_BYTES + pg * (PAGE * 128), &map_k, &kv_full[s], h * 64, row);
-            tma_load_2d(vs + h * HALF_BYTES + pg * (PAGE * 128), &map_v, &kv_full[s], h * 64, row);
-          }
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(k_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_k, &k_full[s], h * 64, row);
+        }
+        if (i >= 2 && !mbar_wait(&v_empty[s], ((i >> 1) - 1) & 1, abort_flag)) break;
+        mbar_expect_tx(&v_full[s], bytes);
+        for (int pg = 0; pg < n_pages; ++pg) {
+          const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
+          for (int h = 0; h < HALVES; ++h)
+            tma_load_2d(v_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_v, &v_full[s], h * 64, row);
         }
       }
     }
   } else if (warp == 5) {
     if (lane == 0) {
-      // ---- MMA issuer ----
+      // ---- MMA issuer.  Order: S(0), S(1), then for each tile  O += P V,  S(i+2).  The two S buffers let
+      //      Q K^T run two tiles ahead of the softmax; the tensor pipe executes in issue order. ----
       constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0);
       constexpr uint32_t idesc_o = instr_desc(BQ, D, 1);
-      ok = mbar_wait(&q_full, 0, abort_flag);
-      for (int i = 0; i < n_kt && ok; ++i) {
+      auto issue_qk = [&](int i) -> bool {
         const int s = i & 1;
-        ok = mbar_wait(&kv_full[s], (i >> 1) & 1, abort_flag);
-        if (!ok) break;
+        if (!mbar_wait(&k_full[s], (i >> 1) & 1, abort_flag)) return false;
         fence_after_sync();
-        const uint32_t qa = smem_u32(q_s), ka = smem_u32(kv_s + (size_t)s * 2 * KV_BYTES), va = ka + KV_BYTES;
+        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * KV_BYTES);
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
           const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_bf16(tmem_s, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, ks > 0);
+          umma_bf16(tmem_s + s * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, ks > 0);
         }
-        umma_commit(&s_full);
-        ok = mbar_wait(&p_full, i & 1, abort_flag);
+        umma_commit(&s_full[s]);
+        umma_commit(&k_empty[s]);
+        return true;
+      };
+      ok = mbar_wait(&q_full, 0, abort_flag);
+      ok = ok && issue_qk(0);
+      if (ok && n_kt > 1) ok = issue_qk(1);
+      for (int i = 0; i < n_kt && ok; ++i) {
+        const int s = i & 1;
+        ok = mbar_wait(&p_full, i & 1, abort_flag) && mbar_wait(&v_full[s], (i >> 1) & 1, abort_flag);
         if (!ok) break;
         fence_after_sync();
-        const uint32_t pa = smem_u32(p_s);
+        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * KV_BYTES);
 #pragma unroll
         for (int j = 0; j < BKV / 16; ++j) {
           const uint32_t poff = (j >> 2) * HALF_BYTES + (j & 3) * 32;
-          umma_bf16(tmem_o, smem_desc(pa + poff, 16, 1024), smem_desc(va + j * 2048, HALF_BYTES, 1024), idesc_o, j > 0);
+          umma_bf16(tmem_o, smem_desc(pa + poff, 16, 1024), smem_desc(va + j * 2048, HALF_BYTES, 1024), idesc_o,
+                    (i > 0 || j > 0) ? 1u : 0u);
         }
         umma_commit(&o_full);
-        umma_commit(&kv_empty[s]);
+        umma_commit(&v_empty[s]);
+        if (i + 2 < n_kt) ok = issue_qk(i + 2);        // S[s] is free: the softmax of tile i has read it
       }
     }
   } else {
-    // ---- softmax: thread `row` owns one query row ----
+    // ---- softmax: thread `row` owns one query row; O stays in tensor memory ----
     const int row = tid;
     const bool live = row < rows;
     const int qp = live ? p.token_pos[tok0 + row] : -1;
     const int lo = live ? window_low(p.window_kind, p.window_size, qp) : 0;
     const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    float m_run = -1e30f, l_run = 0.f;
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
+    float m_ref = -1e30f, l_run = 0.f;                  // reference maximum of the exponentials, row sum
 
+    const int lo_last = window_low(p.window_kind, p.window_size, pos_last);
     for (int i = 0; i < n_kt && ok; ++i) {
       const int key0 = (kt_begin + i) * BKV;
-      ok = mbar_wait(&s_full, i & 1, abort_flag);
+      const uint32_t s_addr = tmem_s + (i & 1) * 128 + lane_addr;
+      // (the tensor-memory loads and the vote below are warp-wide: a warp gives up as a whole)
+      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag));
       if (!ok) break;
-      fence_after_sync();
-      // pass 1: row maximum
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_addr + c, v);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int kp = key0 + c + e;
-          if (kp <= qp && kp >= lo) mx = fmaxf(mx, v[e] * p.scale_log2);
-        }
+      // P V of the previous tile must be done before P is overwritten and before O may be rescaled
+      if (i > 0) {
+        ok = __all_sync(0xffffffffu, mbar_wait(&o_full, (i - 1) & 1, abort_flag));
+        if (!ok) break;
       }
-      const float m_new = fmaxf(m_run, mx);
-      const float alpha = exp2f(m_run - m_new);
-      m_run = m_new;
+      fence_after_sync();
       // the last tile: zero the value rows beyond the newest position (this thread: key row `row`)
       if (i == n_kt - 1) {
-        ok = mbar_wait(&kv_full[i & 1], (i >> 1) & 1, abort_flag);
-        if (ok && key0 + row > pos_last) {
-          uint8_t* vs = kv_s + (size_t)(i & 1) * 2 * KV_BYTES + KV_BYTES;
+        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[i & 1], (i >> 1) & 1, abort_flag));
+        if (!ok) break;
+        if (key0 + row > pos_last) {
+          uint8_t* vs = v_s + (i & 1) * KV_BYTES;
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
             uint4* r4 = reinterpret_cast<uint4*>(vs + h * HALF_BYTES + row * 128);
@@ -266,55 +300,95 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
           }
         }
       }
-      // pass 2: P = 2^(s - m) as bf16 into shared memory (K-major, swizzled), row sum
-      float ls = 0.f;
+      // One pass over S: P = 2^(s - m_ref) as bf16 into shared memory (K-major, swizzled), the row sum, and
+      // the row maximum.  A tile that lies wholly inside every row's window needs no position tests.
+      const bool no_mask = key0 + BKV - 1 <= pos_first && key0 >= lo_last;
+      float mx, ls;
+      auto pass = [&](const float ref) {
+        mx = -INFINITY;
+        ls = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < BKV; c += 32) {
-        float v[32];
-        tmem_ld32(tmem_s + lane_addr + c, v);
+        for (int c = 0; c < BKV; c += 32) {
+          float v[32];
+          tmem_ld32(s_addr + c, v);
+          if (no_mask) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int kp = key0 + c + e;
-          const float pe = (kp <= qp && kp >= lo) ? exp2f(v[e] * p.scale_log2 - m_new) : 0.f;
-          v[e] = pe;
-          ls += pe;
-        }
+            for (int e = 0; e < 32; ++e) {
+              const float x = v[e] * p.scale_log2;
+              mx = fmaxf(mx, x);
+              v[e] = exp2f(x - ref);
+              ls += v[e];
+            }
+          } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int col = c + g * 8;
-          const int chunk = (col & 63) >> 3;
-          uint4 w = make_uint4(pack_bf16(v[g * 8], v[g * 8 + 1]), pack_bf16(v[g * 8 + 2], v[g * 8 + 3]),
-                               pack_bf16(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16(v[g * 8 + 6], v[g * 8 + 7]));
-          *reinterpret_cast<uint4*>(p_s + (col >> 6) * HALF_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = w;
+            for (int e = 0; e < 32; ++e) {
+              const int kp = key0 + c + e;
+              const bool in = kp <= qp && kp >= lo;
+              const float x = v[e] * p.scale_log2;
+              if (in) mx = fmaxf(mx, x);
+              v[e] = in ? exp2f(x - ref) : 0.f;
+              ls += v[e];
+            }
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = c + g * 8;
+            const int chunk = (col & 63) >> 3;
+            uint4 w = make_uint4(pack_bf16(v[g * 8], v[g * 8 + 1]), pack_bf16(v[g * 8 + 2], v[g * 8 + 3]),
+                                 pack_bf16(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16(v[g * 8 + 6], v[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(p_s + (col >> 6) * HALF_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = w;
+          }
         }
+      };
+      // Optimistic: against the reference maximum the row already has.  Only if some row of the warp has
+      // outgrown its reference (always on its first tile) is the reference raised, O rescaled in tensor
+      // memory, and the pass repeated.  (Load and store of tensor memory are warp-wide: every lane takes
+      // part, with factor 1 where nothing changes.)
+      pass(m_ref);
+      const bool grow = mx > m_ref + (m_ref < -1e29f ? 0.f : kRescaleSlack);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx : m_ref;
+        const float f = exp2f(m_ref - m_new);
+        if (i > 0) {
+#pragma unroll 1
+          for (int c = 0; c < D; c += 32) {
+            float v[32];
+            tmem_ld32(tmem_o + lane_addr + c, v);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] *= f;
+            tmem_st32(tmem_o + lane_addr + c, v);
+          }
+        }
+        l_run *= f;
+        m_ref = m_new;
+        pass(m_ref);
       }
-      l_run = l_run * alpha + ls;
+      l_run += ls;
       fence_async_proxy();
       fence_before_sync();
       mbar_arrive(&p_full);
-      // O = O * alpha + P V
-      ok = ok && mbar_wait(&o_full, i & 1, abort_flag);
-      if (!ok) break;
-      fence_after_sync();
-#pragma unroll
+    }
+    // the output: O / l once the last P V is done
+    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_full, (n_kt - 1) & 1, abort_flag));
+    fence_after_sync();
+    if (ok) {
+      const float inv = 1.0f / fmaxf(l_run, 1e-20f);
+      __nv_bfloat16* dst = p.out + ((size_t)(tok0 + row) * p.n_heads + head) * D;
+#pragma unroll 1
       for (int c = 0; c < D; c += 32) {
         float v[32];
         tmem_ld32(tmem_o + lane_addr + c, v);
+        if (live) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) o[c + e] = o[c + e] * alpha + v[e];
-      }
-      fence_before_sync();
-    }
-    if (ok && live) {
-      const float inv = 1.0f / fmaxf(l_run, 1e-20f);
-      __nv_bfloat16* dst = p.out + ((size_t)(tok0 + row) * p.n_heads + head) * D;
-#pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        uint4 w = make_uint4(pack_bf16(o[c] * inv, o[c + 1] * inv), pack_bf16(o[c + 2] * inv, o[c + 3] * inv),
-                             pack_bf16(o[c + 4] * inv, o[c + 5] * inv), pack_bf16(o[c + 6] * inv, o[c + 7] * inv));
-        *reinterpret_cast<uint4*>(dst + c) = w;
+          for (int e = 0; e < 32; e += 8) {
+            uint4 w = make_uint4(pack_bf16(v[e] * inv, v[e + 1] * inv), pack_bf16(v[e + 2] * inv, v[e + 3] * inv),
+                                 pack_bf16(v[e + 4] * inv, v[e + 5] * inv), pack_bf16(v[e + 6] * inv, v[e + 7] * inv));
+            *reinterpret_cast<uint4*>(dst + c + e) = w;
+          }
+        }
       }
     }
+    fence_before_sync();
   }
   if (abort_s) {
     if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 2);
