@@ -11,53 +11,99 @@ namespace cpi {
 
 constexpr int kMaxExperts = 256;
 
-// One block per (expert, token): its threads stride over the hidden axis, then a fixed-order block sum.
+// Router logit = sum over the hidden axis of x * w, float32, in ONE fixed order whichever kernel computes
+// it: thread i of 128 adds, element by element, the groups of 8 consecutive elements number i, i + 128,
+// i + 256, ...; each thread's sum goes through the warp tree, and the four warp results are added in
+// order.  Groups of 8 let every load be 16 bytes (two for float32).
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+// the 8 elements of group `g` (zeros beyond `hidden`); `vec`: rows are 16-byte aligned and hidden % 8 == 0
+template <typename T> __device__ __forceinline__ void load_group(const T* row, int g, int hidden, bool vec, float (&v)[8]) {
+  if (vec) { load8<T>(row + 8 * g, v); return; }
+#pragma unroll
+  for (int u = 0; u < 8; ++u) v[u] = 8 * g + u < hidden ? to_f32(row[8 * g + u]) : 0.f;
+}
+
+// One block per (expert, token) -- for a handful of tokens.
 template <typename TH, typename TW>
 __global__ void __launch_bounds__(128)
 router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
-                     float* __restrict__ logits, int hidden, int n_experts) {
+                     float* __restrict__ logits, int hidden, int n_experts, int vec) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ float scratch[32];
   const int e = blockIdx.x, t = blockIdx.y;
   const TH* x = h + (size_t)t * h_stride;
   const TW* wr = w + (size_t)e * hidden;
+  const int groups = (hidden + 7) / 8;
   float s = 0.f;
-#pragma unroll 8
-  for (int i = threadIdx.x; i < hidden; i += 128) s = fmaf(to_f32(x[i]), to_f32(wr[i]), s);
+  for (int g = threadIdx.x; g < groups; g += 128) {
+    float xv[8], wv[8];
+    load_group<TH>(x, g, hidden, vec, xv);
+    load_group<TW>(wr, g, hidden, vec, wv);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s = fmaf(xv[u], wv[u], s);
+  }
   s = block_sum(s, scratch);
   if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = s;
 }
 
-// The same sums for many tokens: one block per token keeps the token's row in registers and visits the
-// experts one after the other.  Thread i again sums elements i, i + 128, ... and the block sum is the
-// same, so a logit has the same bits whichever of the two kernels computed it.
-template <typename TH, typename TW>
+// A block takes TOK tokens and EXP experts at a time -- for many tokens: every loaded activation is used
+// EXP times and every loaded weight TOK times.  Same order of additions as above, so the same bits.
+template <typename TH, typename TW, int TOK, int EXP>
 __global__ void __launch_bounds__(128)
-router_logits_rows_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
-                          float* __restrict__ logits, int hidden, int n_experts) {
+router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
+                          float* __restrict__ logits, int n_tokens, int hidden, int n_experts, int vec) {
   pdl_launch_dependents();
   pdl_wait();
-  __shared__ float scratch[32];
-  constexpr int PER = 64;                             // up to 8192 hidden elements in registers
-  const int t = blockIdx.x;
-  const TH* x = h + (size_t)t * h_stride;
-  float xv[PER];
+  __shared__ float part[4][TOK * EXP];
+  const int t0 = blockIdx.x * TOK, e0 = blockIdx.y * EXP;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int groups = (hidden + 7) / 8;
+  float acc[TOK][EXP];
 #pragma unroll
-  for (int j = 0; j < PER; ++j) {
-    const int i = threadIdx.x + j * 128;
-    xv[j] = i < hidden ? to_f32(x[i]) : 0.f;
+  for (int a = 0; a < TOK; ++a)
+#pragma unroll
+    for (int b = 0; b < EXP; ++b) acc[a][b] = 0.f;
+  for (int g = threadIdx.x; g < groups; g += 128) {
+    float xv[TOK][8], wv[EXP][8];
+#pragma unroll
+    for (int a = 0; a < TOK; ++a)            // rows beyond the end repeat the last one; they are not stored
+      load_group<TH>(h + (size_t)min(t0 + a, n_tokens - 1) * h_stride, g, hidden, vec, xv[a]);
+#pragma unroll
+    for (int b = 0; b < EXP; ++b)
+      load_group<TW>(w + (size_t)min(e0 + b, n_experts - 1) * hidden, g, hidden, vec, wv[b]);
+#pragma unroll
+    for (int a = 0; a < TOK; ++a)
+#pragma unroll
+      for (int b = 0; b < EXP; ++b)
+#pragma unroll
+        for (int u = 0; u < 8; ++u) acc[a][b] = fmaf(xv[a][u], wv[b][u], acc[a][b]);
   }
-  for (int e = 0; e < n_experts; ++e) {
-    const TW* wr = w + (size_t)e * hidden;
-    float s = 0.f;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-      const int i = threadIdx.x + j * 128;
-      if (i < hidden) s = fmaf(xv[j], to_f32(wr[i]), s);
+  for (int a = 0; a < TOK; ++a)
+#pragma unroll
+    for (int b = 0; b < EXP; ++b) {
+      const float v = warp_sum(acc[a][b]);
+      if (lane == 0) part[warp][a * EXP + b] = v;
     }
-    s = block_sum(s, scratch);
-    if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = s;
+  __syncthreads();
+  for (int k = threadIdx.x; k < TOK * EXP; k += 128) {
+    const int a = k / EXP, b = k % EXP;
+    if (t0 + a < n_tokens && e0 + b < n_experts) {
+      float r = 0.f;
+      for (int wq = 0; wq < 4; ++wq) r += part[wq][k];
+      logits[(size_t)(t0 + a) * n_experts + e0 + b] = r;
+    }
   }
 }
 
@@ -161,13 +207,18 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
   CPI_REQUIRE(top_k >= 1 && top_k <= n_experts, "router: top-k %d of %d experts", top_k, n_experts);
   CPI_REQUIRE(logits != nullptr, "router: the logits buffer is missing");
   CPI_REQUIRE(n_tokens <= 65535, "router: too many tokens in one launch (%d)", n_tokens);
-  if (n_tokens >= 128 && hidden <= 64 * 128) {
+  const int esz_h = h_dtype == kF32 ? 4 : 2, esz_w = w_dtype == kF32 ? 4 : 2;
+  const int vec = hidden % 8 == 0 && (h_stride * esz_h) % 16 == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 &&
+                  ((long)hidden * esz_w) % 16 == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0;
+  if (n_tokens >= 64) {
+    constexpr int TOK = 4, EXP = 4;
+    dim3 grid((n_tokens + TOK - 1) / TOK, (n_experts + EXP - 1) / EXP);
     CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-        (cpi::launch_pdl(router_logits_rows_kernel<TH, TW>, n_tokens, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
+        (cpi::launch_pdl(router_logits_tile_kernel<TH, TW, TOK, EXP>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, n_tokens, hidden, n_experts, vec))));
   } else {
     dim3 grid(n_experts, n_tokens);
     CPI_DISPATCH_DTYPE(h_dtype, TH, CPI_DISPATCH_DTYPE(w_dtype, TW,
-        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts))));
+        (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts, vec))));
   }
   if (check_launch("router_logits")) return 2;
   cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
