@@ -242,3 +242,41 @@ def test_long_context_across_the_chunk_boundary_both_kernel_families_agree():
     print(f"long context: tensor-core vs general kernels, worst relative difference {err:.3e}")
     assert err <= 3e-2
     assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.9
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_scout_layer_sizes_against_plain(dtype):
+    """The layer sizes that the benchmark runs (width 5120, 40 / 8 heads of 128, experts of 8192, llama3
+    scaling, chunk and temperature floor 8192) in two layers (one with rotation, one without), with three
+    experts and a vocabulary that is no multiple of anything: an unequal batch, then decoding."""
+    import shutil
+    cfg = {
+        "architectures": ["Llama4ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 5120,
+        "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192,
+        "intermediate_size_mlp": 16384, "num_local_experts": 3, "num_experts_per_tok": 1,
+        "interleave_moe_layer_step": 1, "vocab_size": 20011, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                         "original_max_position_embeddings": 8192},
+        "nope_layer_interval": 2, "attention_chunk_size": 8192, "use_qk_norm": True,
+        "attn_temperature_tuning": True, "floor_scale": 8192, "attn_scale": 0.1,
+        "tie_word_embeddings": False, "initializer_range": 0.02,
+    }
+    from cpi_b200.engine import Engine
+    if "scout" not in _dirs:
+        _dirs["scout"] = tiny.make_model_dir(cfg, seed=11)
+    d = _dirs["scout"]
+    try:
+        e = Engine.from_model_dir(d, dtype=dtype, max_tokens=256)
+        reqs = {"a": tiny.random_tokens(70 + 6, 20011, 1), "b": tiny.random_tokens(33 + 6, 20011, 2)}
+        rp = Replay(e)
+        rp.step([("a", reqs["a"][:70], [0, 1, 68, 69]), ("b", reqs["b"][:33], [32])])
+        for i in range(6):
+            rp.step([("a", [reqs["a"][70 + i]], [0]), ("b", [reqs["b"][33 + i]], [0])])
+        rp.end("a")
+        rp.end("b")
+        worst = compare_with_plain(d, reqs, rp, dtype)
+        print(f"scout layer sizes, {dtype}: worst relative error {worst:.3e}")
+        del e
+    finally:
+        if dtype == "bfloat16":
+            shutil.rmtree(_dirs.pop("scout"), ignore_errors=True)
