@@ -248,20 +248,51 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
   }
 }
 
-// out[t, h, :] = sum_s w_s O_s / sum_s w_s l_s,  w_s = 2^(m_s - max m)
+// out[t, h, :] = sum_s w_s O_s / sum_s w_s l_s,  w_s = 2^(m_s - max m); at most kMaxSplits splits.
+// The weights are computed once, in parallel, and the sum over splits keeps eight loads in flight.
+constexpr int kMaxSplits = 256;
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int n_splits, int D) {
+  __shared__ float w_s[kMaxSplits], wl_s[kMaxSplits], red_s[4];
   pdl_launch_dependents();
   pdl_wait();
   const size_t th = blockIdx.x;
-  float M = -1e30f;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(th * n_splits + s) * 2]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.f, L = 0.f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float f = exp2f(part_ml[(th * n_splits + s) * 2] - M);
-      acc += f * part_o[(th * n_splits + s) * D + d];
-      L += f * part_ml[(th * n_splits + s) * 2 + 1];
+  const int tid = threadIdx.x, n_warps = blockDim.x >> 5;
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + th * n_splits;
+  float2 mine[kMaxSplits / 64];                       // blockDim.x >= 64
+  float m = -1e30f;
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / 64; ++j) {
+    const int s = tid + j * blockDim.x;
+    mine[j] = s < n_splits ? ml[s] : make_float2(-1e30f, 0.f);
+    m = fmaxf(m, mine[j].x);
+  }
+  m = warp_max(m);
+  if ((tid & 31) == 0) red_s[tid >> 5] = m;
+  __syncthreads();
+  float M = red_s[0];
+  for (int w = 1; w < n_warps; ++w) M = fmaxf(M, red_s[w]);
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / 64; ++j) {
+    const int s = tid + j * blockDim.x;
+    if (s < n_splits) {
+      const float f = exp2f(mine[j].x - M);
+      w_s[s] = f;
+      wl_s[s] = f * mine[j].y;
+    }
+  }
+  __syncthreads();
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += wl_s[s];
+  const float* po = part_o + th * n_splits * D;
+  for (int d = tid; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = s0 + j < n_splits ? po[(size_t)(s0 + j) * D + d] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (s0 + j < n_splits) acc += w_s[s0 + j] * v[j];
     }
     out[th * D + d] = __float2bfloat16_rn(acc / fmaxf(L, 1e-20f));
   }
@@ -289,7 +320,7 @@ extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cach
   CPI_REQUIRE(cpi_attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_decode: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention_decode: window kind %d needs a size > 0", window_kind);
-  CPI_REQUIRE(n_splits >= 1 && n_splits <= 65535 && n_tokens <= 65535, "attention_decode: bad grid (%d splits, %d tokens)", n_splits, n_tokens);
+  CPI_REQUIRE(n_splits >= 1 && n_splits <= dec::kMaxSplits && n_tokens <= 65535, "attention_decode: bad grid (%d splits of at most %d, %d tokens)", n_splits, dec::kMaxSplits, n_tokens);
   CPI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split scratch is missing");
   dec::Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                 page_table, max_blocks, token_seq, token_pos, seq_slot, n_heads, n_kv_heads, window_kind, window_size,

@@ -16,11 +16,15 @@
 // accumulators: rows n and N + n of W; out = silu(g) * u).  Optional per-token scale, output row
 // scatter, and groups (routed experts): tokens [offsets[g], offsets[g+1]) use W[g].
 //
-// Split-K: when a launch has too few tiles to fill the GPU, the k range is cut into `splits` parts.
-// Each CTA stores its raw accumulators into `partials`; the CTA that takes the last ticket of a tile
-// sums the parts in split order (a fixed order: the result does not depend on arrival order), applies
-// the epilogue and resets the ticket.  `partials` and `tickets` are scratch the caller provides;
-// tickets must be zero before the first launch and are left zero.
+// Split-K: when a launch has too few tiles to fill the GPU, the k range is cut into `splits` parts,
+// summed in split order (a fixed order: the result does not depend on arrival order).  Two ways:
+//  * cluster (up to 8 splits, token tiles up to 128): the CTAs of a tile form a thread-block cluster
+//    along z.  Each puts its raw accumulators into its own shared memory; after a cluster barrier every
+//    CTA sums a share of the tile's columns over all CTAs' shared memory (distributed shared memory
+//    loads) and applies the epilogue to them.  No global scratch, and the merge runs in parallel.
+//  * tickets: each CTA stores its raw accumulators into `partials`; the CTA that takes the last ticket
+//    of a tile sums the parts, applies the epilogue and resets the ticket.  `partials` and `tickets`
+//    are scratch the caller provides; tickets must be zero before the first launch and are left zero.
 //
 // Every mbarrier wait is bounded: when it runs out the CTA raises `*error_flag`, stops issuing work,
 // lets copies in flight land, frees its tensor memory and returns.
@@ -52,6 +56,7 @@ struct Params {
   int k_tiles;         // ceil(K / 64)
   int splits, k_tiles_per_split;
   float* partials; int* tickets;
+  int cluster_split;   // 1: the splits of a tile are one cluster along z and merge through shared memory
   int* error_flag;
 };
 
@@ -119,6 +124,20 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
   for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -298,8 +317,9 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     }
   };
 
-  if (ok && p.splits == 1) {
-    if (MODE == kAdd) {
+  if (p.splits == 1) {
+    if (!ok) {
+    } else if (MODE == kAdd) {
       // read-modify-write of the residual: the old values of chunk c+1 are fetched while chunk c is added,
       // so that their latency hides behind the tensor-memory load
       const bool row_ok = n < p.N;
@@ -341,6 +361,56 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 #pragma unroll
         for (int j = 0; j < 16; ++j) emit(c + j, v[j], ACC == 2 ? u[j] : 0.f);
       }
+    }
+  } else if (p.cluster_split) {
+    // Every thread of every CTA of the cluster passes both barriers, whether its own waits held or not.
+    if constexpr (BN <= 128) {
+      static_assert((size_t)ACC * BN * BM * 4 <= (size_t)STAGES * STAGE_BYTES, "the stages must hold a tile of floats");
+      float* red = reinterpret_cast<float*>(smem);        // [acc][col][row]; the stages are idle by now
+      if (ok) {
+#pragma unroll 1
+        for (int a = 0; a < ACC; ++a)
+#pragma unroll 1
+          for (int c = 0; c < n_cols; c += 16) {
+            float v[16];
+            tmem_ld16(lane_addr + a * BN + c, v);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) red[((size_t)a * BN + c + j) * BM + row] = v[j];
+          }
+      }
+      cluster_sync();
+      if (ok) {
+        const int rank = (int)cluster_rank();
+        const uint32_t mine = smem_u32(red + row);
+        uint32_t peer[8];
+#pragma unroll
+        for (int z = 0; z < 8; ++z) peer[z] = map_to_cta(mine, z < p.splits ? z : 0);
+        // this CTA's share: columns 4 rank .. 4 rank + 3, then every (4 splits)-th group of four
+#pragma unroll 1
+        for (int c0 = 4 * rank; c0 < n_valid_t; c0 += 4 * p.splits) {
+          float sum[ACC][4];
+#pragma unroll
+          for (int a = 0; a < ACC; ++a) {
+            float part[4][8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+              for (int z = 0; z < 8; ++z)
+                part[j][z] = (z < p.splits && c0 + j < n_valid_t)
+                                 ? ld_cluster_f32(peer[z] + (uint32_t)(((size_t)a * BN + c0 + j) * BM * 4)) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float t = 0.f;
+#pragma unroll
+              for (int z = 0; z < 8; ++z) if (z < p.splits) t += part[j][z];
+              sum[a][j] = t;
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) emit(c0 + j, sum[0][j], sum[ACC - 1][j]);
+        }
+      }
+      cluster_sync();                                     // nobody leaves while its shared memory is being read
     }
   } else if (ok) {
     // raw accumulators -> partials[tile][split][acc][col][row]
@@ -475,34 +545,124 @@ int get_map_3d_bf16(const void* ptr, uint64_t inner, uint64_t rows, uint64_t gro
 }
 
 template <int BN, int MODE, typename TO>
-static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
-  constexpr int ACC = MODE == kSwiglu ? 2 : 1;
-  constexpr int STAGE = ACC * BM * BK * 2 + BN * BK * 2;
-  constexpr int BUDGET = BN <= 32 ? 108 * 1024 : 196 * 1024;    // two CTAs per SM for narrow token tiles
-  constexpr int S0 = BUDGET / STAGE;
-  constexpr int STAGES = S0 > 8 ? 8 : (S0 < 2 ? 2 : S0);
-  constexpr int SMEM = STAGES * STAGE + 1024;
-  auto kern = gemm_tc_kernel<BN, MODE, TO, STAGES>;
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
-      set_error("gemm_tc: cannot reserve %d bytes of shared memory", SMEM);
-      return 1;
+struct Variant {
+  static constexpr int ACC = MODE == kSwiglu ? 2 : 1;
+  static constexpr int STAGE = ACC * BM * BK * 2 + BN * BK * 2;
+  // two CTAs per SM where the stages stay deep enough: one's epilogue then runs under the other's loads
+  static constexpr int BUDGET = (BN <= 32 || (BN == 64 && ACC == 1)) ? 108 * 1024 : 196 * 1024;
+  static constexpr int S0 = BUDGET / STAGE;
+  static constexpr int STAGES = S0 > 8 ? 8 : (S0 < 2 ? 2 : S0);
+  static constexpr int SMEM = STAGES * STAGE + 1024;
+  using Kernel = void (*)(const CUtensorMap, const CUtensorMap, Params);
+  static Kernel kernel() { return gemm_tc_kernel<BN, MODE, TO, STAGES>; }
+
+  static bool prepare() {
+    static bool done = false;
+    if (!done) {
+      if (cudaFuncSetAttribute(kernel(), cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+        set_error("gemm_tc: cannot reserve %d bytes of shared memory", SMEM);
+        return false;
+      }
+      // all of the SM's configurable memory as shared memory: two CTAs of the narrow variants then fit
+      cudaFuncSetAttribute(kernel(), cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+      cudaGetLastError();
+      done = true;
     }
-    attr_set = true;
+    return true;
   }
-  cpi::launch_pdl(kern, grid, 128, SMEM, stream, mw, mx, p);
-  return check_launch("gemm_tc");
+
+  // CTAs of this variant that share an SM.  Counted here from shared memory and tensor-memory columns:
+  // the runtime's occupancy calculator answers 1 for every kernel that allocates tensor memory, although
+  // such CTAs do run side by side (measured: 296 CTAs of 100 KB with tensor memory ran at once).
+  static int blocks_per_sm() {
+    static int n = -1;
+    if (n < 0) {
+      n = 1;
+      cudaFuncAttributes fa;
+      int dev = 0, per_sm = 0, reserved = 0;
+      if (prepare() && cudaFuncGetAttributes(&fa, kernel()) == cudaSuccess && cudaGetDevice(&dev) == cudaSuccess &&
+          cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) == cudaSuccess &&
+          cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) == cudaSuccess) {
+        const int by_smem = per_sm / (SMEM + (int)fa.sharedSizeBytes + reserved);
+        const int cols = ACC * BN < 32 ? 32 : ACC * BN;
+        const int by_tmem = 512 / cols;
+        n = by_smem < by_tmem ? by_smem : by_tmem;
+        if (n < 1) n = 1;
+      } else {
+        cudaGetLastError();
+      }
+    }
+    return n;
+  }
+
+  // Clusters of `size` CTAs along z that the GPU holds at once (0 when it cannot say): the runtime's count
+  // (which knows how SMs group into GPCs, and assumes one CTA per SM) times the CTAs that share an SM.
+  static int max_clusters(int size) {
+    static int cache[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
+    if (size < 1 || size > 8) return 0;
+    if (cache[size] < 0) {
+      cache[size] = 0;
+      if (prepare()) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(1, 1, size);
+        cfg.blockDim = dim3(128);
+        cfg.dynamicSmemBytes = SMEM;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)size;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, kernel(), &cfg) == cudaSuccess && n > 0) cache[size] = n * blocks_per_sm();
+        else cudaGetLastError();
+      }
+    }
+    return cache[size];
+  }
+
+  static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
+    if (!prepare()) return 1;
+    if (p.cluster_split) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = grid;
+      cfg.blockDim = dim3(128);
+      cfg.dynamicSmemBytes = SMEM;
+      cfg.stream = stream;
+      cudaLaunchAttribute attr[2];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = (unsigned)p.splits;
+      attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 2;
+      count_launch();
+      cudaLaunchKernelEx(&cfg, kernel(), mw, mx, p);
+    } else {
+      cpi::launch_pdl(kernel(), grid, 128, SMEM, stream, mw, mx, p);
+    }
+    return check_launch("gemm_tc");
+  }
+};
+
+// Clusters of `size` that fit at once for the kernel variant of a token tile and epilogue.
+static int max_clusters_for(int bn_cap, bool swiglu, int size) {
+  switch (bn_cap) {
+    case 16:  return swiglu ? Variant<16, kSwiglu, __nv_bfloat16>::max_clusters(size) : Variant<16, kStore, __nv_bfloat16>::max_clusters(size);
+    case 32:  return swiglu ? Variant<32, kSwiglu, __nv_bfloat16>::max_clusters(size) : Variant<32, kStore, __nv_bfloat16>::max_clusters(size);
+    case 64:  return swiglu ? Variant<64, kSwiglu, __nv_bfloat16>::max_clusters(size) : Variant<64, kStore, __nv_bfloat16>::max_clusters(size);
+    case 128: return swiglu ? Variant<128, kSwiglu, __nv_bfloat16>::max_clusters(size) : Variant<128, kStore, __nv_bfloat16>::max_clusters(size);
+  }
+  return 0;
 }
 
 template <int MODE, typename TO>
 static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t s) {
   switch (bn) {
-    case 16:  return launch<16, MODE, TO>(mw, mx, p, grid, s);
-    case 32:  return launch<32, MODE, TO>(mw, mx, p, grid, s);
-    case 64:  return launch<64, MODE, TO>(mw, mx, p, grid, s);
-    case 128: return launch<128, MODE, TO>(mw, mx, p, grid, s);
-    case 256: return launch<256, MODE, TO>(mw, mx, p, grid, s);
+    case 16:  return Variant<16, MODE, TO>::launch(mw, mx, p, grid, s);
+    case 32:  return Variant<32, MODE, TO>::launch(mw, mx, p, grid, s);
+    case 64:  return Variant<64, MODE, TO>::launch(mw, mx, p, grid, s);
+    case 128: return Variant<128, MODE, TO>::launch(mw, mx, p, grid, s);
+    case 256: return Variant<256, MODE, TO>::launch(mw, mx, p, grid, s);
   }
   set_error("gemm_tc: token tile %d is not supported", bn);
   return 1;
@@ -512,6 +672,24 @@ static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const
 }  // namespace cpi
 
 using namespace cpi;
+
+// Whether split-K merges through a cluster's shared memory (default) or through tickets and global scratch.
+static int g_cluster_split = 1;
+extern "C" void cpi_gemm_tc_cluster_split(int on) { g_cluster_split = on; }
+extern "C" int cpi_gemm_tc_uses_cluster_split(int bn, int splits) {
+  return g_cluster_split && splits > 1 && splits <= 8 && bn <= 128;
+}
+
+extern "C" int cpi_gemm_tc_max_clusters(int bn, int swiglu, int size) { return tc::max_clusters_for(bn, swiglu != 0, size); }
+extern "C" int cpi_gemm_tc_blocks_per_sm(int bn, int swiglu) {
+  switch (bn) {
+    case 16:  return swiglu ? tc::Variant<16, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<16, tc::kStore, __nv_bfloat16>::blocks_per_sm();
+    case 32:  return swiglu ? tc::Variant<32, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<32, tc::kStore, __nv_bfloat16>::blocks_per_sm();
+    case 64:  return swiglu ? tc::Variant<64, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<64, tc::kStore, __nv_bfloat16>::blocks_per_sm();
+    case 128: return swiglu ? tc::Variant<128, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<128, tc::kStore, __nv_bfloat16>::blocks_per_sm();
+  }
+  return 0;
+}
 
 // Token-tile width and split count for a launch (also used by the caller to size the scratch).
 // tiles_hint = expected token tiles per group (rows per group / bn, rounded up), groups_hint = groups in use.
@@ -545,15 +723,25 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
   // CTAs that will really run: one per token tile; with groups at most one more per group that has rows
   const int run_y = n_groups > 0 ? (T <= n_groups ? T : (T + bn - 1) / bn + n_groups / 2) : (T + bn - 1) / bn;
   const long ctas = (long)n_tiles * (run_y > 0 ? run_y : 1);
-  const long slots = bn <= 32 ? 2 * 148 : 148;              // resident CTAs: narrow token tiles fit two per SM
-  if (ctas < slots) {
-    // fill one wave and no more: a launch of 1.1 waves takes as long as one of 2
-    splits = (int)(slots / ctas);
-    const int max_by_k = k_tiles / 4 > 0 ? k_tiles / 4 : 1;     // at least 4 k-tiles per split
-    if (splits > max_by_k) splits = max_by_k;
-    if (splits > 8) splits = 8;
-    if (bn >= 64 && splits > 1) splits = 1;                     // wide token tiles: the merge of parts costs more than it saves
-    if (splits < 1) splits = 1;
+  const int max_by_k = k_tiles / 4 > 0 ? k_tiles / 4 : 1;     // at least 4 k-tiles per split
+  if (g_cluster_split && bn <= 128 && (bn & (bn - 1)) == 0) {
+    // the splits of a tile are a cluster: the most splits (up to 8) whose clusters are all resident at
+    // once, so that the launch is one wave (a launch of 1.1 waves takes as long as one of 2)
+    for (int s = max_by_k < 8 ? max_by_k : 8; s >= 2; --s) {
+      const int per_s = (k_tiles + s - 1) / s;
+      if ((long)(s - 1) * per_s >= k_tiles) continue;           // would leave an empty split
+      if (ctas <= tc::max_clusters_for(bn, swiglu != 0, s)) { splits = s; break; }
+    }
+  } else {
+    const long slots = bn <= 32 ? 2 * 148 : 148;              // resident CTAs: narrow token tiles fit two per SM
+    if (ctas < slots) {
+      // fill one wave and no more
+      splits = (int)(slots / ctas);
+      if (splits > max_by_k) splits = max_by_k;
+      if (splits > 8) splits = 8;
+      if (bn >= 64 && splits > 1) splits = 1;                   // wide token tiles: the merge of parts costs more than it saves
+      if (splits < 1) splits = 1;
+    }
   }
   const int per = (k_tiles + splits - 1) / splits;
   splits = (k_tiles + per - 1) / per;
@@ -592,14 +780,15 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   // token tiles: sum_g ceil(rows_g / bn) <= ceil(T / bn) + min(T, groups)
   dim3 grid((N + tc::BM - 1) / tc::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), splits);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc: too many token tiles (%u)", grid.y);
-  if (splits > 1) {
+  const int cluster_split = cpi_gemm_tc_uses_cluster_split(cap, splits);
+  if (splits > 1 && !cluster_split) {
     const long live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
     const long tiles = (long)grid.x * live_y;
     CPI_REQUIRE(bn == cap, "gemm_tc: split-K needs a power-of-two token tile, got %d", bn);
     CPI_REQUIRE(partials && tickets && partials_elems >= tiles * splits * acc * bn * tc::BM && tickets_elems >= tiles,
                 "gemm_tc: split-K scratch is too small (tiles %ld, splits %d)", tiles, splits);
   }
-  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, partials, tickets, error_flag};
+  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, partials, tickets, cluster_split, error_flag};
   if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(cap, mw, mx, p, grid, stream);

@@ -16,6 +16,7 @@ F32, BF16 = 0, 1
 MODE_STORE, MODE_ADD, MODE_SWIGLU = 0, 1, 2
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
+MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
 
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
@@ -198,7 +199,10 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
         bn.value = force_bn
         live_y.value = -(-T // force_bn) + (min(T, n_groups) if grouped else 0)
     sp = splits.value if force_splits is None else force_splits
-    if sp > 1:
+    cap = 16
+    while cap < bn.value:
+        cap *= 2
+    if sp > 1 and not load().cpi_gemm_tc_uses_cluster_split(c_int(cap), c_int(sp)):
         tiles = -(-N // 128) * live_y.value
         need = tiles * sp * (2 if mode == MODE_SWIGLU else 1) * bn.value * 128
         if need > (1 << 26):                 # keep the scratch modest: fewer splits instead
@@ -217,6 +221,12 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
           c_long(st["partials"].numel()), _p(st["tickets"]), c_long(st["tickets"].numel()), _p(st["error"]),
           _stream())
     return True
+
+
+def gemm_cluster_split(on: bool) -> None:
+    """Split-K of `gemm_tc` merges through a cluster's shared memory (default) or, when off, through tickets
+    and global scratch (the older path, kept for comparison)."""
+    load().cpi_gemm_tc_cluster_split(c_int(int(on)))
 
 
 def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_scale=None, group_offsets=None,

@@ -217,6 +217,56 @@ def test_gemm_tensor_core_grouped(counts, bn_rows, mode):
     assert float((out.float() - ref).abs().max()) <= tol
 
 
+@pytest.mark.parametrize("cluster", [True, False])
+@pytest.mark.parametrize("T,N,Kd,splits", [(5, 384, 1024, 2), (16, 200, 2048, 8), (30, 256, 1280, 5), (64, 640, 1536, 3),
+                                           (100, 384, 2048, 7), (128, 128, 4096, 8)])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_gemm_tensor_core_split_k_both_merges(T, N, Kd, splits, mode, cluster):
+    """Split-K merged through a cluster's shared memory and through tickets: same product, and the same
+    bits from one launch to the next."""
+    a = rnd(T, Kd, dtype=torch.bfloat16)
+    w = rnd(2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=2, scale=Kd ** -0.5)
+    scale = rnd(T, seed=5).abs()
+    odt = torch.float32 if mode == 1 else torch.bfloat16
+    K().gemm_cluster_split(cluster)
+    try:
+        outs = []
+        for _ in range(3):
+            out = rnd(T, N, dtype=odt, seed=3)
+            ref = ref_gemm(a, w, mode, out.float().clone(), scale)
+            assert K().gemm_tc(a, w, out, mode, row_scale=scale, force_splits=splits)
+            torch.cuda.synchronize()
+            assert int(K().tc_error_flag(DEV)) == 0
+            outs.append(out)
+    finally:
+        K().gemm_cluster_split(True)
+    tol = (2e-5 if odt == torch.float32 else 1e-2) * max(1.0, float(ref.abs().max()))
+    assert float((outs[0].float() - ref).abs().max()) <= tol
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+@pytest.mark.parametrize("cluster", [True, False])
+def test_gemm_tensor_core_grouped_split_k(cluster):
+    """One token per expert (a decode step of batch 3 over 6 experts), the k range cut in 4."""
+    counts, N, Kd = [1, 0, 0, 1, 0, 1], 256, 2048
+    G, M = len(counts), sum(counts)
+    w = rnd(G, 2 * N, Kd, dtype=torch.bfloat16, seed=1, scale=Kd ** -0.5)
+    a = rnd(M, Kd, dtype=torch.bfloat16)
+    offs = torch.tensor([0] + list(torch.tensor(counts).cumsum(0)), dtype=torch.int32, device=DEV)
+    grp = torch.repeat_interleave(torch.arange(G), torch.tensor(counts)).to(DEV)
+    acc = torch.einsum("mk,mnk->mn", a.float(), w.float()[grp])
+    ref = acc[:, :N] / (1 + torch.exp(-acc[:, :N])) * acc[:, N:]
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    K().gemm_cluster_split(cluster)
+    try:
+        assert K().gemm_tc(a, w, out, 2, m_rows=M, group_offsets=offs, n_groups=G, force_splits=4)
+        torch.cuda.synchronize()
+    finally:
+        K().gemm_cluster_split(True)
+    assert int(K().tc_error_flag(DEV)) == 0
+    assert float((out.float() - ref).abs().max()) <= 1e-2 * max(1.0, float(ref.abs().max()))
+
+
 def test_gemm_tensor_core_split_k_is_deterministic():
     a, w = rnd(8, 5120, dtype=torch.bfloat16), rnd(640, 5120, dtype=torch.bfloat16, scale=0.02)
     outs = []
