@@ -366,6 +366,41 @@ def router_topk(h, w, topk_idx, topk_gate, *, top_k, sigmoid_gate, logits_out=No
               c_int(n), c_int(H), c_int(E), c_int(top_k), c_int(int(sigmoid_gate)), _stream())
 
 
+def moe_route(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, *, top_k,
+              sigmoid_gate, sorted_h=None) -> bool:
+    """Router logits, the top-k choice and the per-expert row lists of a step; returns whether
+    `sorted_h` (the activation rows in expert order) was filled too.  A step with few tokens takes two
+    launches (logits, then one kernel for the rest), a larger one the separate kernels; the results
+    are the same."""
+    _need_cuda(h, w, topk_idx, topk_gate, logits, group_offsets, row_token, row_scale, row_of_slot, sorted_h)
+    _rowmajor(h, "router h")
+    T, H = h.shape
+    E = w.shape[0]
+    if T <= 65535 and T * top_k <= 256 and T * E <= 4096:
+        assert w.is_contiguous() and w.shape[1] == H and logits.dtype == torch.float32 and logits.is_contiguous()
+        _call("cpi_router_topk", _p(h), c_int(dtype_code(h.dtype)), c_long(h.stride(0)), _p(w),
+              c_int(dtype_code(w.dtype)), _p(logits), None, None, c_int(T), c_int(H), c_int(E), c_int(top_k),
+              c_int(int(sigmoid_gate)), _stream())
+        rc = load().cpi_moe_route_small(_p(logits), c_int(T), c_int(E), c_int(top_k), c_int(int(sigmoid_gate)),
+                                        _p(topk_idx), _p(topk_gate), _p(group_offsets), _p(row_token), _p(row_scale),
+                                        _p(row_of_slot), _p(h), c_long(h.stride(0) * h.element_size()), _p(sorted_h),
+                                        c_int(H * h.element_size()), _stream())
+        if rc == 0:
+            global launch_count
+            launch_count += 1
+            return sorted_h is not None
+        if rc > 0:
+            raise KernelError(load().cpi_last_error().decode())
+        # too large or unaligned for the one-launch kernel: select here, lists below
+        _call("cpi_router_select", _p(logits), _p(topk_idx), _p(topk_gate), c_int(T), c_int(E), c_int(top_k),
+              c_int(int(sigmoid_gate)), _stream())
+    else:
+        router_topk(h, w, topk_idx, topk_gate, top_k=top_k, sigmoid_gate=sigmoid_gate, logits_out=logits)
+    moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot, n_tokens=T, top_k=top_k,
+              n_experts=E)
+    return False
+
+
 def moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot, *, n_tokens, top_k,
               n_experts):
     _need_cuda(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot)

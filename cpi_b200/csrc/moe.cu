@@ -107,16 +107,8 @@ router_logits_tile_kernel(const TH* __restrict__ h, long h_stride, const TW* __r
   }
 }
 
-// One thread per token: the k best logits, ties to the lowest index; gate = sigmoid of the chosen logit.
-__global__ void router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx,
-                                     float* __restrict__ topk_gate, int n_tokens, int n_experts, int top_k,
-                                     int gate_mode) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= n_tokens) return;
-  const float* lg = logits + (size_t)t * n_experts;
-  int* idx = topk_idx + (size_t)t * top_k;
+// The k best logits of one token, ties to the lowest index; gate = sigmoid of the chosen logit.
+__device__ __forceinline__ void select_topk(const float* lg, int* idx, float* gate, int n_experts, int top_k, int gate_mode) {
   for (int k = 0; k < top_k; ++k) {
     int best = -1;
     float bv = 0.f;
@@ -137,7 +129,76 @@ __global__ void router_select_kernel(const float* __restrict__ logits, int* __re
       bv = lg[best];
     }
     idx[k] = best;
-    topk_gate[(size_t)t * top_k + k] = gate_mode == 0 ? 1.0f : 1.0f / (1.0f + expf(-bv));
+    gate[k] = gate_mode == 0 ? 1.0f : 1.0f / (1.0f + expf(-bv));
+  }
+}
+
+// One thread per token.
+__global__ void router_select_kernel(const float* __restrict__ logits, int* __restrict__ topk_idx,
+                                     float* __restrict__ topk_gate, int n_tokens, int n_experts, int top_k,
+                                     int gate_mode) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens) return;
+  select_topk(logits + (size_t)t * n_experts, topk_idx + (size_t)t * top_k, topk_gate + (size_t)t * top_k, n_experts,
+              top_k, gate_mode);
+}
+
+// A step with few tokens: selection, the per-expert row lists and the gather of the activation rows in
+// one launch.  Block r owns sorted row r; every block repeats the (tiny) selection and list building in
+// shared memory to learn which token that is, and block 0 also writes the lists out.  Same choices and
+// the same stable order as router_select_kernel + moe_lists_kernel.
+constexpr int kSmallSlots = 256, kSmallLogits = 4096;
+__global__ void __launch_bounds__(128)
+moe_route_small_kernel(const float* __restrict__ logits, int n_tokens, int n_experts, int top_k, int gate_mode,
+                       int* __restrict__ topk_idx, float* __restrict__ topk_gate, int* __restrict__ group_offsets,
+                       int* __restrict__ row_token, float* __restrict__ row_scale, int* __restrict__ row_of_slot,
+                       const uint4* __restrict__ src, long src_stride16, uint4* __restrict__ dst, int chunks) {
+  __shared__ float lg_s[kSmallLogits];
+  __shared__ int idx_s[kSmallSlots], rowtok_s[kSmallSlots], offs_s[kMaxExperts + 1];
+  __shared__ float gate_s[kSmallSlots];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, M = n_tokens * top_k;
+  for (int i = tid; i < n_tokens * n_experts; i += 128) lg_s[i] = logits[i];
+  __syncthreads();
+  for (int t = tid; t < n_tokens; t += 128)
+    select_topk(lg_s + t * n_experts, idx_s + t * top_k, gate_s + t * top_k, n_experts, top_k, gate_mode);
+  __syncthreads();
+  for (int e = tid; e < n_experts; e += 128) {
+    int c = 0;
+    for (int q = 0; q < M; ++q) c += idx_s[q] == e;
+    offs_s[e + 1] = c;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    offs_s[0] = 0;
+    for (int e = 0; e < n_experts; ++e) offs_s[e + 1] += offs_s[e];
+  }
+  __syncthreads();
+  const bool writer = blockIdx.x == 0;
+  for (int q = tid; q < M; q += 128) {
+    const int e = idx_s[q];
+    int r = offs_s[e];
+    for (int q2 = 0; q2 < q; ++q2) r += idx_s[q2] == e;
+    rowtok_s[r] = q / top_k;
+    if (writer) {
+      row_token[r] = q / top_k;
+      row_scale[r] = gate_s[q];
+      row_of_slot[q] = r;
+      topk_idx[q] = e;
+      topk_gate[q] = gate_s[q];
+    }
+  }
+  if (writer)
+    for (int e = tid; e <= n_experts; e += 128) group_offsets[e] = offs_s[e];
+  __syncthreads();
+  const int r = blockIdx.x;
+  if (r < M && src) {
+    const uint4* from = src + (size_t)rowtok_s[r] * src_stride16;
+    uint4* to = dst + (size_t)r * chunks;
+    for (int i = tid; i < chunks; i += 128) to[i] = from[i];
   }
 }
 
@@ -221,6 +282,32 @@ extern "C" int cpi_router_topk(const void* h, int h_dtype, long h_stride, const 
         (cpi::launch_pdl(router_logits_kernel<TH, TW>, grid, 128, 0, stream, (const TH*)h, h_stride, (const TW*)w, logits, hidden, n_experts, vec))));
   }
   if (check_launch("router_logits")) return 2;
+  if (!topk_idx) return 0;                          // logits only: the caller selects in a later kernel
+  cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
+  return check_launch("router_select");
+}
+
+// Selection, lists and (when sorted_h is given) the gather for logits already computed: one launch for a
+// step with few tokens.  Returns 0 launched, 1 error, -1 when the step is too large for this kernel.
+extern "C" int cpi_moe_route_small(const float* logits, int n_tokens, int n_experts, int top_k, int gate_mode,
+                                   int* topk_idx, float* topk_gate, int* group_offsets, int* row_token,
+                                   float* row_scale, int* row_of_slot, const void* h, long h_stride_bytes,
+                                   void* sorted_h, int row_bytes, cudaStream_t stream) {
+  if (n_tokens <= 0 || (long)n_tokens * top_k > kSmallSlots || (long)n_tokens * n_experts > kSmallLogits ||
+      n_experts > kMaxExperts || top_k < 1 || top_k > n_experts)
+    return -1;
+  if (sorted_h && (row_bytes % 16 || h_stride_bytes % 16 || (reinterpret_cast<uintptr_t>(h) & 15) ||
+                   (reinterpret_cast<uintptr_t>(sorted_h) & 15)))
+    return -1;
+  cpi::launch_pdl(moe_route_small_kernel, n_tokens * top_k, 128, 0, stream, logits, n_tokens, n_experts, top_k, gate_mode,
+                  topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_slot,
+                  sorted_h ? (const uint4*)h : (const uint4*)nullptr, h_stride_bytes / 16, (uint4*)sorted_h, row_bytes / 16);
+  return check_launch("moe_route_small") ? 1 : 0;
+}
+
+extern "C" int cpi_router_select(const float* logits, int* topk_idx, float* topk_gate, int n_tokens, int n_experts,
+                                 int top_k, int gate_mode, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
   cpi::launch_pdl(router_select_kernel, (n_tokens + 127) / 128, 128, 0, stream, logits, topk_idx, topk_gate, n_tokens, n_experts, top_k, gate_mode);
   return check_launch("router_select");
 }

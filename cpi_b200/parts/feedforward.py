@@ -127,22 +127,24 @@ class MoESwiGLU(FeedForward):
         idx = ws.get("moe_topk_idx", (T, Kk), i32)
         gate = ws.get("moe_topk_gate", (T, Kk), f32)
         logits = ws.get("moe_router_logits", (T, E), f32)
-        K.router_topk(h, self.w_router, idx, gate, top_k=Kk, sigmoid_gate=self.gate_mode != "none", logits_out=logits)
         offsets = ws.get("moe_offsets", (E + 1,), i32)
         row_token = ws.get("moe_row_token", (T * Kk,), i32)
         row_scale = ws.get("moe_row_scale", (T * Kk,), f32)
         row_of_slot = ws.get("moe_row_of_slot", (T * Kk,), i32)
-        K.moe_lists(idx, gate, offsets, row_token, row_scale, row_of_slot, n_tokens=T, top_k=Kk, n_experts=E)
+        M = T * Kk
+        # rows sorted by expert, so that each expert reads a contiguous block (when rows are 16-byte multiples)
+        sortable = (h.shape[1] * h.element_size()) % 16 == 0 and h.stride(0) * h.element_size() % 16 == 0
+        sorted_h = ws.get("moe_in", (M, self.hidden), h.dtype) if sortable else None
+        gathered = K.moe_route(h, self.w_router, idx, gate, logits, offsets, row_token, row_scale, row_of_slot,
+                               top_k=Kk, sigmoid_gate=self.gate_mode != "none", sorted_h=sorted_h)
         if self.capture is not None:
             self.capture.append(idx.clone())
-        M = T * Kk
         hint = max(1, -(-M // E))
         act = ws.get("moe_act", (M, self.inter), h.dtype)
         in_scale = row_scale if self.gate_mode == "sigmoid_input" else None
-        if (h.shape[1] * h.element_size()) % 16 == 0 and h.stride(0) * h.element_size() % 16 == 0:
-            # rows sorted by expert, so that each expert reads a contiguous block
-            sorted_h = ws.get("moe_in", (M, self.hidden), h.dtype)
-            K.gather_rows(h, row_token, sorted_h)
+        if sortable:
+            if not gathered:
+                K.gather_rows(h, row_token, sorted_h)
             project(sorted_h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, row_scale=in_scale,
                     group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
         else:

@@ -455,6 +455,39 @@ def test_router_and_lists(T, H, E, k):
         assert seg == sorted(seg)
 
 
+@pytest.mark.parametrize("T,H,E,k,dt", [(1, 64, 16, 1, torch.bfloat16), (8, 5120, 16, 1, torch.bfloat16),
+                                        (64, 256, 16, 1, torch.bfloat16), (32, 128, 128, 1, torch.bfloat16),
+                                        (5, 96, 8, 2, torch.float32), (50, 64, 7, 3, torch.bfloat16),
+                                        (300, 128, 16, 1, torch.bfloat16), (9, 100, 4, 2, torch.bfloat16)])
+def test_moe_route_one_launch_equals_the_separate_kernels(T, H, E, k, dt):
+    """The routing of a whole step (choice, lists, rows in expert order) through `moe_route`, which takes
+    one kernel for few tokens, against router_topk + moe_lists + gather_rows: same bits everywhere."""
+    h, w = rnd(T, H, dtype=dt), rnd(E, H, dtype=dt, seed=1)
+    w[1] = w[0]
+    M = T * k
+    def buffers():
+        return dict(idx=torch.full((T, k), -1, dtype=torch.int32, device=DEV), gate=torch.zeros(T, k, device=DEV),
+                    logits=torch.zeros(T, E, device=DEV), offs=torch.full((E + 1,), -1, dtype=torch.int32, device=DEV),
+                    row_token=torch.full((M,), -1, dtype=torch.int32, device=DEV), row_scale=torch.zeros(M, device=DEV),
+                    row_of_slot=torch.full((M,), -1, dtype=torch.int32, device=DEV),
+                    sorted_h=torch.zeros(M, H, dtype=dt, device=DEV))
+    a, b = buffers(), buffers()
+    K().router_topk(h, w, a["idx"], a["gate"], top_k=k, sigmoid_gate=True, logits_out=a["logits"])
+    K().moe_lists(a["idx"], a["gate"], a["offs"], a["row_token"], a["row_scale"], a["row_of_slot"], n_tokens=T, top_k=k,
+                  n_experts=E)
+    sortable = (H * h.element_size()) % 16 == 0
+    if sortable:
+        K().gather_rows(h, a["row_token"], a["sorted_h"])
+    done = K().moe_route(h, w, b["idx"], b["gate"], b["logits"], b["offs"], b["row_token"], b["row_scale"],
+                         b["row_of_slot"], top_k=k, sigmoid_gate=True, sorted_h=b["sorted_h"] if sortable else None)
+    if sortable and not done:
+        K().gather_rows(h, b["row_token"], b["sorted_h"])
+    assert done == (sortable and M <= 256 and T * E <= 4096)
+    torch.cuda.synchronize()
+    for name in a:
+        assert torch.equal(a[name], b[name]), name
+
+
 def test_moe_combine_and_gather_and_swiglu():
     T, k, H = 9, 3, 200
     res = rnd(T, H)
