@@ -1,0 +1,142 @@
+// Epilogue of the tensor-core GEMMs for tiles with many token columns.
+//
+// The accumulator sits in tensor memory with the output FEATURE along the lanes (one thread each) and
+// the TOKEN along the columns, while the output is [token][feature]: written straight from the
+// registers, every store instruction of a warp covers only 32 features of one token (64 bytes of
+// bfloat16), one instruction per token.  Measured on a 256 x 208 tile that cost 13 us (bf16 store) to
+// 30 us (SwiGLU into rows 16 KB apart) against 2 us for reading tensor memory.  So the tile is turned
+// in shared memory instead: each thread drops its feature's values at stage[token][feature] (a warp
+// writes 32 neighbouring words: no bank conflicts), and after a barrier each warp copies whole token
+// rows of 128 features with 16-byte (float32) or 8-byte (bfloat16) accesses per lane; the
+// read-modify-write of the ADD epilogue keeps four rows in flight.  Arithmetic and its order are those
+// of the direct epilogue: out = old + acc * scale, or silu(g * scale) * (u * scale).
+#pragma once
+#include "common.cuh"
+
+namespace cpi {
+namespace epi {
+
+enum Mode : int { kStore = 0, kAdd = 1, kSwiglu = 2 };
+
+// silu(g) * u with the hardware's exponential and reciprocal (two special-function instructions and a few
+// multiplies; relative error ~1e-7, far below the bfloat16 rounding of the result).  An exact division
+// costs a dependent chain of ~30 instructions per element, which the four epilogue warps of a CTA cannot
+// hide: on a 256-token tile it took longer than the tile's matrix product.  Every tensor-core epilogue
+// uses this one function, so prefill and decode round alike.
+__device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+
+template <typename TO> struct Stage;
+template <> struct Stage<float> {
+  using T = float;
+  static __device__ __forceinline__ float put(float v) { return v; }
+};
+template <> struct Stage<__nv_bfloat16> {
+  using T = __nv_bfloat16;
+  static __device__ __forceinline__ __nv_bfloat16 put(float v) { return __float2bfloat16_rn(v); }
+};
+
+// Whether the staged epilogue may be used for this output: 128-feature rows of the tile start on
+// 16-byte boundaries and the tile is wide enough for the detour to pay.
+template <typename TO>
+__device__ __forceinline__ bool staged_ok(const void* out, long ldo, int n_valid_t) {
+  return n_valid_t >= 32 && (ldo % (16 / (int)sizeof(TO))) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+}
+
+// ld16(col, dst): the caller's tensor-memory load of 16 columns starting at `col` of accumulator 0;
+// ld16u the same for the second accumulator (SwiGLU).  `stage` holds STAGE_COLS x 128 elements of TO
+// (STAGE_COLS a multiple of 16); a tile with more columns goes through in several passes.
+// All 128 threads call this; it contains __syncthreads().
+template <int MODE, typename TO, int STAGE_COLS, typename Ld, typename LdU>
+__device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int warp, int lane, int n0, int N, int t0,
+                                       int n_valid_t, int n_cols, TO* out, long ldo, const int* out_rows,
+                                       const float* row_scale) {
+  static_assert(STAGE_COLS >= 16 && STAGE_COLS % 16 == 0, "the stage holds whole chunks of 16 columns");
+  using S = typename Stage<TO>::T;
+  S* stage = reinterpret_cast<S*>(stage_mem);
+  const int row = warp * 32 + lane;                      // feature within the tile
+  const float* scale = row_scale ? row_scale + t0 : nullptr;
+  // Phase A.  Branch-free per chunk: the 16 values are computed side by side (one basic block, so their
+  // special-function latencies overlap) and all are dropped into the stage; columns past the tile's
+  // tokens hold zeros or finite junk and are never copied out.
+  constexpr int PER = 4;                                 // features per lane: 32 lanes cover the 128 of a row
+  constexpr int R = 8;
+  const int n = n0 + PER * lane;
+  const bool whole = n + PER <= N;
+#pragma unroll 1
+  for (int p0 = 0; p0 < n_cols; p0 += STAGE_COLS) {      // one pass per STAGE_COLS columns
+  const int p1 = min(p0 + STAGE_COLS, n_cols), v1 = min(p0 + STAGE_COLS, n_valid_t);
+  if (p0 > 0) __syncthreads();                           // the previous pass has been copied out
+#pragma unroll 1
+  for (int c = p0; c < p1; c += 16) {
+    float v[16], u[16];
+    ld16(c, v);
+    if (MODE == kSwiglu) ld16u(c, u);
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const float s = scale ? scale[min(c + j, n_valid_t - 1)] : 1.0f;
+      float x = v[j] * s;
+      if (MODE == kSwiglu) x = silu_mul(x, u[j] * s);
+      v[j] = x;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) stage[(c - p0 + j) * 128 + row] = Stage<TO>::put(v[j]);
+  }
+  __syncthreads();
+  // Phase B.  A warp copies rows warp, warp + 4, ...; eight rows per round, all their loads first.
+#pragma unroll 1
+  for (int cb = p0 + warp; cb < v1; cb += 4 * R) {
+    TO* dst[R];
+    bool live[R];
+#pragma unroll
+    for (int q = 0; q < R; ++q) {
+      const int col = cb + 4 * q;
+      live[q] = col < v1;
+      const int lr = t0 + (live[q] ? col : cb);
+      dst[q] = out + (size_t)(out_rows ? out_rows[lr] : lr) * ldo + n;
+    }
+    if (sizeof(TO) == 4) {
+      float4 old[R], sv[R];
+      if (MODE == kAdd) {
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+          if (live[q] && whole) old[q] = *reinterpret_cast<const float4*>(dst[q]);
+      }
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+        sv[q] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + ((live[q] ? cb + 4 * q : cb) - p0) * 128 + PER * lane);
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        if (!live[q]) continue;
+        if (whole) {
+          float4 r = sv[q];
+          if (MODE == kAdd) { r.x = old[q].x + r.x; r.y = old[q].y + r.y; r.z = old[q].z + r.z; r.w = old[q].w + r.w; }
+          *reinterpret_cast<float4*>(dst[q]) = r;
+        } else {
+          const float e[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w};
+          float* d = reinterpret_cast<float*>(dst[q]);
+          for (int i = 0; i < PER && n + i < N; ++i) d[i] = MODE == kAdd ? d[i] + e[i] : e[i];
+        }
+      }
+    } else {
+      uint2 sv[R];
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+        sv[q] = *reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(stage) + ((live[q] ? cb + 4 * q : cb) - p0) * 128 + PER * lane);
+#pragma unroll
+      for (int q = 0; q < R; ++q) {
+        if (!live[q]) continue;
+        if (whole) {
+          *reinterpret_cast<uint2*>(dst[q]) = sv[q];
+        } else {
+          const __nv_bfloat16* src = reinterpret_cast<const __nv_bfloat16*>(&sv[q]);
+          __nv_bfloat16* d = reinterpret_cast<__nv_bfloat16*>(dst[q]);
+          for (int i = 0; i < PER && n + i < N; ++i) d[i] = src[i];
+        }
+      }
+    }
+  }
+  }
+}
+
+}  // namespace epi
+}  // namespace cpi

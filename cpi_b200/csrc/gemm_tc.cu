@@ -29,6 +29,7 @@
 // Every mbarrier wait is bounded: when it runs out the CTA raises `*error_flag`, stops issuing work,
 // lets copies in flight land, frees its tensor memory and returns.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include <cuda.h>
 #include <mutex>
 #include <unordered_map>
@@ -292,7 +293,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   pdl_wait();                                    // before any global read or write of this thread
   bool ok = mbar_wait(&accum_bar, 0, abort_flag);
   fence_after_sync();
-  ok = ok && !abort_s;
+  ok = __syncthreads_and(ok && !abort_s) != 0;            // one verdict for the CTA
 
   const int row = warp * 32 + lane;                       // accumulator lane = output feature n0 + row
   const int n = n0 + row;
@@ -309,7 +310,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     TO* o = out + (size_t)(p.out_rows ? p.out_rows[lr] : lr) * p.ldo + n;
     if (MODE == kSwiglu) {
       u *= s;
-      store_out<TO>(o, v / (1.0f + __expf(-v)) * u);
+      store_out<TO>(o, epi::silu_mul(v, u));
     } else if (MODE == kAdd) {
       store_out<TO>(o, to_f32(*o) + v);
     } else {
@@ -319,6 +320,13 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   if (p.splits == 1) {
     if (!ok) {
+    } else if (epi::staged_ok<TO>(p.out, p.ldo, n_valid_t)) {
+      // wide tile: turned in shared memory (the stages are idle: every MMA has completed), leaves in whole rows
+      constexpr int kFit = (int)((size_t)STAGES * STAGE_BYTES / (128 * sizeof(TO))) / 16 * 16;   // columns the idle stages hold
+      constexpr int kStageCols = kFit < BN ? kFit : BN;
+      auto ld = [&](int c, float* d) { tmem_ld16(lane_addr + c, d); };
+      auto ldu = [&](int c, float* d) { tmem_ld16(lane_addr + BN + c, d); };
+      epi::staged<MODE, TO, kStageCols>(smem, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows, p.row_scale);
     } else if (MODE == kAdd) {
       // read-modify-write of the residual: the old values of chunk c+1 are fetched while chunk c is added,
       // so that their latency hides behind the tensor-memory load

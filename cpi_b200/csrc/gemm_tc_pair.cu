@@ -16,6 +16,7 @@
 // The reference has no tensor-core kernel of its own (src/kernels/kernels_ops_matvec.cu:343-418 are
 // SIMT GEMVs); this file has no counterpart there.
 #include "common.cuh"
+#include "gemm_epilogue.cuh"
 #include <cuda.h>
 
 namespace cpi {
@@ -166,7 +167,19 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
     if (found_s[0] < 0) return;                                  // both CTAs of the pair leave together
     group = found_s[0]; tile_t = found_s[1]; t_begin = offs_s[group]; t_end = offs_s[group + 1];
   }
-  const int n0 = blockIdx.x * BM;                                // this CTA's output features
+  int pair_n = blockIdx.x >> 1;                                  // which 256 output features
+  if (!p.group_offsets) {
+    // Dense product: pairs are handed out (x fastest, then y) so that the ones running at the same time
+    // cover a band of up to 8 token tiles times as many weight tiles as fit: a wave then pulls about
+    // 8 + 9 operand strips through the L2 instead of 28 + 3, and the weights come from DRAM once.
+    const int n_pairs = gridDim.x >> 1, n_tok = gridDim.y, W = 8;
+    const int pid = blockIdx.y * n_pairs + pair_n;
+    const int band = pid / (W * n_pairs), rem = pid - band * W * n_pairs;
+    const int w_eff = min(W, n_tok - band * W);
+    tile_t = band * W + rem % w_eff;
+    pair_n = rem / w_eff;
+  }
+  const int n0 = (pair_n * 2 + (int)rank) * BM;                  // this CTA's output features
   const int t0 = t_begin + tile_t * p.bn;
   const int n_valid_t = min(p.bn, t_end - t0);
   const int n_mma = min(BN, (n_valid_t + 31) & ~31);             // MMA width: both halves stay multiples of 16
@@ -247,14 +260,22 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
   pdl_wait();
   bool ok = mbar_wait(&accum_bar, 0, abort_flag);
   fence_after_sync();
-  ok = ok && !abort_s;
+  ok = __syncthreads_and(ok && !abort_s) != 0;                   // one verdict for the CTA
   const int row = warp * 32 + lane;
   const int n = n0 + row;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
   const int n_cols = min(BN, (n_valid_t + 15) & ~15);
   TO* out = reinterpret_cast<TO*>(p.out);
   const bool row_ok = n < p.N;
-  if (ok && MODE == kAdd) {
+  if (ok && epi::staged_ok<TO>(p.out, p.ldo, n_valid_t)) {
+    // the tile is turned in shared memory (the stages are idle: every MMA has completed) and leaves in
+    // whole rows
+    constexpr int kFit = (int)((size_t)STAGES * STAGE_BYTES / (128 * sizeof(TO))) / 16 * 16;   // columns the idle stages hold
+      constexpr int kStageCols = kFit < BN ? kFit : BN;
+      auto ld = [&](int c, float* d) { tmem_ld16(lane_addr + c, d); };
+    auto ldu = [&](int c, float* d) { tmem_ld16(lane_addr + BN + c, d); };
+    epi::staged<MODE, TO, kStageCols>(smem, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows, p.row_scale);
+  } else if (ok && MODE == kAdd) {
     float* outf = reinterpret_cast<float*>(p.out);
     float old[2][16];
     auto fetch = [&](int c, float* dst) {
@@ -296,7 +317,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
         if (!row_ok || col >= n_valid_t) continue;
         const float s = p.row_scale ? p.row_scale[t0 + col] : 1.0f;
         float x = v[j] * s;
-        if (MODE == kSwiglu) x = x / (1.0f + __expf(-x)) * (u[j] * s);
+        if (MODE == kSwiglu) x = epi::silu_mul(x, u[j] * s);
         store_out<TO>(out + (size_t)(p.out_rows ? p.out_rows[t0 + col] : t0 + col) * p.ldo + n, x);
       }
     }
@@ -315,7 +336,11 @@ template <int BN, int MODE, typename TO>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
   constexpr int ACC = MODE == kSwiglu ? 2 : 1;
   constexpr int STAGE = ACC * BM * BK * 2 + (BN / 2) * BK * 2;
-  constexpr int S0 = (196 * 1024) / STAGE;
+  // One accumulator: half the shared memory per pair, so that two pairs share an SM pair and the epilogue
+  // of one runs under the matrix product of the other (measured 1.4x).  Two accumulators fill the tensor
+  // memory: one pair per SM pair, with all the stages.
+  constexpr int BUDGET = ACC == 1 ? 108 * 1024 : 196 * 1024;
+  constexpr int S0 = BUDGET / STAGE;
   constexpr int STAGES = S0 > 8 ? 8 : S0;
   constexpr int SMEM = STAGES * STAGE + 1024;
   auto kern = gemm_tc_pair_kernel<BN, MODE, TO, STAGES>;
