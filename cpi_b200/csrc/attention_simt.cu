@@ -112,6 +112,110 @@ __global__ void qkv_post_kernel(QkvPostParams p) {
   }
 }
 
+// The same work for bfloat16 heads of 128 with half-split pairs, 16 bytes per lane: a warp takes two heads
+// at a time (lanes 0-15 one, 16-31 the other; lane l of a head holds elements 8l .. 8l+7, its rotation
+// partner sits 8 lanes away), a block takes a slice of one token's heads and computes the token's 64
+// sines and cosines once.  Same formulas as qkv_post_kernel; sums of squares in another order.
+__global__ void __launch_bounds__(256) qkv_post_d128_kernel(QkvPostParams p, int heads_per_block) {
+  __shared__ float cos_s[64], sin_s[64];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pos = p.token_pos[t];
+  if (p.inv_freq && tid < 64) {
+    float s, c;
+    sincosf((float)pos * p.inv_freq[tid], &s, &c);
+    cos_s[tid] = c; sin_s[tid] = s;
+  }
+  __syncthreads();
+  const int heads_total = p.n_heads + (p.write_kv ? 2 * p.n_kv_heads : 0);
+  const int h_begin = blockIdx.y * heads_per_block, h_end = min(heads_total, h_begin + heads_per_block);
+  const int sub = lane >> 4, l = lane & 15;
+  const __nv_bfloat16* row = reinterpret_cast<const __nv_bfloat16*>(p.qkv) + (size_t)t * p.qkv_stride;
+  int page = 0;
+  if (p.write_kv) {
+    const int slot = p.seq_slot[p.token_seq[t]];
+    page = p.page_table[(size_t)slot * p.max_blocks + pos / p.page_size];
+  }
+  const float temp = p.temperature ? 1.0f + p.attn_scale * logf(floorf(((float)pos + 1.0f) / p.floor_scale) + 1.0f) : 1.0f;
+  for (int hs = h_begin + 2 * warp + sub; hs < h_end + sub; hs += 2 * (blockDim.x >> 5)) {
+    // (all 32 lanes stay in the loop together so that the shuffles below are whole-warp; a lane whose
+    // head is past the end computes on zeros and stores nothing)
+    const bool live = hs < h_end;
+    const bool is_q = hs < p.n_heads, is_v = hs >= p.n_heads + p.n_kv_heads;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live) raw = *reinterpret_cast<const uint4*>(row + (size_t)hs * 128 + 8 * l);
+    __nv_bfloat16* dst = nullptr;
+    if (live) {
+      if (is_q) {
+        dst = reinterpret_cast<__nv_bfloat16*>(p.q_out) + ((size_t)t * p.n_heads + hs) * 128 + 8 * l;
+      } else {
+        const int kvh = is_v ? hs - p.n_heads - p.n_kv_heads : hs - p.n_heads;
+        __nv_bfloat16* base = reinterpret_cast<__nv_bfloat16*>(is_v ? p.v_cache : p.k_cache);
+        dst = base + (((size_t)page * p.n_kv_heads + kvh) * p.page_size + pos % p.page_size) * 128 + 8 * l;
+      }
+    }
+    float x[8];
+    {
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(h2[j]); x[2 * j] = f.x; x[2 * j + 1] = f.y; }
+    }
+    const bool rotate = !is_v;                                  // v is copied as it is
+    auto group_sum = [&](float v) {
+      v += __shfl_xor_sync(0xffffffffu, v, 8); v += __shfl_xor_sync(0xffffffffu, v, 4);
+      v += __shfl_xor_sync(0xffffffffu, v, 2); v += __shfl_xor_sync(0xffffffffu, v, 1);
+      return v;
+    };
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+    ss = group_sum(ss);
+    if (p.qk_norm && p.norm_before_rope && rotate) {
+      const float inv = 1.0f / sqrtf(ss / 128.0f + p.norm_eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= inv;
+    }
+    if (p.inv_freq) {
+      float other[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) other[j] = __shfl_xor_sync(0xffffffffu, x[j], 8);
+      if (rotate) {
+        const bool first = l < 8;                               // first half: a' = a c - b s; second: b' = a s + b c
+        ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int i = 8 * (l & 7) + j;
+          const float c = cos_s[i], sn = sin_s[i];
+          x[j] = first ? x[j] * c - other[j] * sn : other[j] * sn + x[j] * c;
+          ss += x[j] * x[j];
+        }
+      }
+      ss = group_sum(ss);
+    }
+    if (p.qk_norm && !p.norm_before_rope && rotate) {
+      const float inv = 1.0f / sqrtf(ss / 128.0f + p.norm_eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= inv;
+    }
+    if (is_q && p.temperature) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] *= temp;
+    }
+    if (live) {
+      uint4 o;
+      if (is_v) {
+        o = raw;
+      } else {
+        __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(x[2 * j], x[2 * j + 1]);
+      }
+      *reinterpret_cast<uint4*>(dst) = o;
+    }
+  }
+}
+
 struct AttnParams {
   const void* q; void* out;              // [T, NH D]
   const void* k_cache; const void* v_cache;
@@ -213,6 +317,20 @@ extern "C" int cpi_qkv_post(const void* qkv, long qkv_stride, void* q_out, void*
                   token_seq, token_pos, seq_slot, inv_freq, interleaved, qk_norm, norm_before_rope,
                   norm_eps, temperature, floor_scale, attn_scale, n_heads, n_kv_heads, head_dim, write_kv};
   const int heads_total = n_heads + (write_kv ? 2 * n_kv_heads : 0);
+  auto aligned16 = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (dtype == kBF16 && head_dim == 128 && !interleaved && qkv_stride % 8 == 0 && aligned16(qkv) && aligned16(q_out) &&
+      (!write_kv || (aligned16(k_cache) && aligned16(v_cache))) && n_tokens <= 65535) {
+    // enough blocks for two waves of the GPU, at most one block per 16 heads
+    int slices = (2 * 148 * 8 + n_tokens - 1) / n_tokens;
+    const int max_slices = (heads_total + 15) / 16;
+    if (slices > max_slices) slices = max_slices;
+    if (slices < 1) slices = 1;
+    int per = (heads_total + slices - 1) / slices;
+    per = (per + 1) & ~1;                                        // warps take heads two at a time
+    dim3 grid_v(n_tokens, (heads_total + per - 1) / per);
+    cpi::launch_pdl(qkv_post_d128_kernel, grid_v, 256, 0, stream, p, per);
+    return check_launch("qkv_post");
+  }
   dim3 grid(n_tokens, (heads_total + 3) / 4);
   CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(qkv_post_kernel<T>, grid, 128, 0, stream, p));
   return check_launch("qkv_post");

@@ -363,11 +363,14 @@ def test_attention_finds_one_far_key_among_hundreds():
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("D,interleaved,norm,before,temp", [(16, False, True, False, None), (48, True, True, True, None),
-                                                            (128, False, False, False, (32.0, 0.1)),
-                                                            (256, True, True, False, (8.0, 0.5))])
-def test_qkv_post(dtype, D, interleaved, norm, before, temp):
-    NH, NKV, page, T = 3, 1, 16, 6
+@pytest.mark.parametrize("D,interleaved,norm,before,temp,heads", [
+    (16, False, True, False, None, (3, 1)), (48, True, True, True, None, (3, 1)),
+    (128, False, False, False, (32.0, 0.1), (3, 1)), (256, True, True, False, (8.0, 0.5), (3, 1)),
+    # heads of 128 in bfloat16 take the 16-byte kernel: odd and large head counts, both norm orders
+    (128, False, True, False, (32.0, 0.1), (6, 2)), (128, False, True, True, None, (40, 8)),
+    (128, False, False, False, None, (16, 1))])
+def test_qkv_post(dtype, D, interleaved, norm, before, temp, heads):
+    (NH, NKV), page, T = heads, 16, 6
     qkv = rnd(T, (NH + 2 * NKV) * D, dtype=dtype, seed=1)
     pos = [0, 1, 31, 32, 1000, 17]
     table = torch.tensor([[0] * 70, list(range(5, 75))], dtype=torch.int32, device=DEV)
