@@ -57,6 +57,7 @@ struct Params {
   int k_tiles;         // ceil(K / 64)
   int splits, k_tiles_per_split;
   float* partials; int* tickets;
+  int tiles_on_x;      // 1: blockIdx.x counts token tiles and blockIdx.y weight tiles (groups with many tokens)
   int cluster_split;   // 1: the splits of a tile are one cluster along z and merge through shared memory
   int* error_flag;
 };
@@ -185,7 +186,9 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   pdl_launch_dependents();
   // ---- which tile ----
-  int group = 0, t_begin = 0, t_end = p.T, tile_t = blockIdx.y;
+  // Groups with many tokens: the token tiles of one (weight tile, group) are neighbours in launch order,
+  // so the second one finds the weight strip in the L2 that the first one pulled from DRAM.
+  int group = 0, t_begin = 0, t_end = p.T, tile_t = p.tiles_on_x ? blockIdx.x : blockIdx.y;
   if (p.group_offsets) {
     pdl_wait();                                  // the row lists come from the kernel before this one
     // One division per group, done by one thread each; thread 0 then walks the counts.  (Every CTA of the
@@ -213,7 +216,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   }
   const int t0 = t_begin + tile_t * p.bn;
   if (t0 >= t_end) return;
-  const int n0 = blockIdx.x * BM;
+  const int n0 = (p.tiles_on_x ? blockIdx.y : blockIdx.x) * BM;
   const int split = blockIdx.z;
   const int kt_begin = split * p.k_tiles_per_split;
   const int kt_end = min(p.k_tiles, kt_begin + p.k_tiles_per_split);
@@ -796,7 +799,11 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
     CPI_REQUIRE(partials && tickets && partials_elems >= tiles * splits * acc * bn * tc::BM && tickets_elems >= tiles,
                 "gemm_tc: split-K scratch is too small (tiles %ld, splits %d)", tiles, splits);
   }
-  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, partials, tickets, cluster_split, error_flag};
+  // (measured on 16 experts: 5 % faster for the two-accumulator product at 2,048 tokens, slower for the
+  // one-accumulator product, whose token rows are the larger operand)
+  const int tiles_on_x = mode == tc::kSwiglu && n_groups > 0 && T > 2 * n_groups && splits == 1 && grid.x <= 65535;
+  if (tiles_on_x) { const unsigned gx = grid.x; grid.x = grid.y; grid.y = gx; }
+  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, partials, tickets, tiles_on_x, cluster_split, error_flag};
   if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(cap, mw, mx, p, grid, stream);

@@ -209,6 +209,7 @@ moe_route_small_kernel(const float* __restrict__ logits, int n_tokens, int n_exp
 //   row_of_slot[t*K + k]      logical row that holds (t, k)'s expert output
 // A warp owns experts warp, warp + 32, ...; it scans the slots 32 at a time and places the matching
 // ones with a ballot, which keeps them in slot order.
+constexpr int kListSlotsInSmem = 8192;
 __global__ void __launch_bounds__(1024)
 moe_lists_kernel(const int* __restrict__ topk_idx, const float* __restrict__ topk_gate,
                  int* __restrict__ group_offsets, int* __restrict__ row_token,
@@ -218,12 +219,20 @@ moe_lists_kernel(const int* __restrict__ topk_idx, const float* __restrict__ top
   pdl_wait();
   __shared__ int counts[kMaxExperts];
   __shared__ int offsets[kMaxExperts + 1];
+  __shared__ int idx_s[kListSlotsInSmem];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // the choices are scanned twice by every warp: keep them in shared memory when they fit
+  const bool staged = n_slots <= kListSlotsInSmem;
+  if (staged) {
+    for (int s = threadIdx.x; s < n_slots; s += blockDim.x) idx_s[s] = topk_idx[s];
+    __syncthreads();
+  }
+  const int* idx = staged ? idx_s : topk_idx;
   for (int e = warp; e < n_experts; e += 32) {
     int c = 0;
     for (int s0 = 0; s0 < n_slots; s0 += 32) {
       const int s = s0 + lane;
-      const bool hit = s < n_slots && topk_idx[s] == e;
+      const bool hit = s < n_slots && idx[s] == e;
       c += __popc(__ballot_sync(0xffffffffu, hit));
     }
     if (lane == 0) counts[e] = c;
@@ -240,7 +249,7 @@ moe_lists_kernel(const int* __restrict__ topk_idx, const float* __restrict__ top
     int m = offsets[e];
     for (int s0 = 0; s0 < n_slots; s0 += 32) {
       const int s = s0 + lane;
-      const bool hit = s < n_slots && topk_idx[s] == e;
+      const bool hit = s < n_slots && idx[s] == e;
       const unsigned mask = __ballot_sync(0xffffffffu, hit);
       if (hit) {
         const int r = m + __popc(mask & ((1u << lane) - 1u));
