@@ -72,6 +72,84 @@ template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
   return row * D + ((chunk ^ (row & 7)) << 3);
 }
 
+// out[th, :] = sum_s w_s O_s / sum_s w_s l_s,  w_s = 2^(m_s - max m), for one (token, head); at most
+// kMaxSplits splits.  All threads of the block call it (it has barriers); the weights are computed once,
+// in parallel, and the sum over splits keeps eight loads in flight.  (Merging inside the attention kernel, by
+// the block that takes a group's last ticket, was measured slower at every batch size: one block then
+// merges all the heads of its group one after the other.)
+constexpr int kMaxSplits = 256;
+struct CombineSmem { float w[kMaxSplits], wl[kMaxSplits], red[4]; };
+__device__ __forceinline__ void combine_head(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                             __nv_bfloat16* __restrict__ out, size_t th, int n_splits, int D,
+                                             CombineSmem& sm) {
+  const int tid = threadIdx.x, n_warps = blockDim.x >> 5;
+  const float2* ml = reinterpret_cast<const float2*>(part_ml) + th * n_splits;
+  const float* po = part_o + th * n_splits * D;
+  if (n_splits <= 32 && D <= (int)blockDim.x) {
+    // Few splits: every thread fetches all (m, l) pairs and its own feature of every part at once (one
+    // round trip to the L2 instead of two or more), then does the arithmetic alone; no barrier.
+    float2 mlv[32];
+    float v[32];
+    const bool mine = tid < D;
+#pragma unroll
+    for (int s = 0; s < 32; ++s) {
+      mlv[s] = s < n_splits ? __ldcg(ml + s) : make_float2(-1e30f, 0.f);
+      v[s] = (s < n_splits && mine) ? __ldcg(po + (size_t)s * D + tid) : 0.f;
+    }
+    float M = -1e30f;
+#pragma unroll
+    for (int s = 0; s < 32; ++s) M = fmaxf(M, mlv[s].x);
+    float L = 0.f, acc = 0.f;
+#pragma unroll
+    for (int s = 0; s < 32; ++s) {
+      if (s < n_splits) {
+        const float f = exp2f(mlv[s].x - M);
+        L += f * mlv[s].y;
+        acc += f * v[s];
+      }
+    }
+    if (mine) out[th * D + tid] = __float2bfloat16_rn(acc / fmaxf(L, 1e-20f));
+    return;
+  }
+  float2 part[kMaxSplits / 64];                       // blockDim.x >= 64
+  float m = -1e30f;
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / 64; ++j) {
+    const int s = tid + j * blockDim.x;
+    part[j] = s < n_splits ? __ldcg(ml + s) : make_float2(-1e30f, 0.f);
+    m = fmaxf(m, part[j].x);
+  }
+  m = warp_max(m);
+  __syncthreads();                                    // the previous head's readers are done with sm
+  if ((tid & 31) == 0) sm.red[tid >> 5] = m;
+  __syncthreads();
+  float M = sm.red[0];
+  for (int w = 1; w < n_warps; ++w) M = fmaxf(M, sm.red[w]);
+#pragma unroll
+  for (int j = 0; j < kMaxSplits / 64; ++j) {
+    const int s = tid + j * blockDim.x;
+    if (s < n_splits) {
+      const float f = exp2f(part[j].x - M);
+      sm.w[s] = f;
+      sm.wl[s] = f * part[j].y;
+    }
+  }
+  __syncthreads();
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += sm.wl[s];
+  for (int d = tid; d < D; d += blockDim.x) {
+    float acc = 0.f;
+    for (int s0 = 0; s0 < n_splits; s0 += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = s0 + j < n_splits ? __ldcg(po + (size_t)(s0 + j) * D + d) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) if (s0 + j < n_splits) acc += sm.w[s0 + j] * v[j];
+    }
+    out[th * D + d] = __float2bfloat16_rn(acc / fmaxf(L, 1e-20f));
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
   pdl_launch_dependents();
@@ -248,54 +326,12 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
   }
 }
 
-// out[t, h, :] = sum_s w_s O_s / sum_s w_s l_s,  w_s = 2^(m_s - max m); at most kMaxSplits splits.
-// The weights are computed once, in parallel, and the sum over splits keeps eight loads in flight.
-constexpr int kMaxSplits = 256;
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          __nv_bfloat16* __restrict__ out, int n_splits, int D) {
-  __shared__ float w_s[kMaxSplits], wl_s[kMaxSplits], red_s[4];
+  __shared__ CombineSmem sm;
   pdl_launch_dependents();
   pdl_wait();
-  const size_t th = blockIdx.x;
-  const int tid = threadIdx.x, n_warps = blockDim.x >> 5;
-  const float2* ml = reinterpret_cast<const float2*>(part_ml) + th * n_splits;
-  float2 mine[kMaxSplits / 64];                       // blockDim.x >= 64
-  float m = -1e30f;
-#pragma unroll
-  for (int j = 0; j < kMaxSplits / 64; ++j) {
-    const int s = tid + j * blockDim.x;
-    mine[j] = s < n_splits ? ml[s] : make_float2(-1e30f, 0.f);
-    m = fmaxf(m, mine[j].x);
-  }
-  m = warp_max(m);
-  if ((tid & 31) == 0) red_s[tid >> 5] = m;
-  __syncthreads();
-  float M = red_s[0];
-  for (int w = 1; w < n_warps; ++w) M = fmaxf(M, red_s[w]);
-#pragma unroll
-  for (int j = 0; j < kMaxSplits / 64; ++j) {
-    const int s = tid + j * blockDim.x;
-    if (s < n_splits) {
-      const float f = exp2f(mine[j].x - M);
-      w_s[s] = f;
-      wl_s[s] = f * mine[j].y;
-    }
-  }
-  __syncthreads();
-  float L = 0.f;
-  for (int s = 0; s < n_splits; ++s) L += wl_s[s];
-  const float* po = part_o + th * n_splits * D;
-  for (int d = tid; d < D; d += blockDim.x) {
-    float acc = 0.f;
-    for (int s0 = 0; s0 < n_splits; s0 += 8) {
-      float v[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = s0 + j < n_splits ? po[(size_t)(s0 + j) * D + d] : 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) if (s0 + j < n_splits) acc += w_s[s0 + j] * v[j];
-    }
-    out[th * D + d] = __float2bfloat16_rn(acc / fmaxf(L, 1e-20f));
-  }
+  combine_head(part_o, part_ml, out, blockIdx.x, n_splits, D, sm);
 }
 
 }  // namespace dec
