@@ -21,10 +21,10 @@ use_paired_kernel = True
 def project(a, w, out, mode=MODE_STORE, **kw):
     """Dense or grouped projection; see csrc/lib.py: gemm_simt for the keyword arguments."""
     if use_tensor_cores and a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
-        # dense products with many tokens go to the two-SM kernel; for the routed experts it measured no
-        # faster than the single-CTA kernel (both wait on memory latency there), so they stay on that one
-        dense = "a_rows" not in kw and "group_offsets" not in kw
-        if use_paired_kernel and dense and a.shape[0] >= 512 and K.gemm_tc_pair(a, w, out, mode, **kw):
+        # products with many tokens go to the two-SM kernel, dense or grouped (it refuses, launching nothing,
+        # what it does not take: few tokens per group, features that are no multiple of 256, a row gather)
+        if use_paired_kernel and "a_rows" not in kw and kw.get("m_rows", a.shape[0]) >= 512 \
+                and K.gemm_tc_pair(a, w, out, mode, **kw):
             return
         if K.gemm_tc(a, w, out, mode, **kw):
             return
