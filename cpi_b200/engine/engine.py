@@ -148,21 +148,34 @@ class Engine:
                 for piece in pieces]
         return torch.cat(outs, dim=0)
 
-    def _run(self, slots, toks, wants) -> torch.Tensor:
+    def step_decode(self, slots: Sequence[int], tokens: torch.Tensor) -> torch.Tensor:
+        """One more token for each slot, the token ids taken from an int32 device tensor [len(slots)]
+        (for instance the sampler's output of the step before, which the host has not read yet); logits of
+        every slot's token.  Otherwise the same as `step` with one-token entries."""
+        B = len(slots)
+        if B == 0:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        if tokens.dtype != torch.int32 or tokens.numel() != B or tokens.device != self.device:
+            raise ValueError("step_decode: tokens must be an int32 tensor on the engine's device, one per slot")
+        return self._run([int(x) for x in slots], [[0]] * B, [[0]] * B, device_tokens=tokens)
+
+    def _run(self, slots, toks, wants, device_tokens=None) -> torch.Tensor:
         """Runs one piece; the returned logits live in a buffer that the next step overwrites."""
         n_new = [len(t) for t in toks]
         starts = self.cache.prepare_step(slots, n_new)
         decode = max(n_new) == 1
         if decode and self.use_graphs and not self._routing_capture:
-            logits = self._run_decode_graph(slots, starts, toks, wants)
+            logits = self._run_decode_graph(slots, starts, toks, wants, device_tokens)
         else:
             batch = self.stager.stage(slots, starts, toks, wants, self.dtype)
+            if device_tokens is not None:
+                batch.tokens.copy_(device_tokens.view(-1))
             logits = self.model.run(batch, self.cache)
         self.cache.commit_step(slots, n_new)
         self.steps_run += 1
         return logits
 
-    def _run_decode_graph(self, slots, starts, toks, wants) -> torch.Tensor:
+    def _run_decode_graph(self, slots, starts, toks, wants, device_tokens=None) -> torch.Tensor:
         B = len(slots)
         R = sum(len(w) for w in wants)
         longest = max(s + 1 for s in starts)
@@ -179,8 +192,12 @@ class Engine:
             dev = torch.empty(self.stager.words_needed(B, B, R), dtype=torch.int32, device=self.device)
             self._graphs[key] = {"dev": dev, "graph": None, "logits": None, "gen": None, "kernels": 0}
             batch = self.stager.stage(slots, starts, toks, wants, self.dtype, static_dev=dev)
+            if device_tokens is not None:
+                batch.tokens.copy_(device_tokens.view(-1))
             return self.model.run(batch, self.cache)
         batch = self.stager.stage(slots, starts, toks, wants, self.dtype, static_dev=st["dev"])
+        if device_tokens is not None:
+            batch.tokens.copy_(device_tokens.view(-1))          # after the staged copy, before the replay
         if st["graph"] is None:
             torch.cuda.synchronize(self.device)
             g = torch.cuda.CUDAGraph()

@@ -83,6 +83,12 @@ class Generator:
             from .engine import StepEntry as step_entry
         self._entry = step_entry
         self.stats = GenerationStats()
+        # Decode steps are launched one ahead of the host: step n+1 takes its tokens from the device tensor
+        # that the sampler of step n wrote, while the host is still reading step n's tokens for the stop
+        # checks.  Needs nothing from the host between steps, so it is off for requests with a callback, a
+        # repetition penalty or n-gram bans.
+        self.pipelined = True
+        self._pinned = None
 
     def generate(self, requests: Sequence[GenerationRequest],
                  on_token: Optional[Callable[[int, int], bool]] = None) -> list:
@@ -109,6 +115,11 @@ class Generator:
         return results
 
     def _run_batch(self, idxs, reqs, results, on_token):
+        needs_host = on_token is not None or any(
+            reqs[i].sampling.repetition_penalty > 1.0 or reqs[i].sampling.no_repeat_ngram_size > 1 for i in idxs)
+        if self.pipelined and not needs_host and hasattr(self.engine, "step_decode") \
+                and hasattr(self.sampler, "sample_device"):
+            return self._run_batch_pipelined(idxs, reqs, results)
         eng = self.engine
         max_len = eng.cache.max_seq_len
         live = list(idxs)
@@ -122,9 +133,11 @@ class Generator:
             step = 0
             t1 = None
             while live:
-                toks = self.sampler.sample(logits, [reqs[i].sampling for i in live],
-                                           [list(reqs[i].prompt) + out[i] for i in live],
-                                           [(i, step) for i in live])
+                params = [reqs[i].sampling for i in live]
+                # the histories (prompt + generated ids) are only looked at by the penalties and the n-gram bans
+                need_hist = any(p.repetition_penalty > 1.0 or p.no_repeat_ngram_size > 1 for p in params)
+                hist = [list(reqs[i].prompt) + out[i] for i in live] if need_hist else [None] * len(live)
+                toks = self.sampler.sample(logits, params, hist, [(i, step) for i in live])
                 if t1 is None:                      # the first sample ends the prefill phase
                     t1 = time.perf_counter()
                     self.stats.prefill_ms += (t1 - t0) * 1e3
@@ -158,3 +171,93 @@ class Generator:
         finally:
             for s in slot.values():                 # an error must not leak slots
                 eng.release_slot(s)
+
+    # ---- one step ahead --------------------------------------------------------------------------
+    def _host_copy(self, toks_dev, k):
+        """Starts the copy of a device token tensor to the host; returns a function that waits and lists it."""
+        if not toks_dev.is_cuda:
+            return toks_dev.tolist
+        import torch
+        if self._pinned is None or self._pinned[0].numel() < toks_dev.numel():
+            n = max(self.max_batch, toks_dev.numel())
+            self._pinned = [torch.empty(n, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        buf = self._pinned[k % 4][:toks_dev.numel()]
+        buf.copy_(toks_dev, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+
+        def wait():
+            ev.synchronize()
+            return buf.tolist()
+        return wait
+
+    def _run_batch_pipelined(self, idxs, reqs, results):
+        """The same decisions as the loop above, with the next step launched before the tokens of the last
+        one are known on the host.  A request that turns out to have ended on a stop token has then been
+        run for one token too many; that token is dropped and the others' results do not depend on it."""
+        eng, sampler = self.engine, self.sampler
+        max_len = eng.cache.max_seq_len
+        live = list(idxs)
+        slot = {i: eng.acquire_slot() for i in live}
+        out = {i: [] for i in live}
+        stops = {i: set(self.default_stop_ids if reqs[i].stop_ids is None else reqs[i].stop_ids) for i in live}
+        plen = {i: len(reqs[i].prompt) for i in live}
+        t0 = time.perf_counter()
+        t1 = None
+        try:
+            logits = eng.step([self._entry(slot[i], reqs[i].prompt, [plen[i] - 1]) for i in live])
+            self.stats.prompt_tokens += sum(plen[i] for i in live)
+            step = 0
+            toks_dev = sampler.sample_device(logits, [reqs[i].sampling for i in live], [None] * len(live),
+                                             [(i, step) for i in live])
+            pending, wait = live, self._host_copy(toks_dev, step)
+            while pending:
+                # requests that go on after the pending token unless it is a stop token
+                cont = [i for i in pending
+                        if len(out[i]) + 1 < reqs[i].max_new and plen[i] + len(out[i]) + 1 <= max_len]
+                nxt_dev = nxt_wait = None
+                if cont:
+                    sel = toks_dev
+                    if len(cont) != len(pending):
+                        where = {i: k for k, i in enumerate(pending)}
+                        sel = toks_dev[[where[i] for i in cont]]
+                    logits = eng.step_decode([slot[i] for i in cont], sel)
+                    self.stats.decode_steps += 1
+                    nxt_dev = sampler.sample_device(logits, [reqs[i].sampling for i in cont], [None] * len(cont),
+                                                    [(i, step + 1) for i in cont])
+                    nxt_wait = self._host_copy(nxt_dev, step + 1)
+                toks = wait()
+                if t1 is None:                      # the first tokens on the host end the prefill phase
+                    t1 = time.perf_counter()
+                    self.stats.prefill_ms += (t1 - t0) * 1e3
+                ended = set()
+                for i, tok in zip(pending, toks):
+                    tok = int(tok)
+                    out[i].append(tok)
+                    self.stats.generated_tokens += 1
+                    reason = None
+                    if tok in stops[i]:
+                        reason = "stop_token"
+                    elif len(out[i]) >= reqs[i].max_new:
+                        reason = "max_new"
+                    elif plen[i] + len(out[i]) > max_len:
+                        reason = "capacity"
+                    if reason is not None:
+                        results[i] = GenerationResult(out[i], reason, plen[i])
+                        eng.release_slot(slot.pop(i))
+                        ended.add(i)
+                if not cont:
+                    break
+                keep = [k for k, i in enumerate(cont) if i not in ended]
+                if len(keep) != len(cont):          # ended on a stop token: their extra token is dropped
+                    full = nxt_wait
+                    nxt_dev = nxt_dev[keep] if keep else None
+                    nxt_wait = (lambda f=full, kk=keep: [f()[k] for k in kk])
+                pending, toks_dev, wait = [cont[k] for k in keep], nxt_dev, nxt_wait
+                step += 1
+            if t1 is not None:
+                self.stats.decode_ms += (time.perf_counter() - t1) * 1e3
+        finally:
+            for sl in slot.values():                # an error must not leak slots
+                eng.release_slot(sl)
+

@@ -46,15 +46,20 @@ class Sampler:
         return torch.tensor(xs, dtype=torch.float32, device=self.device)
 
     def sample(self, logits: torch.Tensor, params: list, histories: list, counters: list) -> list:
+        """The chosen token ids as a list (waits for the device)."""
+        return self.sample_device(logits, params, histories, counters).tolist()
+
+    def sample_device(self, logits: torch.Tensor, params: list, histories: list, counters: list) -> torch.Tensor:
         """logits [R, V] float32 on the device (modified in place when penalties apply);
-        histories[r] = prompt + generated ids of row r; counters[r] = (request index, step)."""
+        histories[r] = prompt + generated ids of row r (None where no option of the row reads it);
+        counters[r] = (request index, step).  Returns int32 [R] on the device without waiting for it."""
         R = logits.shape[0]
-        if R == 0:
-            return []
         out = torch.empty(R, dtype=torch.int32, device=self.device)
+        if R == 0:
+            return out
         if all(p.is_plain_greedy for p in params):
             K.argmax(logits, out)
-            return out.tolist()
+            return out
         for p in params:
             p.validate()
         if any(p.repetition_penalty > 1.0 for p in params):
@@ -79,4 +84,4 @@ class Sampler:
         K.sample(logits, self._work, self._f32([p.temperature for p in params]),
                  self._i32([max(1, min(p.top_k, self.vocab)) for p in params]),
                  self._f32([p.top_p for p in params]), self._f32(u), out)
-        return out.tolist()
+        return out

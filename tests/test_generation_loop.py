@@ -66,6 +66,27 @@ def gen(engine, **kw):
     return Generator(engine, FakeSampler(), step_entry=Entry, **kw)
 
 
+class AheadEngine(FakeEngine):
+    """The fake engine with the call that takes its tokens from a tensor, as the loop that runs one step
+    ahead of the host uses it."""
+
+    def step_decode(self, slots, tokens):
+        toks = tokens.tolist()
+        assert len(toks) == len(slots)
+        return self.step([Entry(s, [t], [0]) for s, t in zip(slots, toks)])
+
+
+class AheadSampler(FakeSampler):
+    def sample_device(self, logits, params, histories, counters):
+        import torch
+        self.last = (params, histories, counters)
+        return torch.tensor(list(logits), dtype=torch.int32)
+
+
+def gen_ahead(engine, **kw):
+    return Generator(engine, AheadSampler(), step_entry=Entry, **kw)
+
+
 def test_stop_token_is_kept_and_ends_the_sequence():
     e = FakeEngine()
     g = gen(e, max_batch=4, default_stop_ids=[13])
@@ -154,10 +175,15 @@ def test_slots_are_returned_when_a_step_fails():
 def test_sampler_receives_histories_and_counters():
     e = FakeEngine()
     g = gen(e, max_batch=2)
-    sp = SamplingParams(temperature=0.7, seed=3)
+    sp = SamplingParams(temperature=0.7, seed=3, repetition_penalty=1.2)
     g.generate([GenerationRequest([1, 2], 3, sp), GenerationRequest([7], 2, sp)])
     params, hist, counters = g.sampler.last
     assert hist == [[1, 2, 3, 4]] and counters == [(0, 2)] and params == [sp]
+    # histories are only built for the options that read them (they grow with the context)
+    sp = SamplingParams(temperature=0.7, seed=3)
+    g.generate([GenerationRequest([1, 2], 3, sp)])
+    params, hist, counters = g.sampler.last
+    assert hist == [None] and counters == [(0, 2)] and params == [sp]
 
 
 def test_ngram_bans_and_uniforms():
@@ -177,3 +203,45 @@ def test_sampling_params_validation():
         SamplingParams(repetition_penalty=0.0).validate()
     assert SamplingParams(temperature=0.0).is_plain_greedy
     assert not SamplingParams(temperature=0.0, repetition_penalty=1.2).is_plain_greedy
+
+
+SCENARIOS = [
+    dict(reqs=[([10], 20), ([1, 2, 3], 4)], stop=[13], eng={}),
+    dict(reqs=[([3], 6), ([3], 1), ([40], 30), ([7, 8], 5)], stop=[45, 9], eng={}),
+    dict(reqs=[([0, 1, 2, 3, 4], 50)], stop=[], eng=dict(max_seq_len=8, page_size=4, n_pages=8)),
+    dict(reqs=[([i], 2 + i) for i in range(5)], stop=[4], eng=dict(slots=2), max_batch=2),
+    dict(reqs=[([5], 1), ([6], 1)], stop=[], eng={}),
+]
+
+
+@pytest.mark.parametrize("sc", SCENARIOS)
+def test_one_step_ahead_loop_decides_like_the_plain_loop(sc):
+    """Same tokens, reasons and slot discipline whether the host reads a step's tokens before the next
+    step is launched or after; the loop that runs ahead may spend one step more on a request that ended
+    on a stop token, never more."""
+    reqs = [GenerationRequest(list(p), m) for p, m in sc["reqs"]]
+    e0, e1 = FakeEngine(**sc["eng"]), AheadEngine(**sc["eng"])
+    mb = sc.get("max_batch", 4)
+    g0, g1 = gen(e0, max_batch=mb, default_stop_ids=sc["stop"]), gen_ahead(e1, max_batch=mb, default_stop_ids=sc["stop"])
+    r0, r1 = g0.generate(reqs), g1.generate(reqs)
+    assert [(r.tokens, r.finish_reason, r.prompt_tokens) for r in r0] == [(r.tokens, r.finish_reason, r.prompt_tokens) for r in r1]
+    assert not e1.live and sorted(e1.free) == sorted(e0.free)
+    assert g1.stats.generated_tokens == g0.stats.generated_tokens and g1.stats.batches == g0.stats.batches
+    stopped = sum(r.finish_reason == "stop_token" for r in r0)
+    assert g0.stats.decode_steps <= g1.stats.decode_steps <= g0.stats.decode_steps + stopped
+    # every request's tokens went through the engine in order, one at a time after the prompt
+    fed0 = sorted(tuple(t) for st in e0.steps for _, t in st)
+    fed1 = sorted(tuple(t) for st in e1.steps for _, t in st)
+    assert len(fed1) - len(fed0) <= stopped and all(x in fed1 for x in fed0)
+
+
+def test_one_step_ahead_loop_is_left_for_callbacks_and_history_options():
+    e = AheadEngine()
+    g = gen_ahead(e, max_batch=2)
+    calls = []
+    g.sampler.sample = lambda *a: (calls.append("host"), FakeSampler.sample(g.sampler, *a))[1]
+    g.generate([GenerationRequest([1], 3)], lambda i, t: True)
+    g.generate([GenerationRequest([1], 3, SamplingParams(temperature=0.5, repetition_penalty=1.3))])
+    assert len(calls) == 6
+    g.generate([GenerationRequest([1], 3)])
+    assert len(calls) == 6                        # plain requests run ahead: sample_device, not sample
