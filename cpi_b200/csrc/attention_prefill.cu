@@ -1,14 +1,16 @@
 // Prefill attention in bfloat16 on tcgen05: tiles of 128 queries of one head against the paged cache.
 //
-// A CTA owns 128 consecutive tokens of one sequence and one query head.  Warp 4 streams key/value tiles
-// (128 positions = two cache pages, through TMA with the 128-byte swizzle, two stages); one thread of
-// warp 5 issues the MMAs; warps 0-3 are the softmax: thread r owns query row r, so row maxima and sums
-// need no shuffles.  Per key tile:
+// A CTA owns 128 consecutive tokens of one sequence and one query head.  Warp 8 streams key/value tiles
+// (128 positions = two cache pages, through TMA with the 128-byte swizzle, three stages each for keys and
+// values: a tile's load takes about as long as a tile's arithmetic, so it is requested two tiles ahead); one thread of
+// warp 9 issues the MMAs; warps 0-7 are the softmax: threads r and 128 + r own query row r (half of a
+// tile's key columns each), so row maxima and sums need no shuffles.  Per key tile:
 //     S = Q K^T            tcgen05.mma, both operands K-major from shared memory, S in tensor memory
 //                          (two S buffers: the MMAs run two tiles ahead of the softmax)
-//     P = 2^(S*c - m)      read S with tcgen05.ld, mask by position, write P as bf16 into shared memory
-//     O += P V             tcgen05.mma accumulating in tensor memory, V consumed MN-major straight from
-//                          the page layout [position][dim]
+//     P = 2^(S*c - m)      read S with tcgen05.ld, mask by position, write P as bf16 back into tensor memory
+//                          (two P buffers, so the softmax of tile i+1 does not wait for the P V of tile i)
+//     O += P V             tcgen05.mma with P as the A operand from tensor memory, accumulating in tensor
+//                          memory; V consumed MN-major straight from the page layout [position][dim]
 // m is a reference maximum that is raised, and O rescaled in tensor memory, only when the row maximum
 // has outgrown it by 2^8; the division by the row sum comes once, at the end.
 // Masks: key position <= query position, and >= the window's low end (chunk or sliding window).  The
@@ -74,6 +76,16 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
+// the same with the A operand (M x 16 bfloat16, two per 32-bit column) in tensor memory
+__device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t acc) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc) : "memory");
+}
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -91,6 +103,18 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 #pragma unroll
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// the same load without the wait: the caller overlaps it with arithmetic on the chunk before
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void fence_before_sync() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_proxy() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
@@ -136,31 +160,43 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 16 packed columns (32 bfloat16 of this thread's row) into tensor memory; the caller waits once per pass
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t* w) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+      ::"r"(taddr), "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]),
+        "r"(w[8]), "r"(w[9]), "r"(w[10]), "r"(w[11]), "r"(w[12]), "r"(w[13]), "r"(w[14]), "r"(w[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
 // Exponentials are taken against a reference maximum that is only raised when the true row maximum has
 // outgrown it by more than this many powers of two; the accumulated output then needs rescaling only
 // then (rarely after the first tiles), and intermediate values stay below 2^kRescaleSlack.
 constexpr float kRescaleSlack = 8.0f;
 
 template <int D>
-__global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                 const __grid_constant__ CUtensorMap map_k,
                                                                 const __grid_constant__ CUtensorMap map_v, Params p) {
   constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a row
   constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows x 128 bytes
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES;
   constexpr uint32_t KV_BYTES = HALVES * HALF_BYTES;   // one of K or V, 128 positions
-  constexpr uint32_t TMEM_COLS = 512;                  // S twice (128 columns each), then O (D columns)
-  extern __shared__ uint8_t smem_raw[];
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_full, o_full;
+  constexpr uint32_t TMEM_COLS = 512;                  // S twice (128 columns each), O (D columns), P twice (64 each)
+  constexpr int KS = 3;                                // stages of K and of V
+  // (aligned by declaration: with head size 128 the tiles fill what an SM has, there is no room for slack)
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  __shared__ uint64_t q_full, k_full[KS], k_empty[KS], v_full[KS], v_empty[KS], s_full[2], p_full[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
+  __shared__ float xch_s[2][2][128];                   // what the two halves of a row tell each other (maxima by tile parity; at the end, sums)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* smem = smem_raw;
   uint8_t* q_s = smem;
-  uint8_t* k_s = q_s + Q_BYTES;                        // [2 stages]
-  uint8_t* v_s = k_s + 2 * KV_BYTES;                   // [2 stages]
-  uint8_t* p_s = v_s + 2 * KV_BYTES;
+  uint8_t* k_s = q_s + Q_BYTES;                        // [KS stages]
+  uint8_t* v_s = k_s + KS * KV_BYTES;                  // [KS stages]
 
   pdl_launch_dependents();
   pdl_wait();
@@ -175,12 +211,14 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
 
   if (tid == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < KS; ++s) {
       mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1);
     }
-    mbar_init(&p_full, 128); mbar_init(&o_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 256); mbar_init(&o_done[s], 1);
+    }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -191,11 +229,11 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
-  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256;
+  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256, tmem_p = tmem_base_s + 384;
   volatile int* abort_flag = &abort_s;
   bool ok = true;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       // ---- TMA producer: keys and values have barriers of their own, so that the keys of tile i+2 can
       //      come as soon as Q K^T of tile i is done, long before its P V ----
@@ -204,18 +242,18 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
       const int* table = p.page_table + (size_t)slot * p.max_blocks;
       const int last_block = pos_last / PAGE;
       for (int i = 0; i < n_kt; ++i) {
-        const int s = i & 1;
+        const int s = i % KS;
         const int blk0 = (kt_begin + i) * (BKV / PAGE);
         const int n_pages = min(BKV / PAGE, last_block - blk0 + 1);
         const uint32_t bytes = (uint32_t)n_pages * HALVES * (PAGE * 128);
-        if (i >= 2 && !mbar_wait(&k_empty[s], ((i >> 1) - 1) & 1, abort_flag)) break;
+        if (i >= KS && !mbar_wait(&k_empty[s], ((i / KS) - 1) & 1, abort_flag)) break;
         mbar_expect_tx(&k_full[s], bytes);
         for (int pg = 0; pg < n_pages; ++pg) {
           const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
           for (int h = 0; h < HALVES; ++h)
             tma_load_2d(k_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_k, &k_full[s], h * 64, row);
         }
-        if (i >= 2 && !mbar_wait(&v_empty[s], ((i >> 1) - 1) & 1, abort_flag)) break;
+        if (i >= KS && !mbar_wait(&v_empty[s], ((i / KS) - 1) & 1, abort_flag)) break;
         mbar_expect_tx(&v_full[s], bytes);
         for (int pg = 0; pg < n_pages; ++pg) {
           const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
@@ -224,24 +262,31 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       // ---- MMA issuer.  Order: S(0), S(1), then for each tile  O += P V,  S(i+2).  The two S buffers let
       //      Q K^T run two tiles ahead of the softmax; the tensor pipe executes in issue order. ----
       constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0);
       constexpr uint32_t idesc_o = instr_desc(BQ, D, 1);
+      // The descriptors of every operand tile are built once: this one thread issues all the MMAs, and a
+      // descriptor takes it a chain of a dozen dependent instructions (measured: two tiles' worth of MMAs
+      // took twice as long to issue as to run).  A k-step is then one 64-bit addition away (the address
+      // field counts 16-byte units and shared memory ends far below the field's range).
+      const uint64_t dq = smem_desc(smem_u32(q_s), 16, 1024);
+      const uint64_t dk0 = smem_desc(smem_u32(k_s), 16, 1024), dv0 = smem_desc(smem_u32(v_s), HALF_BYTES, 1024);
+      constexpr uint64_t kStageUnits = KV_BYTES >> 4;     // a stage further, in the descriptor's 16-byte units
       auto issue_qk = [&](int i) -> bool {
-        const int s = i & 1;
-        if (!mbar_wait(&k_full[s], (i >> 1) & 1, abort_flag)) return false;
+        const int s = i & 1, st = i % KS;
+        if (!mbar_wait(&k_full[st], (i / KS) & 1, abort_flag)) return false;
         fence_after_sync();
-        const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * KV_BYTES);
+        const uint64_t dk = dk0 + (uint64_t)st * kStageUnits;
 #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks) {
-          const uint32_t off = (ks >> 2) * HALF_BYTES + (ks & 3) * 32;
-          umma_bf16(tmem_s + s * 128, smem_desc(qa + off, 16, 1024), smem_desc(ka + off, 16, 1024), idesc_s, ks > 0);
+          const uint64_t off = (uint64_t)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4);
+          umma_bf16(tmem_s + s * 128, dq + off, dk + off, idesc_s, ks > 0);
         }
         umma_commit(&s_full[s]);
-        umma_commit(&k_empty[s]);
+        umma_commit(&k_empty[st]);
         return true;
       };
       ok = mbar_wait(&q_full, 0, abort_flag);
@@ -249,49 +294,50 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
       if (ok && n_kt > 1) ok = issue_qk(1);
       for (int i = 0; i < n_kt && ok; ++i) {
         const int s = i & 1;
-        ok = mbar_wait(&p_full, i & 1, abort_flag) && mbar_wait(&v_full[s], (i >> 1) & 1, abort_flag);
+        const int st = i % KS;
+        ok = mbar_wait(&p_full[s], (i >> 1) & 1, abort_flag) && mbar_wait(&v_full[st], (i / KS) & 1, abort_flag);
         if (!ok) break;
         fence_after_sync();
-        const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * KV_BYTES);
+        const uint64_t dv = dv0 + (uint64_t)st * kStageUnits;
 #pragma unroll
-        for (int j = 0; j < BKV / 16; ++j) {
-          const uint32_t poff = (j >> 2) * HALF_BYTES + (j & 3) * 32;
-          umma_bf16(tmem_o, smem_desc(pa + poff, 16, 1024), smem_desc(va + j * 2048, HALF_BYTES, 1024), idesc_o,
-                    (i > 0 || j > 0) ? 1u : 0u);
-        }
-        umma_commit(&o_full);
-        umma_commit(&v_empty[s]);
+        for (int j = 0; j < BKV / 16; ++j)
+          umma_bf16_a_tmem(tmem_o, tmem_p + s * 64 + j * 8, dv + (uint64_t)(j * (2048 >> 4)), idesc_o,
+                           (i > 0 || j > 0) ? 1u : 0u);
+        umma_commit(&o_done[s]);
+        umma_commit(&v_empty[st]);
         if (i + 2 < n_kt) ok = issue_qk(i + 2);        // S[s] is free: the softmax of tile i has read it
       }
     }
   } else {
-    // ---- softmax: thread `row` owns one query row; O stays in tensor memory ----
-    const int row = tid;
+    // ---- softmax: eight warps.  Query row r belongs to threads r and 128 + r; the first takes the key
+    //      columns 0-63 of a tile, the second 64-127 (a warp may touch the 32 lanes of tensor memory given
+    //      by its number modulo 4, so warps w and w + 4 share rows).  Two warps per scheduler hide each
+    //      other's latencies; the halves meet once per tile, at a named barrier, to agree on the row
+    //      maxima.  O stays in tensor memory. ----
+    const int row = tid & 127, half = tid >> 7;
     const bool live = row < rows;
     const int qp = live ? p.token_pos[tok0 + row] : -1;
     const int lo = live ? window_low(p.window_kind, p.window_size, qp) : 0;
-    const uint32_t lane_addr = (uint32_t)(warp * 32) << 16;
-    float m_ref = -1e30f, l_run = 0.f;                  // reference maximum of the exponentials, row sum
-
+    const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
+    constexpr int HC = BKV / 2;                         // key columns of a tile per thread
+    const int c0 = half * HC;
+    float m_ref = -1e30f, l_run = 0.f;                  // reference maximum of the exponentials; this half's row sum
+    const float sc = p.scale_log2;                      // > 0: the maximum may be taken before scaling
     const int lo_last = window_low(p.window_kind, p.window_size, pos_last);
-    for (int i = 0; i < n_kt && ok; ++i) {
+    for (int i = 0; i < n_kt; ++i) {
       const int key0 = (kt_begin + i) * BKV;
-      const uint32_t s_addr = tmem_s + (i & 1) * 128 + lane_addr;
-      // (the tensor-memory loads and the vote below are warp-wide: a warp gives up as a whole)
-      ok = __all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag));
-      if (!ok) break;
-      // P V of the previous tile must be done before P is overwritten and before O may be rescaled
-      if (i > 0) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&o_full, (i - 1) & 1, abort_flag));
-        if (!ok) break;
-      }
-      fence_after_sync();
-      // the last tile: zero the value rows beyond the newest position (this thread: key row `row`)
-      if (i == n_kt - 1) {
-        ok = __all_sync(0xffffffffu, mbar_wait(&v_full[i & 1], (i >> 1) & 1, abort_flag));
-        if (!ok) break;
-        if (key0 + row > pos_last) {
-          uint8_t* vs = v_s + (i & 1) * KV_BYTES;
+      const uint32_t s_addr = tmem_s + (i & 1) * 128 + lane_addr + c0;
+      const uint32_t p_addr = tmem_p + (i & 1) * 64 + lane_addr + (c0 >> 1);
+      // (tensor-memory loads and votes are warp-wide: a warp gives up as a whole.  Nobody leaves the loop
+      // before the named barrier below: the other half would wait there for ever.)
+      bool okl = __all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag));
+      // this tile's P buffer was last read by P V of tile i - 2
+      if (okl && i >= 2) okl = __all_sync(0xffffffffu, mbar_wait(&o_done[i & 1], ((i >> 1) - 1) & 1, abort_flag));
+      // the last tile: zero the value rows beyond the newest position (thread r of the first half: key row r)
+      if (okl && i == n_kt - 1 && half == 0) {
+        okl = __all_sync(0xffffffffu, mbar_wait(&v_full[i % KS], (i / KS) & 1, abort_flag));
+        if (okl && key0 + row > pos_last) {
+          uint8_t* vs = v_s + (i % KS) * KV_BYTES;
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
             uint4* r4 = reinterpret_cast<uint4*>(vs + h * HALF_BYTES + row * 128);
@@ -299,83 +345,100 @@ __global__ void __launch_bounds__(192) attention_prefill_kernel(const __grid_con
             for (int q = 0; q < 8; ++q) r4[q] = make_uint4(0, 0, 0, 0);
           }
         }
+        fence_async_proxy();                             // the MMA reads V through the async proxy
       }
-      // One pass over S: P = 2^(s - m_ref) as bf16 into shared memory (K-major, swizzled), the row sum, and
-      // the row maximum.  A tile that lies wholly inside every row's window needs no position tests.
+      fence_after_sync();
+      // One pass over this thread's half of S: P = 2^(s*c - m_ref) as bf16 into tensor memory, the sum, and
+      // the maximum.  A tile that lies wholly inside every row's window needs no position tests.
       const bool no_mask = key0 + BKV - 1 <= pos_first && key0 >= lo_last;
-      float mx, ls;
+      float mx = -INFINITY, ls = 0.f;
       auto pass = [&](const float ref) {
-        mx = -INFINITY;
-        ls = 0.f;
-#pragma unroll 1
-        for (int c = 0; c < BKV; c += 32) {
+        const float nref = -ref;
+        float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, ls4[4] = {0.f, 0.f, 0.f, 0.f};
+        uint32_t raw[2][32];
+        tmem_ld32_issue(s_addr, raw[0]);
+#pragma unroll
+        for (int cc = 0; cc < HC / 32; ++cc) {
+          const int c = cc * 32;
+          tmem_wait_ld();                                  // chunk cc has arrived
+          if (cc + 1 < HC / 32) tmem_ld32_issue(s_addr + c + 32, raw[(cc + 1) & 1]);   // the next one is on its way
           float v[32];
-          tmem_ld32(s_addr + c, v);
+#pragma unroll
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[cc & 1][e]);
           if (no_mask) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              const float x = v[e] * p.scale_log2;
-              mx = fmaxf(mx, x);
-              v[e] = exp2f(x - ref);
-              ls += v[e];
-            }
+            for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = exp2_fast(fmaf(v[e], sc, nref));
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              const int kp = key0 + c + e;
+              const int kp = key0 + c0 + c + e;
               const bool in = kp <= qp && kp >= lo;
-              const float x = v[e] * p.scale_log2;
-              if (in) mx = fmaxf(mx, x);
-              v[e] = in ? exp2f(x - ref) : 0.f;
-              ls += v[e];
+              if (in) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
+              v[e] = in ? exp2_fast(fmaf(v[e], sc, nref)) : 0.f;
             }
           }
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = c + g * 8;
-            const int chunk = (col & 63) >> 3;
-            uint4 w = make_uint4(pack_bf16(v[g * 8], v[g * 8 + 1]), pack_bf16(v[g * 8 + 2], v[g * 8 + 3]),
-                                 pack_bf16(v[g * 8 + 4], v[g * 8 + 5]), pack_bf16(v[g * 8 + 6], v[g * 8 + 7]));
-            *reinterpret_cast<uint4*>(p_s + (col >> 6) * HALF_BYTES + row * 128 + ((chunk ^ (row & 7)) << 4)) = w;
-          }
+          for (int e = 0; e < 32; ++e) ls4[e & 3] += v[e];
+          uint32_t w[16];
+#pragma unroll
+          for (int g = 0; g < 16; ++g) w[g] = pack_bf16(v[2 * g], v[2 * g + 1]);
+          tmem_st16_nowait(p_addr + (c >> 1), w);
         }
+        mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
+        ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
+        tmem_wait_st();
       };
       // Optimistic: against the reference maximum the row already has.  Only if some row of the warp has
       // outgrown its reference (always on its first tile) is the reference raised, O rescaled in tensor
-      // memory, and the pass repeated.  (Load and store of tensor memory are warp-wide: every lane takes
-      // part, with factor 1 where nothing changes.)
-      pass(m_ref);
+      // memory, and the pass repeated.  Both halves of a row see the same maximum and so decide alike.
+      if (okl) pass(m_ref);
+      xch_s[i & 1][half][row] = mx;                       // (two buffers: the next tile writes the other one)
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (abort_s) break;                                // the same for all 256 threads
+      mx = fmaxf(mx, xch_s[i & 1][half ^ 1][row]);
       const bool grow = mx > m_ref + (m_ref < -1e29f ? 0.f : kRescaleSlack);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_ref;
         const float f = exp2f(m_ref - m_new);
+        bool ok2 = true;
         if (i > 0) {
+          // O is rescaled in place, half of its columns by each half: every P V issued so far must have landed
+          ok2 = __all_sync(0xffffffffu, mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag));
+          fence_after_sync();
+          if (ok2) {
 #pragma unroll 1
-          for (int c = 0; c < D; c += 32) {
-            float v[32];
-            tmem_ld32(tmem_o + lane_addr + c, v);
+            for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
+              float v[32];
+              tmem_ld32(tmem_o + lane_addr + c, v);
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] *= f;
-            tmem_st32(tmem_o + lane_addr + c, v);
+              for (int e = 0; e < 32; ++e) v[e] *= f;
+              tmem_st32(tmem_o + lane_addr + c, v);
+            }
           }
         }
         l_run *= f;
         m_ref = m_new;
-        pass(m_ref);
+        if (ok2) pass(m_ref);
       }
       l_run += ls;
-      fence_async_proxy();
       fence_before_sync();
-      mbar_arrive(&p_full);
+      mbar_arrive(&p_full[i & 1]);
     }
-    // the output: O / l once the last P V is done
-    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_full, (n_kt - 1) & 1, abort_flag));
+    // the output: O / l once the last P V is done; each half writes half of the columns
+    asm volatile("bar.sync 1, 256;" ::: "memory");      // the maxima of the last tile have been read
+    xch_s[0][half][row] = l_run;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float l_all = xch_s[0][0][row] + xch_s[0][1][row];
+    ok = !abort_s && n_kt > 0;
+    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_done[(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1, abort_flag));
     fence_after_sync();
     if (ok) {
-      const float inv = 1.0f / fmaxf(l_run, 1e-20f);
+      const float inv = 1.0f / fmaxf(l_all, 1e-20f);
       __nv_bfloat16* dst = p.out + ((size_t)(tok0 + row) * p.n_heads + head) * D;
 #pragma unroll 1
-      for (int c = 0; c < D; c += 32) {
+      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
         float v[32];
         tmem_ld32(tmem_o + lane_addr + c, v);
         if (live) {
@@ -433,15 +496,15 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
                 n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag};
   dim3 grid(n_tiles, n_heads);
   const int halves = head_dim / 64;
-  const int smem = halves * 128 * 128 * (1 + 4) + 2 * 128 * 128 + 1024;
+  const int smem = halves * 128 * 128 * (1 + 6);             // Q, three stages of K and of V
   if (head_dim == 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    cpi::launch_pdl(pre::attention_prefill_kernel<128>, grid, 192, smem, stream, mq, mk, mv, p);
+    cpi::launch_pdl(pre::attention_prefill_kernel<128>, grid, 320, smem, stream, mq, mk, mv, p);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    cpi::launch_pdl(pre::attention_prefill_kernel<64>, grid, 192, smem, stream, mq, mk, mv, p);
+    cpi::launch_pdl(pre::attention_prefill_kernel<64>, grid, 320, smem, stream, mq, mk, mv, p);
   }
   return check_launch("attention_prefill");
 }
