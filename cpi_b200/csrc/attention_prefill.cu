@@ -81,6 +81,33 @@ __device__ __forceinline__ void umma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_
   asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
                ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(acc) : "memory");
 }
+// One lane of a converged warp.  The warp that issues the MMAs runs its loop with all 32 lanes (so that the
+// compiler sees uniform values and keeps descriptors and loop counters on the uniform datapath) and only
+// the tcgen05 instructions themselves sit under this predicate.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+  return pred != 0;
+}
+// accumulate known at compile time: no run-time predicate set-up per instruction
+template <bool ACC>
+__device__ __forceinline__ void umma_bf16_c(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc) {
+  if (ACC)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc) : "memory");
+  else
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc) : "memory");
+}
+template <bool ACC>
+__device__ __forceinline__ void umma_bf16_a_tmem_c(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc) {
+  if (ACC)
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.eq.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc) : "memory");
+  else
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, 0, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc) : "memory");
+}
 __device__ __forceinline__ float exp2_fast(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -190,7 +217,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
   __shared__ uint64_t q_full, k_full[KS], k_empty[KS], v_full[KS], v_empty[KS], s_full[2], p_full[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
-  __shared__ float xch_s[2][2][128];                   // what the two halves of a row tell each other (maxima by tile parity; at the end, sums)
+  __shared__ float xch_s[1][2][128];                   // the two halves of a row add their sums at the end
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* smem = smem_raw;
@@ -217,7 +244,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 256); mbar_init(&o_done[s], 1);
+      mbar_init(&p_full[s], 8); mbar_init(&o_done[s], 1);
     }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -263,57 +290,69 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       }
     }
   } else if (warp == 9) {
-    if (lane == 0) {
-      // ---- MMA issuer.  Order: S(0), S(1), then for each tile  O += P V,  S(i+2).  The two S buffers let
-      //      Q K^T run two tiles ahead of the softmax; the tensor pipe executes in issue order. ----
-      constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0);
-      constexpr uint32_t idesc_o = instr_desc(BQ, D, 1);
-      // The descriptors of every operand tile are built once: this one thread issues all the MMAs, and a
-      // descriptor takes it a chain of a dozen dependent instructions (measured: two tiles' worth of MMAs
-      // took twice as long to issue as to run).  A k-step is then one 64-bit addition away (the address
-      // field counts 16-byte units and shared memory ends far below the field's range).
-      const uint64_t dq = smem_desc(smem_u32(q_s), 16, 1024);
-      const uint64_t dk0 = smem_desc(smem_u32(k_s), 16, 1024), dv0 = smem_desc(smem_u32(v_s), HALF_BYTES, 1024);
-      constexpr uint64_t kStageUnits = KV_BYTES >> 4;     // a stage further, in the descriptor's 16-byte units
-      auto issue_qk = [&](int i) -> bool {
-        const int s = i & 1, st = i % KS;
-        if (!mbar_wait(&k_full[st], (i / KS) & 1, abort_flag)) return false;
-        fence_after_sync();
-        const uint64_t dk = dk0 + (uint64_t)st * kStageUnits;
+    // ---- MMA issuer.  Order: S(0), S(1), then for each tile  O += P V,  S(i+2).  The two S buffers let
+    //      Q K^T run two tiles ahead of the softmax; the tensor pipe executes in issue order.
+    //      This warp shares its scheduler with two softmax warps that always have something to issue, so
+    //      every instruction it spends between two MMAs delays the tensor pipe (measured: with descriptor
+    //      arithmetic, divisions by the stage count and a predicate per MMA, issuing a tile's 16 MMAs took
+    //      2.4 times as long as running them).  Hence: the whole warp runs the loop (uniform values), stage
+    //      and phase are counters, descriptors are built once and advanced by additions, and the accumulate
+    //      flags are compile-time. ----
+    constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0);
+    constexpr uint32_t idesc_o = instr_desc(BQ, D, 1);
+    constexpr uint64_t kStageUnits = KV_BYTES >> 4;     // a stage further, in the descriptor's 16-byte units
+    const uint64_t dq = smem_desc(smem_u32(q_s), 16, 1024);
+    const uint64_t dk0 = smem_desc(smem_u32(k_s), 16, 1024), dv0 = smem_desc(smem_u32(v_s), HALF_BYTES, 1024);
+    int qk_st = 0, qk_ph = 0;                            // stage and phase of the next Q K^T; likewise for P V
+    uint64_t dk = dk0;
+    auto issue_qk = [&](int s) -> bool {                 // s = S buffer
+      if (!__all_sync(0xffffffffu, mbar_wait(&k_full[qk_st], qk_ph, abort_flag))) return false;
+      fence_after_sync();
+      if (elect_one()) {
+        umma_bf16_c<false>(tmem_s + s * 128, dq, dk, idesc_s);
 #pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks) {
+        for (int ks = 1; ks < D / 16; ++ks) {
           const uint64_t off = (uint64_t)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4);
-          umma_bf16(tmem_s + s * 128, dq + off, dk + off, idesc_s, ks > 0);
+          umma_bf16_c<true>(tmem_s + s * 128, dq + off, dk + off, idesc_s);
         }
         umma_commit(&s_full[s]);
-        umma_commit(&k_empty[st]);
-        return true;
-      };
-      ok = mbar_wait(&q_full, 0, abort_flag);
-      ok = ok && issue_qk(0);
-      if (ok && n_kt > 1) ok = issue_qk(1);
-      for (int i = 0; i < n_kt && ok; ++i) {
-        const int s = i & 1;
-        const int st = i % KS;
-        ok = mbar_wait(&p_full[s], (i >> 1) & 1, abort_flag) && mbar_wait(&v_full[st], (i / KS) & 1, abort_flag);
-        if (!ok) break;
-        fence_after_sync();
-        const uint64_t dv = dv0 + (uint64_t)st * kStageUnits;
-#pragma unroll
-        for (int j = 0; j < BKV / 16; ++j)
-          umma_bf16_a_tmem(tmem_o, tmem_p + s * 64 + j * 8, dv + (uint64_t)(j * (2048 >> 4)), idesc_o,
-                           (i > 0 || j > 0) ? 1u : 0u);
-        umma_commit(&o_done[s]);
-        umma_commit(&v_empty[st]);
-        if (i + 2 < n_kt) ok = issue_qk(i + 2);        // S[s] is free: the softmax of tile i has read it
+        umma_commit(&k_empty[qk_st]);
       }
+      __syncwarp();
+      if (++qk_st == KS) { qk_st = 0; qk_ph ^= 1; dk = dk0; } else { dk += kStageUnits; }
+      return true;
+    };
+    ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, abort_flag));
+    ok = ok && issue_qk(0);
+    if (ok && n_kt > 1) ok = issue_qk(1);
+    int pv_st = 0, pv_ph = 0, sp_ph = 0;                 // sp_ph: phase of the S / P buffer pair
+    uint64_t dv = dv0;
+    for (int i = 0; i < n_kt && ok; ++i) {
+      const int s = i & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait(&p_full[s], sp_ph, abort_flag) && mbar_wait(&v_full[pv_st], pv_ph, abort_flag));
+      if (!ok) break;
+      fence_after_sync();
+      if (elect_one()) {
+        const uint32_t pa = tmem_p + s * 64;
+        if (i > 0) umma_bf16_a_tmem_c<true>(tmem_o, pa, dv, idesc_o);
+        else umma_bf16_a_tmem_c<false>(tmem_o, pa, dv, idesc_o);
+#pragma unroll
+        for (int j = 1; j < BKV / 16; ++j)
+          umma_bf16_a_tmem_c<true>(tmem_o, pa + j * 8, dv + (uint64_t)(j * (2048 >> 4)), idesc_o);
+        umma_commit(&o_done[s]);
+        umma_commit(&v_empty[pv_st]);
+      }
+      __syncwarp();
+      if (++pv_st == KS) { pv_st = 0; pv_ph ^= 1; dv = dv0; } else { dv += kStageUnits; }
+      sp_ph ^= s;                                        // both buffers of the pair done: next phase
+      if (i + 2 < n_kt) ok = issue_qk(s);                // S[s] is free: the softmax of tile i has read it
     }
   } else {
     // ---- softmax: eight warps.  Query row r belongs to threads r and 128 + r; the first takes the key
     //      columns 0-63 of a tile, the second 64-127 (a warp may touch the 32 lanes of tensor memory given
     //      by its number modulo 4, so warps w and w + 4 share rows).  Two warps per scheduler hide each
-    //      other's latencies; the halves meet once per tile, at a named barrier, to agree on the row
-    //      maxima.  O stays in tensor memory. ----
+    //      other's latencies.  Each half reads the whole row for its maximum, so the halves need not meet
+    //      until the row sums are added at the end.  O stays in tensor memory. ----
     const int row = tid & 127, half = tid >> 7;
     const bool live = row < rows;
     const int qp = live ? p.token_pos[tok0 + row] : -1;
@@ -326,10 +365,9 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
     const int lo_last = window_low(p.window_kind, p.window_size, pos_last);
     for (int i = 0; i < n_kt; ++i) {
       const int key0 = (kt_begin + i) * BKV;
-      const uint32_t s_addr = tmem_s + (i & 1) * 128 + lane_addr + c0;
+      const uint32_t s_row = tmem_s + (i & 1) * 128 + lane_addr;
       const uint32_t p_addr = tmem_p + (i & 1) * 64 + lane_addr + (c0 >> 1);
-      // (tensor-memory loads and votes are warp-wide: a warp gives up as a whole.  Nobody leaves the loop
-      // before the named barrier below: the other half would wait there for ever.)
+      // (tensor-memory loads and votes are warp-wide: a warp gives up as a whole)
       bool okl = __all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag));
       // this tile's P buffer was last read by P V of tile i - 2
       if (okl && i >= 2) okl = __all_sync(0xffffffffu, mbar_wait(&o_done[i & 1], ((i >> 1) - 1) & 1, abort_flag));
@@ -356,35 +394,45 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
         const float nref = -ref;
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, ls4[4] = {0.f, 0.f, 0.f, 0.f};
         uint32_t raw[2][32];
-        tmem_ld32_issue(s_addr, raw[0]);
+        // The whole row is read for its maximum (so that the two halves of a row decide alike without
+        // talking to each other: no barrier per tile, and the halves drift apart, one's exponentials
+        // under the other's waits), the exponentials are taken of this thread's half only.  Chunk order:
+        // the other half's two chunks first, then this half's.
+        const int first = (half ^ 1) * HC;
+        tmem_ld32_issue(s_row + first, raw[0]);
 #pragma unroll
-        for (int cc = 0; cc < HC / 32; ++cc) {
-          const int c = cc * 32;
+        for (int cc = 0; cc < BKV / 32; ++cc) {
+          const int c = ((cc < 2 ? first : c0) + (cc & 1) * 32);     // column of this chunk within the tile
           tmem_wait_ld();                                  // chunk cc has arrived
-          if (cc + 1 < HC / 32) tmem_ld32_issue(s_addr + c + 32, raw[(cc + 1) & 1]);   // the next one is on its way
+          if (cc + 1 < BKV / 32)
+            tmem_ld32_issue(s_row + (cc + 1 < 2 ? first : c0) + ((cc + 1) & 1) * 32, raw[(cc + 1) & 1]);
           float v[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[cc & 1][e]);
           if (no_mask) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
+            if (cc >= 2) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = exp2_fast(fmaf(v[e], sc, nref));
+              for (int e = 0; e < 32; ++e) v[e] = exp2_fast(fmaf(v[e], sc, nref));
+            }
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              const int kp = key0 + c0 + c + e;
+              const int kp = key0 + c + e;
               const bool in = kp <= qp && kp >= lo;
               if (in) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
-              v[e] = in ? exp2_fast(fmaf(v[e], sc, nref)) : 0.f;
+              if (cc >= 2) v[e] = in ? exp2_fast(fmaf(v[e], sc, nref)) : 0.f;
             }
           }
+          if (cc >= 2) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) ls4[e & 3] += v[e];
-          uint32_t w[16];
+            for (int e = 0; e < 32; ++e) ls4[e & 3] += v[e];
+            uint32_t w[16];
 #pragma unroll
-          for (int g = 0; g < 16; ++g) w[g] = pack_bf16(v[2 * g], v[2 * g + 1]);
-          tmem_st16_nowait(p_addr + (c >> 1), w);
+            for (int g = 0; g < 16; ++g) w[g] = pack_bf16(v[2 * g], v[2 * g + 1]);
+            tmem_st16_nowait(p_addr + ((cc & 1) * 16), w);
+          }
         }
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
         ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
@@ -392,12 +440,9 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       };
       // Optimistic: against the reference maximum the row already has.  Only if some row of the warp has
       // outgrown its reference (always on its first tile) is the reference raised, O rescaled in tensor
-      // memory, and the pass repeated.  Both halves of a row see the same maximum and so decide alike.
-      if (okl) pass(m_ref);
-      xch_s[i & 1][half][row] = mx;                       // (two buffers: the next tile writes the other one)
-      asm volatile("bar.sync 1, 256;" ::: "memory");
-      if (abort_s) break;                                // the same for all 256 threads
-      mx = fmaxf(mx, xch_s[i & 1][half ^ 1][row]);
+      // memory, and the pass repeated.  Both halves of a row compute the same maximum and so decide alike.
+      if (!okl) break;
+      pass(m_ref);
       const bool grow = mx > m_ref + (m_ref < -1e29f ? 0.f : kRescaleSlack);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_ref;
@@ -424,10 +469,10 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       }
       l_run += ls;
       fence_before_sync();
-      mbar_arrive(&p_full[i & 1]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[i & 1]);        // one arrival per warp
     }
     // the output: O / l once the last P V is done; each half writes half of the columns
-    asm volatile("bar.sync 1, 256;" ::: "memory");      // the maxima of the last tile have been read
     xch_s[0][half][row] = l_run;
     asm volatile("bar.sync 1, 256;" ::: "memory");
     const float l_all = xch_s[0][0][row] + xch_s[0][1][row];
