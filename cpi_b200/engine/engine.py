@@ -64,8 +64,10 @@ class Engine:
         # Decode steps (one token per sequence) are captured into CUDA graphs, one per (sequences, wanted
         # rows, context bucket): the first step of a kind runs eagerly, the second is captured, later ones
         # replay.  What changes from step to step -- tokens, positions, slots, page tables -- lives in
-        # device buffers with fixed addresses that are refilled before each replay.
-        self.use_graphs = True
+        # device buffers with fixed addresses that are refilled before each replay.  Only if every part of the
+        # model declares itself safe for that (`Part.graph_safe`): a part that looks at host values of a step
+        # would be replayed with those of the step that was captured.
+        self.use_graphs = all(getattr(part, "graph_safe", False) for part in self.model.all_parts())
         self._graphs = {}
         self.graph_kernel_launches = 0       # kernels run by graph replays (they are not host launches)
         self._routing_capture = False

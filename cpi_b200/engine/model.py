@@ -24,6 +24,14 @@ class Layer:
     def parts(self):
         return (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward)
 
+    def all_parts(self):
+        """Every object whose code runs in a step of this layer (the mixer's position encoding included)."""
+        out = [self.block, *self.parts()]
+        pos = getattr(self.mixer, "position", None)
+        if pos is not None:
+            out.append(pos)
+        return out
+
 
 class DecoderModel:
     def __init__(self, spec: ModelSpec, dtype: torch.dtype, device, workspace: Workspace | None = None):
@@ -53,6 +61,14 @@ class DecoderModel:
         self.err_flag = None
 
     # ---- weights ---------------------------------------------------------------------------------
+    def all_parts(self) -> list:
+        """Every part object of the model (layers' blocks, norms, mixers with their position encodings,
+        feed-forwards, the final norm)."""
+        out = [self.final_norm]
+        for layer in self.layers:
+            out += layer.all_parts()
+        return out
+
     def requirements(self) -> list:
         V, H = self.spec.vocab_size, self.spec.hidden_size
         reqs = [TensorReq(self.embed_name, (V, H))]

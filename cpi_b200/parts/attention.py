@@ -29,6 +29,7 @@ use_tensor_core_kernels = True
 
 @register_mixer("attention")
 class AttentionMixer(Mixer):
+    graph_safe = True
     def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
         super().__init__(spec, prefix)
         p = spec.params

@@ -19,7 +19,9 @@ stream [tokens, hidden], updated in place.  A mixer must give the same result fo
 the sequence's tokens come in one step or one at a time; what it needs to remember lives in `cache`.
 
 A new kind is added with `register_mixer("name")(cls)` (likewise for the others) and is then chosen
-by a `PartSpec` of that kind; nothing else in the library changes.
+by a `PartSpec` of that kind; nothing else in the library changes.  A part whose step depends on the step
+only through device buffers sets `graph_safe = True`; decode steps of a model are captured into CUDA
+graphs only if all its parts do.
 """
 from __future__ import annotations
 
@@ -31,6 +33,12 @@ from ..config.spec import PartSpec
 
 
 class Part:
+    # Whether a decode step through this part may be captured into a CUDA graph and replayed: its launches
+    # must then depend on the step only through device buffers (tokens, positions, slots, page tables),
+    # never through host values such as `batch.slots`, data-dependent shapes or a synchronisation.  A part
+    # says so itself; the default is no, and the engine replays graphs only if every part of the model does.
+    graph_safe = False
+
     def __init__(self, spec: PartSpec, prefix: str = ""):
         self.spec, self.prefix = spec, prefix
 

@@ -7,6 +7,7 @@ from .base import Block, register_block
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
+    graph_safe = True
     def __init__(self, spec, prefix="", **_):
         super().__init__(spec, prefix)
 

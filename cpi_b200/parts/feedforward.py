@@ -32,6 +32,7 @@ def _stack(a, b):
 
 @register_feed_forward("dense_swiglu")
 class DenseSwiGLU(FeedForward):
+    graph_safe = True
     def __init__(self, spec, prefix="", workspace=None, names=("feed_forward.gate_proj.weight",
                                                                 "feed_forward.up_proj.weight",
                                                                 "feed_forward.down_proj.weight")):
@@ -59,6 +60,7 @@ class DenseSwiGLU(FeedForward):
 
 @register_feed_forward("moe_swiglu")
 class MoESwiGLU(FeedForward):
+    graph_safe = True
     def __init__(self, spec, prefix="", workspace=None):
         super().__init__(spec, prefix)
         p = spec.params

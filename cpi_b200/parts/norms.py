@@ -11,6 +11,7 @@ from .base import Norm, register_norm
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
     """params: size, eps, weight (tensor name relative to the prefix, or None for a weightless norm)."""
+    graph_safe = True
 
     def __init__(self, spec, prefix="", workspace=None, tag="norm"):
         super().__init__(spec, prefix)

@@ -38,6 +38,7 @@ def llama3_frequencies(head_dim: int, theta: float, scaling) -> np.ndarray:
 class RotaryPosition(Position):
     """params: head_dim, theta, pairing ("half_split" pairs (d, d+D/2); "interleaved" pairs (2d, 2d+1)),
     scaling (None or the llama3 dictionary)."""
+    graph_safe = True
 
     def __init__(self, spec, prefix=""):
         super().__init__(spec, prefix)
@@ -56,5 +57,6 @@ class RotaryPosition(Position):
 
 @register_position("none")
 class NoPosition(Position):
+    graph_safe = True
     interleaved = False
     inv_freq = None

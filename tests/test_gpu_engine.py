@@ -22,6 +22,7 @@ def engine(name, dtype, max_tokens=1024):
     if key not in _engines:
         _engines[key] = Engine.from_model_dir(model_dir(name), dtype=dtype, max_tokens=max_tokens)
     e = _engines[key]
+    assert e.use_graphs, "every part of the library's own model is safe to capture"
     assert not e.cache.live_slots(), "a previous test left slots behind"
     return e
 

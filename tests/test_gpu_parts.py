@@ -234,6 +234,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     W = {n: t.float() for n, t in drawn.items()}
     e = Engine(spec, DictSource(drawn), dtype="float32", max_tokens=512)
     assert not e.cache.groups and len(e.cache.state) == 4          # no keys or values, two states per entry
+    assert not e.use_graphs                  # the toy mixer reads host values of the step and does not claim otherwise
 
     def plain(tokens):
         x = W["emb.weight"][tokens]
@@ -261,3 +262,121 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
         e.release_slot(sa)
         for got, want in rows:
             assert float((got - want).abs().max()) <= 2e-5 * float(ra.abs().max())
+
+
+# ------------------------------------------------------------------- toy feed-forward with routing, toy positions
+def _register_toy_ffn_and_position():
+    """Two more kinds defined here, outside the library: a feed-forward that routes each token to one of its
+    ReLU experts by the largest of the token's first features, and a position encoding that the attention
+    mixer consumes like rotary frequencies (positions divided by a constant: linear interpolation)."""
+    import numpy as np
+    from cpi_b200.parts import FeedForward, Position, register_feed_forward, register_position
+    from cpi_b200.weights import TensorReq
+
+    @register_feed_forward("toy_routed_relu")
+    class RoutedRelu(FeedForward):
+        def __init__(self, spec, prefix="", workspace=None):
+            super().__init__(spec, prefix)
+            self.h, self.i, self.e = int(spec["hidden_size"]), int(spec["inner"]), int(spec["experts"])
+
+        def requirements(self):
+            return [TensorReq(self.prefix + "ffn.w1", (self.e, self.i, self.h)),
+                    TensorReq(self.prefix + "ffn.w2", (self.e, self.h, self.i))]
+
+        def load(self, source, device):
+            self.w1 = source.get(self.prefix + "ffn.w1", device).float()
+            self.w2 = source.get(self.prefix + "ffn.w2", device).float()
+
+        def forward(self, h, residual, batch):
+            x = h.float()
+            which = x[:, :self.e].argmax(-1)                       # the routing: a function of the token alone
+            for e in range(self.e):
+                rows = (which == e).nonzero().flatten()
+                if rows.numel():
+                    residual[rows] += torch.relu(x[rows] @ self.w1[e].T) @ self.w2[e].T
+
+    @register_position("toy_interpolated")
+    class Interpolated(Position):
+        interleaved = True
+
+        def __init__(self, spec, prefix=""):
+            super().__init__(spec, prefix)
+            d, div = int(spec["head_dim"]), float(spec["divide_by"])
+            self.frequencies = (np.float32(1.0 / div) *
+                                np.float32(spec["theta"]) ** (-np.arange(d // 2, dtype=np.float32) * 2 / d)).astype(np.float32)
+            self.inv_freq = None
+
+        def prepare(self, device):
+            self.inv_freq = torch.from_numpy(self.frequencies).to(device)
+
+    return RoutedRelu, Interpolated
+
+
+def test_toy_routed_feed_forward_and_toy_positions_register_build_and_step():
+    """A model whose feed-forward and position encoding are defined in this test, around the library's
+    attention mixer: whole prompts, an unequal batch, and decoding, against plain formulas (in float32: the
+    toy routing is an arg-max of raw features, which bfloat16 rounding would flip now and then)."""
+    dtype = "float32"
+    from cpi_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from cpi_b200.engine import Engine, StepEntry
+    from cpi_b200.engine.model import tensor_requirements
+    from cpi_b200.weights import DictSource, RandomSource
+    _, Interp = _register_toy_ffn_and_position()
+    H, V, NH, NKV, D, I, E = 64, 120, 4, 2, 32, 48, 3
+    pos = PartSpec("toy_interpolated", {"head_dim": D, "theta": 5000.0, "divide_by": 4.0})
+    norm = lambda w: PartSpec("rmsnorm", {"size": H, "eps": 1e-5, "weight": w})
+    attn = PartSpec("attention", {"hidden_size": H, "num_heads": NH, "num_kv_heads": NKV, "head_dim": D,
+                                  "softmax_scale": D ** -0.5, "position": pos, "qk_norm": False, "qk_norm_eps": 0.0,
+                                  "qk_norm_order": "after_rope", "window": {"kind": "sliding", "size": 7},
+                                  "query_temperature": None})
+    layers = tuple(LayerSpec(prefix=f"l{i}.", block=PartSpec("pre_norm"), mixer=attn,
+                             feed_forward=PartSpec("toy_routed_relu", {"hidden_size": H, "inner": I, "experts": E}),
+                             mixer_norm=norm("n1.weight"), feed_forward_norm=norm("n2.weight")) for i in range(2))
+    spec = ModelSpec(architecture="Toy2", hidden_size=H, vocab_size=V,
+                     embedding=PartSpec("token_embedding", {"weight": "emb.weight"}), layers=layers,
+                     run_order=(RunEntry(0), RunEntry(1)), final_norm=norm("norm.weight"),
+                     head=PartSpec("linear_head", {"weight": "head.weight"}), initializer_range=0.2)
+    src = RandomSource(tensor_requirements(spec), 5, 0.2)
+    drawn = {n: src.get(n, "cpu") for n in src.names()}
+    W = {n: t.float() for n, t in drawn.items()}
+    e = Engine(spec, DictSource(drawn), dtype=dtype, max_tokens=512)
+    assert not e.use_graphs                  # the toy feed-forward synchronises: its steps are not captured
+    freqs = Interp(pos).frequencies
+
+    def plain(tokens):
+        n = len(tokens)
+        p = list(range(n))
+        x = W["emb.weight"][tokens]
+        for i in range(2):
+            h = P.rmsnorm(x, W[f"l{i}.n1.weight"], 1e-5)
+            q = (h @ W[f"l{i}.self_attn.q_proj.weight"].T).reshape(n, NH, D)
+            k = (h @ W[f"l{i}.self_attn.k_proj.weight"].T).reshape(n, NKV, D)
+            v = (h @ W[f"l{i}.self_attn.v_proj.weight"].T).reshape(n, NKV, D)
+            q, k = P.rope(q, p, freqs, "interleaved"), P.rope(k, p, freqs, "interleaved")
+            pt = torch.tensor(p)
+            mask = (pt[None, :] <= pt[:, None]) & (pt[None, :] > pt[:, None] - 7)
+            x = x + P.attention(q, k, v, mask, D ** -0.5) @ W[f"l{i}.self_attn.o_proj.weight"].T
+            h2 = P.rmsnorm(x, W[f"l{i}.n2.weight"], 1e-5)
+            which = h2[:, :E].argmax(-1)
+            y = torch.zeros_like(x)
+            for ex in range(E):
+                rows = (which == ex).nonzero().flatten()
+                y[rows] = torch.relu(h2[rows] @ W[f"l{i}.ffn.w1"][ex].T) @ W[f"l{i}.ffn.w2"][ex].T
+            x = x + y
+        return P.rmsnorm(x, W["norm.weight"], 1e-5) @ W["head.weight"].T
+
+    a, b = tiny.random_tokens(40, V, 1), tiny.random_tokens(13, V, 2)
+    ra, rb = plain(a), plain(b)
+    tol = 2e-5 * float(ra.abs().max())
+    sa, sb = e.acquire_slot(), e.acquire_slot()
+    out = e.step([StepEntry(sa, a[:33], [0, 32]), StepEntry(sb, b[:12], [11])]).float().cpu()
+    rows = [(out[0], ra[0]), (out[1], ra[32]), (out[2], rb[11])]
+    out = e.step([StepEntry(sa, [a[33]], [0]), StepEntry(sb, [b[12]], [0])]).float().cpu()
+    rows += [(out[0], ra[33]), (out[1], rb[12])]
+    e.release_slot(sb)
+    for t in range(34, 40):
+        rows.append((e.step([StepEntry(sa, [a[t]], [0])]).float().cpu()[0], ra[t]))
+    e.release_slot(sa)
+    e.check_device_errors()
+    for got, want in rows:
+        assert float((got - want).abs().max()) <= tol
