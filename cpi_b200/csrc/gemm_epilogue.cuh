@@ -59,7 +59,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
   // special-function latencies overlap) and all are dropped into the stage; columns past the tile's
   // tokens hold zeros or finite junk and are never copied out.
   constexpr int PER = 4;                                 // features per lane: 32 lanes cover the 128 of a row
-  constexpr int R = 8;
+  constexpr int R = MODE == kAdd ? 16 : 8;              // rows in flight per warp (the read-modify-write waits on its loads)
   const int n = n0 + PER * lane;
   const bool whole = n + PER <= N;
 #pragma unroll 1
@@ -82,7 +82,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
     for (int j = 0; j < 16; ++j) stage[(c - p0 + j) * 128 + row] = Stage<TO>::put(v[j]);
   }
   __syncthreads();
-  // Phase B.  A warp copies rows warp, warp + 4, ...; eight rows per round, all their loads first.
+  // Phase B.  A warp copies rows warp, warp + 4, ...; R rows per round, all their global loads first.
 #pragma unroll 1
   for (int cb = p0 + warp; cb < v1; cb += 4 * R) {
     TO* dst[R];
@@ -95,24 +95,22 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
       dst[q] = out + (size_t)(out_rows ? out_rows[lr] : lr) * ldo + n;
     }
     if (sizeof(TO) == 4) {
-      float4 old[R], sv[R];
+      float4 old[R];
       if (MODE == kAdd) {
 #pragma unroll
         for (int q = 0; q < R; ++q)
           if (live[q] && whole) old[q] = *reinterpret_cast<const float4*>(dst[q]);
       }
 #pragma unroll
-      for (int q = 0; q < R; ++q)
-        sv[q] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + ((live[q] ? cb + 4 * q : cb) - p0) * 128 + PER * lane);
-#pragma unroll
       for (int q = 0; q < R; ++q) {
         if (!live[q]) continue;
+        const float4 sv = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(stage) + ((cb + 4 * q) - p0) * 128 + PER * lane);
         if (whole) {
-          float4 r = sv[q];
+          float4 r = sv;
           if (MODE == kAdd) { r.x = old[q].x + r.x; r.y = old[q].y + r.y; r.z = old[q].z + r.z; r.w = old[q].w + r.w; }
           *reinterpret_cast<float4*>(dst[q]) = r;
         } else {
-          const float e[4] = {sv[q].x, sv[q].y, sv[q].z, sv[q].w};
+          const float e[4] = {sv.x, sv.y, sv.z, sv.w};
           float* d = reinterpret_cast<float*>(dst[q]);
           for (int i = 0; i < PER && n + i < N; ++i) d[i] = MODE == kAdd ? d[i] + e[i] : e[i];
         }
