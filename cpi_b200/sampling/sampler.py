@@ -8,7 +8,6 @@ function of (seed, request, step), so runs repeat.
 """
 from __future__ import annotations
 
-import numpy as np
 import torch
 
 from ..csrc import lib as K
@@ -28,16 +27,59 @@ def banned_by_ngram(history: list, n: int) -> list:
     return sorted(banned)
 
 
+_M64 = (1 << 64) - 1
+
+
+def _mix64(x: int) -> int:
+    """The finaliser of SplitMix64: a bijection of 64-bit integers that spreads every input bit."""
+    x = (x + 0x9E3779B97F4A7C15) & _M64
+    x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+    x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & _M64
+    return x ^ (x >> 31)
+
+
 def uniform_for(seed: int, request: int, step: int) -> float:
-    """A float32 in [0, 1) that depends only on (seed, request, step)."""
-    g = np.random.Generator(np.random.Philox(key=int(seed) & (2 ** 64 - 1), counter=[int(request), int(step), 0, 0]))
-    return float(np.float32(g.random(dtype=np.float32)))
+    """A float32 in [0, 1) that depends only on (seed, request, step): a counter-based draw (three chained
+    64-bit mixes, the top 24 bits), so that a run repeats from its seed whatever else was in the batch.
+    Plain integer arithmetic: it is computed for every row of every step on the host."""
+    x = _mix64(int(seed) & _M64)
+    x = _mix64(x ^ (int(request) & _M64))
+    x = _mix64(x ^ (int(step) & _M64))
+    return (x >> 40) * (1.0 / (1 << 24))
 
 
 class Sampler:
     def __init__(self, device, vocab_size: int):
         self.device, self.vocab = torch.device(device), vocab_size
         self._work = None
+        self._stage = None         # pinned host rows (temperature, top-k, top-p, uniform) and their device twin
+        self._stage_k = 0
+
+    def _staged(self, temperature, top_k, top_p, uniform):
+        """The four per-row parameter arrays on the device through one copy from pinned memory."""
+        R = len(temperature)
+        if self.device.type != "cuda":
+            return (self._f32(temperature), self._i32(top_k), self._f32(top_p), self._f32(uniform))
+        if self._stage is None or self._stage[0][0].shape[1] < R:
+            n = max(64, R)
+            ring = [torch.empty((4, n), dtype=torch.float32, pin_memory=True) for _ in range(4)]
+            self._stage = (ring, torch.empty((4, 4, n), dtype=torch.float32, device=self.device),
+                           [torch.cuda.Event() for _ in range(4)])
+            self._stage_k = 0
+        ring, dev, events = self._stage
+        j = self._stage_k % 4
+        self._stage_k += 1
+        if self._stage_k > 4:
+            events[j].synchronize()                      # the copy that last read this pinned buffer is done
+        host = ring[j]
+        host[0, :R] = torch.tensor(temperature, dtype=torch.float32)
+        host[1, :R] = torch.tensor(top_k, dtype=torch.int32).view(torch.float32)
+        host[2, :R] = torch.tensor(top_p, dtype=torch.float32)
+        host[3, :R] = torch.tensor(uniform, dtype=torch.float32)
+        d = dev[j]
+        d.copy_(host, non_blocking=True)
+        events[j].record()
+        return d[0, :R], d[1, :R].view(torch.int32), d[2, :R], d[3, :R]
 
     def _i32(self, xs):
         return torch.tensor(xs, dtype=torch.int32, device=self.device)
@@ -81,7 +123,8 @@ class Sampler:
         if self._work is None or self._work.numel() < R * self.vocab:
             self._work = torch.empty(R * self.vocab, dtype=torch.float32, device=self.device)
         u = [uniform_for(p.seed, req, step) for p, (req, step) in zip(params, counters)]
-        K.sample(logits, self._work, self._f32([p.temperature for p in params]),
-                 self._i32([max(1, min(p.top_k, self.vocab)) for p in params]),
-                 self._f32([p.top_p for p in params]), self._f32(u), out)
+        t, k, tp, ud = self._staged([p.temperature for p in params],
+                                    [max(1, min(p.top_k, self.vocab)) for p in params],
+                                    [p.top_p for p in params], u)
+        K.sample(logits, self._work, t, k, tp, ud, out)
         return out

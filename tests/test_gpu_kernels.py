@@ -644,3 +644,66 @@ def test_attention_prefill_far_key_and_general_kernel_agree():
     K().attention_general(c["q"], gen, *args, n_heads=NH, n_kv_heads=NKV, head_dim=D, window_kind=0, window_size=0,
                           scale=1.0)
     assert float((out.float() - gen.float()).abs().max()) <= 2e-2 * float(gen.float().abs().max())
+
+
+# ------------------------------------------------------------------------------------------------ sampling
+@pytest.mark.parametrize("V,quantum", [(50021, 0.0), (50021, 0.5), (3000, 2.0), (202048, 0.0)])
+def test_sample_kernel_keeps_the_k_most_probable_with_ties_by_index(V, quantum):
+    """Temperature / top-k / top-p draws at a large vocabulary against a host walk over the kernel's own
+    weights (its scratch holds e = exp(logit / T - max) after the call): the k largest, equal ones by
+    index, mass cut at top_p with the crossing token kept, renormalised, drawn with the given uniform.
+    Quantised logits make thousands of exact ties around the k-th place."""
+    g = torch.Generator().manual_seed(V)
+    cases = [(0.7, 1, 1.0), (1.0, 7, 1.0), (0.8, 40, 0.9), (1.3, 256, 0.3), (1.0, 256, 1.0), (0.5, 100, 0.95),
+             (1.0, 300, 1.0), (2.0, 13, 0.5)]
+    R = len(cases) * 3
+    logits = torch.randn(R, V, generator=g) * 3
+    if quantum:
+        logits = torch.round(logits / quantum) * quantum
+    logits[1, 5] = float("nan")
+    logits[2, 7] = float("inf")
+    T = torch.tensor([c[0] for c in cases] * 3)
+    k = torch.tensor([c[1] for c in cases] * 3, dtype=torch.int32)
+    p = torch.tensor([c[2] for c in cases] * 3)
+    u = torch.rand(R, generator=g)
+    dev = lambda t: t.to(DEV)
+    work = torch.empty(R * V, device=DEV)
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    K().sample(dev(logits), work, dev(T), dev(k), dev(p), dev(u), out)
+    torch.cuda.synchronize()
+    e_all = work.view(R, V).cpu()
+    near = 0
+    for r in range(R):
+        e = e_all[r]
+        kk = max(1, min(int(k[r]), V, 256))
+        order = sorted(range(V), key=lambda i: (-float(e[i]), i))[:kk] if V <= 5000 else None
+        if order is None:                                   # the same order without sorting the whole vocabulary
+            top = torch.topk(e, min(V, kk + 4096)).values[-1]
+            idx = (e >= top).nonzero().flatten().tolist()
+            order = sorted(idx, key=lambda i: (-float(e[i]), i))[:kk]
+        order = [i for i in order if float(e[i]) > 0]
+        total = float(e.double().sum())
+        probs, mass = [], 0.0
+        margin = 1.0
+        for i in order:
+            q = float(e[i]) / total
+            probs.append(q)
+            mass += q
+            if 0 < float(p[r]) < 1:
+                margin = min(margin, abs(mass - float(p[r])))
+                if mass >= float(p[r]):
+                    break
+        kept = order[:len(probs)]
+        s = sum(probs)
+        run, pick = 0.0, kept[-1]
+        for i, q in zip(kept, probs):
+            run += q / s
+            margin = min(margin, abs(run - float(u[r])))
+            if float(u[r]) <= run:
+                pick = i
+                break
+        if margin < 1e-5:                                   # a float32 rounding could decide: not a fair case
+            near += 1
+            continue
+        assert int(out[r]) == pick, (r, cases[r % len(cases)], int(out[r]), pick)
+    assert near <= 2
