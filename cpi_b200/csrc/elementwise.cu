@@ -22,7 +22,20 @@ __global__ void embedding_kernel(const int* __restrict__ tokens, const TT* __res
     return;
   }
   const TT* row = table + (size_t)tok * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_f32(row[i]);
+  float* dst = out + (size_t)t * hidden;
+  if (sizeof(TT) == 2 && hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+    // eight elements per thread and load: a row is only a few kilobytes, what counts is one round trip
+    const uint4* r16 = reinterpret_cast<const uint4*>(row);
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+      const uint4 raw = r16[i];
+      const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]), c = __bfloat1622float2(h2[2]), d = __bfloat1622float2(h2[3]);
+      reinterpret_cast<float4*>(dst)[2 * i] = make_float4(a.x, a.y, b.x, b.y);
+      reinterpret_cast<float4*>(dst)[2 * i + 1] = make_float4(c.x, c.y, d.x, d.y);
+    }
+    return;
+  }
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(row[i]);
 }
 
 // One block per row.  The sum of squares is taken in a fixed order (thread-strided, then a warp
@@ -76,17 +89,35 @@ __global__ void rmsnorm_kernel(const TX* __restrict__ x, long x_stride, const in
   }
 }
 
-// float32 rows whose length is a multiple of 4: 16-byte loads, the row kept in registers (up to 8192 elements)
+// float32 rows whose length is a multiple of 4: 16-byte loads, the row kept in registers (up to 8192
+// elements).  The norm weights are no kernel's output, so they are fetched (as vectors too) before the wait
+// on the preceding kernel; after the reduction there is only arithmetic and one vector store per group.
 template <typename TO>
 __global__ void __launch_bounds__(256) rmsnorm_vec4_kernel(const float* __restrict__ x, long x_stride,
                                                            const int* __restrict__ rows, const void* __restrict__ w,
                                                            int w_dtype, TO* __restrict__ out, long out_stride, int n,
                                                            float eps) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float scratch[32];
   constexpr int PER = 8;
   const int r = blockIdx.x, n4 = n >> 2;
+  float4 g[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int i = threadIdx.x + j * 256;
+    g[j] = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (w && i < n4) {
+      if (w_dtype == kF32) {
+        g[j] = reinterpret_cast<const float4*>(w)[i];
+      } else {
+        const uint2 raw = reinterpret_cast<const uint2*>(w)[i];
+        const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        g[j] = make_float4(lo.x, lo.y, hi.x, hi.y);
+      }
+    }
+  }
+  pdl_wait();
   const float4* xr = reinterpret_cast<const float4*>(x + (size_t)(rows ? rows[r] : r) * x_stride);
   float4 v[PER];
   float ss = 0.f;
@@ -103,13 +134,17 @@ __global__ void __launch_bounds__(256) rmsnorm_vec4_kernel(const float* __restri
   for (int j = 0; j < PER; ++j) {
     const int i = threadIdx.x + j * 256;
     if (i < n4) {
-      float y[4] = {v[j].x * inv, v[j].y * inv, v[j].z * inv, v[j].w * inv};
-      if (w) {
-#pragma unroll
-        for (int u = 0; u < 4; ++u) y[u] *= load_any(w, w_dtype, 4 * i + u);
+      // (x * inv) * weight, in this order, as the scalar kernel does
+      const float y0 = v[j].x * inv * g[j].x, y1 = v[j].y * inv * g[j].y, y2 = v[j].z * inv * g[j].z, y3 = v[j].w * inv * g[j].w;
+      if (sizeof(TO) == 4) {
+        *reinterpret_cast<float4*>(reinterpret_cast<float*>(o) + 4 * i) = make_float4(y0, y1, y2, y3);
+      } else {
+        __nv_bfloat162 a = __floats2bfloat162_rn(y0, y1), b = __floats2bfloat162_rn(y2, y3);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&a);
+        pk.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(o) + 4 * i) = pk;
       }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) o[4 * i + u] = from_f32<TO>(y[u]);
     }
   }
 }
@@ -212,7 +247,9 @@ extern "C" int cpi_rmsnorm(const void* x, int x_dtype, long x_stride, const int*
                            float eps, cudaStream_t stream) {
   if (n_rows == 0) return 0;
   CPI_REQUIRE(n_rows > 0 && n > 0, "rmsnorm: bad sizes rows=%d n=%d", n_rows, n);
-  if (x_dtype == kF32 && n % 4 == 0 && n >= 1024 && n <= 8192 && x_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+  const int out_esz = out_dtype == kF32 ? 4 : 2;
+  if (x_dtype == kF32 && n % 4 == 0 && n >= 1024 && n <= 8192 && x_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(w) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (out_stride * out_esz) % 16 == 0) {
     CPI_DISPATCH_DTYPE(out_dtype, TO,
         (cpi::launch_pdl(rmsnorm_vec4_kernel<TO>, n_rows, 256, 0, stream, (const float*)x, x_stride, rows, w, w_dtype,
                          (TO*)out, out_stride, n, eps)));

@@ -42,9 +42,23 @@ __global__ void __launch_bounds__(SAMP_NT) argmax_kernel(const float* __restrict
   const float* row = logits + (size_t)blockIdx.x * stride;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += SAMP_NT) {
-    const float v = row[i];
-    if (v > best) { best = v; bi = i; }               // strided scan keeps the smallest index per thread
+  if (vocab % 4 == 0 && (reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    // 16-byte loads, several in flight: one block reads the whole row.  A thread meets its elements in
+    // increasing index order, so `>` keeps its smallest index; the block then prefers the smallest index.
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+#pragma unroll 4
+    for (int i = threadIdx.x; i < vocab / 4; i += SAMP_NT) {
+      const float4 v = r4[i];
+      if (v.x > best) { best = v.x; bi = 4 * i; }
+      if (v.y > best) { best = v.y; bi = 4 * i + 1; }
+      if (v.z > best) { best = v.z; bi = 4 * i + 2; }
+      if (v.w > best) { best = v.w; bi = 4 * i + 3; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += SAMP_NT) {
+      const float v = row[i];
+      if (v > best) { best = v; bi = i; }             // strided scan keeps the smallest index per thread
+    }
   }
   block_argmax(best, bi, sv, si);
   if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
