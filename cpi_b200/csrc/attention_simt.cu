@@ -119,7 +119,8 @@ __global__ void qkv_post_kernel(QkvPostParams p) {
 __global__ void __launch_bounds__(256) qkv_post_d128_kernel(QkvPostParams p, int heads_per_block) {
   __shared__ float cos_s[64], sin_s[64];
   pdl_launch_dependents();
-  pdl_wait();
+  // positions and page tables are copied to the device before the step's first kernel and the frequencies
+  // are constants: the angles do not wait for the kernel that writes q, k and v
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int pos = p.token_pos[t];
   if (p.inv_freq && tid < 64) {
@@ -127,6 +128,7 @@ __global__ void __launch_bounds__(256) qkv_post_d128_kernel(QkvPostParams p, int
     sincosf((float)pos * p.inv_freq[tid], &s, &c);
     cos_s[tid] = c; sin_s[tid] = s;
   }
+  pdl_wait();
   __syncthreads();
   const int heads_total = p.n_heads + (p.write_kv ? 2 * p.n_kv_heads : 0);
   const int h_begin = blockIdx.y * heads_per_block, h_end = min(heads_total, h_begin + heads_per_block);

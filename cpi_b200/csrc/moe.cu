@@ -39,19 +39,41 @@ __global__ void __launch_bounds__(128)
 router_logits_kernel(const TH* __restrict__ h, long h_stride, const TW* __restrict__ w,
                      float* __restrict__ logits, int hidden, int n_experts, int vec) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float scratch[32];
   const int e = blockIdx.x, t = blockIdx.y;
   const TH* x = h + (size_t)t * h_stride;
   const TW* wr = w + (size_t)e * hidden;
   const int groups = (hidden + 7) / 8;
   float s = 0.f;
-  for (int g = threadIdx.x; g < groups; g += 128) {
-    float xv[8], wv[8];
-    load_group<TH>(x, g, hidden, vec, xv);
-    load_group<TW>(wr, g, hidden, vec, wv);
+  if (groups <= 8 * 128) {
+    // the router's weights are no kernel's output: this thread's (up to eight) groups of them are fetched
+    // before the wait on the kernel that writes the activations; same order of additions as below
+    float wv[8][8];
 #pragma unroll
-    for (int u = 0; u < 8; ++u) s = fmaf(xv[u], wv[u], s);
+    for (int j = 0; j < 8; ++j) {
+      const int g = threadIdx.x + j * 128;
+      if (g < groups) load_group<TW>(wr, g, hidden, vec, wv[j]);
+    }
+    pdl_wait();
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int g = threadIdx.x + j * 128;
+      if (g < groups) {
+        float xv[8];
+        load_group<TH>(x, g, hidden, vec, xv);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s = fmaf(xv[u], wv[j][u], s);
+      }
+    }
+  } else {
+    pdl_wait();
+    for (int g = threadIdx.x; g < groups; g += 128) {
+      float xv[8], wv[8];
+      load_group<TH>(x, g, hidden, vec, xv);
+      load_group<TW>(wr, g, hidden, vec, wv);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s = fmaf(xv[u], wv[u], s);
+    }
   }
   s = block_sum(s, scratch);
   if (threadIdx.x == 0) logits[(size_t)t * n_experts + e] = s;
