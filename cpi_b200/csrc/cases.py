@@ -73,6 +73,8 @@ def case_gemm(a) -> None:
         kw["force_bn"] = a.bn
     if a.splits:
         kw["force_splits"] = a.splits
+    if a.persistent is not None:
+        K.gemm_pair_persistent(a.persistent)
     fn = K.gemm_tc_pair if a.pair else K.gemm_tc
     if a.pair:
         kw.pop("force_bn", None); kw.pop("force_splits", None)
@@ -194,6 +196,7 @@ def main() -> int:
     g.add_argument("--mode", choices=["store", "add", "swiglu"], default="store")
     g.add_argument("--groups", type=int, default=0)
     g.add_argument("--pair", action="store_true", help="use the paired (two-SM) kernel")
+    g.add_argument("--persistent", type=int, default=None, help="paired kernel: 2 a pair per SM pair works through the tiles, 0 a launch slot per tile, 1 by shape")
     g.add_argument("--bn", type=int, default=0, help="force the token-tile width (tuning)")
     g.add_argument("--splits", type=int, default=0, help="force the split-K count (tuning)")
     d = sub.add_parser("attention_decode")

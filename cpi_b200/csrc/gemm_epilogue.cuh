@@ -42,14 +42,21 @@ __device__ __forceinline__ bool staged_ok(const void* out, long ldo, int n_valid
   return n_valid_t >= 32 && (ldo % (16 / (int)sizeof(TO))) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
 }
 
+// Barriers of the turning: all threads of the CTA, or a named barrier over the calling threads only
+// (a kernel whose other warps are busy with the next tile).
+struct CtaSync { __device__ __forceinline__ void operator()() const { __syncthreads(); } };
+template <int ID, int THREADS> struct NamedSync {
+  __device__ __forceinline__ void operator()() const { asm volatile("bar.sync %0, %1;" ::"n"(ID), "n"(THREADS) : "memory"); }
+};
+
 // ld16(col, dst): the caller's tensor-memory load of 16 columns starting at `col` of accumulator 0;
 // ld16u the same for the second accumulator (SwiGLU).  `stage` holds STAGE_COLS x 128 elements of TO
 // (STAGE_COLS a multiple of 16); a tile with more columns goes through in several passes.
-// All 128 threads call this; it contains __syncthreads().
-template <int MODE, typename TO, int STAGE_COLS, typename Ld, typename LdU>
+// The 128 threads that own the accumulator's lanes call this; it contains barriers (`sync`).
+template <int MODE, typename TO, int STAGE_COLS, typename Ld, typename LdU, typename Sync = CtaSync>
 __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int warp, int lane, int n0, int N, int t0,
                                        int n_valid_t, int n_cols, TO* out, long ldo, const int* out_rows,
-                                       const float* row_scale) {
+                                       const float* row_scale, Sync sync = Sync()) {
   static_assert(STAGE_COLS >= 16 && STAGE_COLS % 16 == 0, "the stage holds whole chunks of 16 columns");
   using S = typename Stage<TO>::T;
   S* stage = reinterpret_cast<S*>(stage_mem);
@@ -65,7 +72,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
 #pragma unroll 1
   for (int p0 = 0; p0 < n_cols; p0 += STAGE_COLS) {      // one pass per STAGE_COLS columns
   const int p1 = min(p0 + STAGE_COLS, n_cols), v1 = min(p0 + STAGE_COLS, n_valid_t);
-  if (p0 > 0) __syncthreads();                           // the previous pass has been copied out
+  if (p0 > 0) sync();                                    // the previous pass has been copied out
 #pragma unroll 1
   for (int c = p0; c < p1; c += 16) {
     float v[16], u[16];
@@ -81,7 +88,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
 #pragma unroll
     for (int j = 0; j < 16; ++j) stage[(c - p0 + j) * 128 + row] = Stage<TO>::put(v[j]);
   }
-  __syncthreads();
+  sync();
   // Phase B.  A warp copies rows warp, warp + 4, ...; R rows per round, all their global loads first.
 #pragma unroll 1
   for (int cb = p0 + warp; cb < v1; cb += 4 * R) {

@@ -332,6 +332,215 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
 }
 
+// ---------------------------------------------------------------------------------------------- persistent
+// The same product with one pair per SM pair that works through a list of tiles (dense products only).
+// Six warps per CTA: 0-3 own the accumulator's lanes and run the epilogue, warp 4 issues the TMA loads,
+// warp 5 (of the leading CTA) the MMAs.  The stage ring runs on across tiles, and with one accumulator per
+// tile there are two accumulator buffers in tensor memory: the MMAs of tile j+1 run while tile j is turned
+// in shared memory and written out, so an SM pair's tiles follow each other at the tensor pipe's rate
+// instead of each paying fill, drain and epilogue.  (With two accumulators, SwiGLU, the tensor memory
+// holds one tile: its MMAs wait for the epilogue, but its loads do not.)
+//   full[s] / empty[s]            stage ring, as above
+//   acc_full[b]                   MMA -> epilogue warps of both CTAs (commit with multicast)
+//   acc_empty[b] (in the leader)  epilogue warps of both CTAs -> MMA: one arrival per warp, 8 in all
+template <int BN, int MODE, typename TO, int STAGES>
+__global__ void __launch_bounds__(192) gemm_tc_pair_persistent_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                      const __grid_constant__ CUtensorMap map_x,
+                                                                      Params p, int n_pairs, int n_tok) {
+  constexpr int ACC = MODE == kSwiglu ? 2 : 1;
+  constexpr int NB = ACC == 1 ? 2 : 1;                           // accumulator buffers in tensor memory
+  constexpr int HALF = BN / 2;
+  constexpr uint32_t A_BYTES = BM * BK * 2, B_BYTES = HALF * BK * 2;
+  constexpr uint32_t STAGE_BYTES = ACC * A_BYTES + B_BYTES;
+  constexpr int BOX_ROWS = 64;
+  constexpr uint32_t BOX_BYTES = BOX_ROWS * BK * 2;
+  constexpr uint32_t TMEM_COLS = 512;
+  constexpr int EPI_COLS = 64;                                   // columns turned at a time
+  extern __shared__ __align__(1024) uint8_t smem[];
+  __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[NB], acc_empty[NB];
+  __shared__ uint32_t tmem_base_s;
+  __shared__ int abort_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  uint8_t* ring = smem;
+  uint8_t* epi = smem + (size_t)STAGES * STAGE_BYTES;
+  const uint32_t rank = cluster_rank();
+  pdl_launch_dependents();
+  const int n_tiles = n_pairs * n_tok;
+  const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
+  const int n_kt = p.k_tiles;
+  // tile number -> (token tile, weight pair), in bands of 8 token tiles as the kernel above
+  auto tile_of = [&](int pid, int& tile_t, int& pair_n) {
+    const int W = 8;
+    const int band = pid / (W * n_pairs), rem = pid - band * W * n_pairs;
+    const int w_eff = min(W, n_tok - band * W);
+    tile_t = band * W + rem % w_eff;
+    pair_n = rem / w_eff;
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+    for (int b = 0; b < NB; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;");
+  }
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync();
+  fence_after_sync();
+  const uint32_t tmem_base = tmem_base_s;
+  volatile int* abort_flag = &abort_s;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      // ---- TMA producer (both CTAs); weights need no wait on the preceding kernel, tokens do ----
+      bool waited = false;
+      int it = 0;
+      for (int pid = cluster_id; pid < n_tiles; pid += n_clusters) {
+        int tile_t, pair_n;
+        tile_of(pid, tile_t, pair_n);
+        const int n0 = (pair_n * 2 + (int)rank) * BM, t0 = tile_t * p.bn;
+        const int n_valid_t = min(p.bn, p.T - t0);
+        const int half = min(BN, (n_valid_t + 31) & ~31) / 2;
+        const int n_boxes = (half + BOX_ROWS - 1) / BOX_ROWS;
+        const uint32_t cta_tx = ACC * A_BYTES + (uint32_t)n_boxes * BOX_BYTES;
+        bool ok = true;
+        for (int kt = 0; kt < n_kt; ++kt, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, abort_flag)) { ok = false; break; }
+          uint8_t* st = ring + (size_t)s * STAGE_BYTES;
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[s]), 0);
+          if (rank == 0) mbar_expect_tx(&full_bar[s], 2 * cta_tx);
+          tma2_load_3d(st, &map_w, bar, kt * BK, n0, 0);
+          if (ACC == 2) tma2_load_3d(st + A_BYTES, &map_w, bar, kt * BK, p.N + n0, 0);
+          if (!waited) { pdl_wait(); waited = true; }
+          for (int b = 0; b < n_boxes; ++b)
+            tma2_load_2d(st + ACC * A_BYTES + b * BOX_BYTES, &map_x, bar, kt * BK, t0 + (int)rank * half + b * BOX_ROWS);
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer (leader only) ----
+      int it = 0, j = 0;
+      bool ok = true;
+      for (int pid = cluster_id; pid < n_tiles && ok; pid += n_clusters, ++j) {
+        int tile_t, pair_n;
+        tile_of(pid, tile_t, pair_n);
+        const int n_valid_t = min(p.bn, p.T - tile_t * p.bn);
+        const uint32_t idesc = instr_desc_pair(min(BN, (n_valid_t + 31) & ~31));
+        const int b = j % NB;
+        if (j >= NB) ok = mbar_wait(&acc_empty[b], ((j / NB) - 1) & 1, abort_flag);     // the epilogue has read it
+        if (!ok) break;
+        fence_after_sync();
+        const uint32_t d0 = tmem_base + b * (ACC * BN);
+        for (int kt = 0; kt < n_kt; ++kt, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(&full_bar[s], (it / STAGES) & 1, abort_flag);
+          if (!ok) break;
+          fence_after_sync();
+          const uint32_t a_addr = smem_u32(ring + (size_t)s * STAGE_BYTES);
+          const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + ACC * A_BYTES);
+          const uint64_t da2 = smem_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+          for (int q = 0; q < BK / UMMA_K; ++q) {
+            const uint32_t acc = (kt > 0 || q > 0) ? 1u : 0u;
+            umma2_bf16(d0, da + 2 * q, db + 2 * q, idesc, acc);
+            if (ACC == 2) umma2_bf16(d0 + BN, da2 + 2 * q, db + 2 * q, idesc, acc);
+          }
+          umma2_commit_both(&empty_bar[s]);
+        }
+        if (ok) umma2_commit_both(&acc_full[b]);
+      }
+    }
+  } else {
+    // ---- epilogue: warps 0-3 of both CTAs; each CTA stores its 128 features of the tile's tokens ----
+    pdl_wait();
+    const uint32_t leader_empty0 = map_to_cta(smem_u32(&acc_empty[0]), 0);
+    int j = 0;
+    for (int pid = cluster_id; pid < n_tiles; pid += n_clusters, ++j) {
+      int tile_t, pair_n;
+      tile_of(pid, tile_t, pair_n);
+      const int n0 = (pair_n * 2 + (int)rank) * BM, t0 = tile_t * p.bn;
+      const int n_valid_t = min(p.bn, p.T - t0);
+      const int n_cols = min(BN, (n_valid_t + 15) & ~15);
+      const int b = j % NB;
+      mbar_wait(&acc_full[b], (j / NB) & 1, abort_flag);
+      // one verdict for the four warps (a named barrier has no time limit: nobody may leave alone); it also
+      // keeps the turning buffer of the tile before from being overwritten while a warp still copies it out
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (abort_s) break;
+      fence_after_sync();
+      const uint32_t lane_addr = tmem_base + b * (ACC * BN) + ((uint32_t)(warp * 32) << 16);
+      auto ld = [&](int c, float* d) { tmem_ld16(lane_addr + c, d); };
+      auto ldu = [&](int c, float* d) { tmem_ld16(lane_addr + BN + c, d); };
+      TO* out = reinterpret_cast<TO*>(p.out);
+      epi::staged<MODE, TO, EPI_COLS>(epi, ld, ldu, warp, lane, n0, p.N, t0, n_valid_t, n_cols, out, p.ldo, p.out_rows,
+                                      p.row_scale, epi::NamedSync<1, 128>());
+      // the accumulator has been read (the last tensor-memory load of the tile precedes the last barrier above)
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];"
+                     ::"r"(leader_empty0 + (uint32_t)(b * sizeof(uint64_t))) : "memory");
+    }
+  }
+  __syncwarp();
+  if (abort_s) {
+    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 4);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+  }
+  fence_before_sync();
+  __syncthreads();
+  cluster_sync();                                                // neither CTA leaves while the other may still use it
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS));
+}
+
+template <int BN, int MODE, typename TO>
+static int launch_persistent(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, int n_pairs, int n_tok,
+                             cudaStream_t stream) {
+  constexpr int ACC = MODE == kSwiglu ? 2 : 1;
+  constexpr int STAGE = ACC * BM * BK * 2 + (BN / 2) * BK * 2;
+  constexpr int EPI = 64 * 128 * (int)sizeof(TO);
+  constexpr int S0 = (222 * 1024 - EPI) / STAGE;
+  constexpr int STAGES = S0 > 8 ? 8 : S0;
+  constexpr int SMEM = STAGES * STAGE + EPI;
+  auto kern = gemm_tc_pair_persistent_kernel<BN, MODE, TO, STAGES>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM) != cudaSuccess) {
+      set_error("gemm_tc_pair: cannot reserve %d bytes of shared memory", SMEM);
+      return 1;
+    }
+    attr_set = true;
+  }
+  int dev = 0, n_sm = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev);
+  int clusters = n_sm / 2;
+  if (clusters > n_pairs * n_tok) clusters = n_pairs * n_tok;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * clusters);
+  cfg.blockDim = dim3(192);
+  cfg.dynamicSmemBytes = SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  count_launch();
+  cudaLaunchKernelEx(&cfg, kern, mw, mx, p, n_pairs, n_tok);
+  return check_launch("gemm_tc_pair_persistent");
+}
+
 template <int BN, int MODE, typename TO>
 static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
   constexpr int ACC = MODE == kSwiglu ? 2 : 1;
@@ -375,6 +584,16 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
 using namespace cpi;
 
 // Whether the paired kernel takes this product, and the token-tile width it would use (0: not taken).
+// Dense products: one pair per SM pair working through a tile list (2: always), one launch slot per tile
+// (0: always), or whichever measured faster (1, the default).  Both run at what the L2 can deliver to the
+// SMs (a 256 x 256 pair tile at the tensor pipe's full rate would pull 64 bytes per cycle and SM, ~15 TB/s
+// over the GPU; measured: the MMA thread of the persistent kernel waits for operands a third of the time).
+// Two pairs sharing an SM pair hide that latency better for one accumulator; the persistent kernel wins
+// where the epilogue is long or cannot overlap otherwise: SwiGLU (two accumulators fill the tensor memory,
+// no second pair fits) and the read-modify-write of ADD at many tokens.
+static int g_persistent = 1;
+extern "C" void cpi_gemm_tc_pair_persistent(int mode) { g_persistent = mode; }
+
 extern "C" int cpi_gemm_tc_pair_plan(int T, int N, int K, int swiglu, int n_groups) {
   if (N % 256 != 0 || K % 8 != 0) return 0;
   if (n_groups > 0) {
@@ -417,6 +636,14 @@ extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* ou
   dim3 grid(N / tc2::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), 1);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc_pair: too many token tiles (%u)", grid.y);
   const int cap = bn <= 128 ? 128 : 256;
+  const bool persistent = g_persistent == 2 || (g_persistent == 1 && (mode == tc2::kSwiglu || (mode == tc2::kAdd && T >= 4096)));
+  if (persistent && n_groups == 0 && cap == 256) {
+    const int n_pairs = N / 256, n_tok = (T + bn - 1) / bn;
+    if (mode == tc2::kStore && out_dtype == kBF16) return tc2::launch_persistent<256, tc2::kStore, __nv_bfloat16>(mw, mx, p, n_pairs, n_tok, stream);
+    if (mode == tc2::kStore && out_dtype == kF32) return tc2::launch_persistent<256, tc2::kStore, float>(mw, mx, p, n_pairs, n_tok, stream);
+    if (mode == tc2::kAdd) return tc2::launch_persistent<256, tc2::kAdd, float>(mw, mx, p, n_pairs, n_tok, stream);
+    if (mode == tc2::kSwiglu) return tc2::launch_persistent<256, tc2::kSwiglu, __nv_bfloat16>(mw, mx, p, n_pairs, n_tok, stream);
+  }
 #define CPI_PAIR(CAP)                                                                                         \
   if (mode == tc2::kStore && out_dtype == kBF16) return tc2::launch<CAP, tc2::kStore, __nv_bfloat16>(mw, mx, p, grid, stream); \
   if (mode == tc2::kStore && out_dtype == kF32) return tc2::launch<CAP, tc2::kStore, float>(mw, mx, p, grid, stream);         \

@@ -229,6 +229,13 @@ def gemm_cluster_split(on: bool) -> None:
     load().cpi_gemm_tc_cluster_split(c_int(int(on)))
 
 
+def gemm_pair_persistent(mode) -> None:
+    """Dense products of `gemm_tc_pair`: 2 / True = always one pair of CTAs per SM pair working through the
+    tiles (the epilogue of one tile under the MMAs of the next), 0 / False = always a launch slot per tile,
+    1 = the library's choice by shape (the default)."""
+    load().cpi_gemm_tc_pair_persistent(c_int(2 if mode is True else 0 if mode is False else int(mode)))
+
+
 def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_scale=None, group_offsets=None,
                  n_groups=0, rows_per_group_hint=None) -> bool:
     """The paired (two-SM) tcgen05 kernel for products with many tokens, dense or grouped (see

@@ -120,10 +120,21 @@ def test_gemm_tensor_core_modes(T, N, Kd, mode):
         assert err <= tol, (odt, err, tol)
 
 
-@pytest.mark.parametrize("T,N,Kd", [(512, 256, 64), (2048, 1024, 512), (700, 512, 200), (1000, 768, 1032), (4096, 5120, 256)])
+@pytest.mark.parametrize("persistent", [True, False])
+@pytest.mark.parametrize("T,N,Kd", [(512, 256, 64), (2048, 1024, 512), (700, 512, 200), (1000, 768, 1032), (4096, 5120, 256),
+                                    (5000, 2048, 1024)])
 @pytest.mark.parametrize("mode", [0, 1, 2])
-def test_gemm_tensor_core_pair_kernel(T, N, Kd, mode):
-    """Two CTAs on one tile: every mode, token tails that are no multiple of 32, k tails."""
+def test_gemm_tensor_core_pair_kernel(T, N, Kd, mode, persistent):
+    """Two CTAs on one tile: every mode, token tails that are no multiple of 32, k tails; as a pair per SM
+    pair that works through the tiles (more tiles than pairs in the last shape) and as a launch slot per tile."""
+    K().gemm_pair_persistent(persistent)
+    try:
+        _pair_kernel_case(T, N, Kd, mode)
+    finally:
+        K().gemm_pair_persistent(1)
+
+
+def _pair_kernel_case(T, N, Kd, mode):
     a = rnd(T, Kd, dtype=torch.bfloat16)
     w = rnd(2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=2, scale=Kd ** -0.5)
     scale = rnd(T, seed=5).abs()
