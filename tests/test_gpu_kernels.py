@@ -153,9 +153,18 @@ def _pair_kernel_case(T, N, Kd, mode):
         assert not K().gemm_tc_pair(a, wn, out[:, : N - 128], mode)         # features no multiple of 256
 
 
-@pytest.mark.parametrize("counts", [[300, 0, 129, 83], [128, 128, 128, 128, 1, 255, 256, 0]])
+@pytest.mark.parametrize("persistent", [2, 0])
+@pytest.mark.parametrize("counts", [[300, 0, 129, 83], [128, 128, 128, 128, 1, 255, 256, 0], [700, 3, 0, 0, 513, 64]])
 @pytest.mark.parametrize("mode", [0, 1, 2])
-def test_gemm_tensor_core_pair_kernel_grouped(counts, mode):
+def test_gemm_tensor_core_pair_kernel_grouped(counts, mode, persistent):
+    K().gemm_pair_persistent(persistent)
+    try:
+        _pair_kernel_grouped_case(counts, mode)
+    finally:
+        K().gemm_pair_persistent(1)
+
+
+def _pair_kernel_grouped_case(counts, mode):
     G, N, Kd = len(counts), 512, 320
     M = sum(counts)
     w = rnd(G, 2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=1, scale=Kd ** -0.5)
