@@ -2,16 +2,17 @@
 
 The reference has no such mode (its substitute for real weights is the .ll2c
 packing tool chain, tools/pack_ll2c.py).  Every tensor the model's parts declare
-is drawn from N(0, initializer_range) in float32 and rounded to bfloat16, norm
-weights are 1.  Each tensor has a generator of its own, seeded from (seed, tensor
-name), so the values do not depend on the order of creation.  Values drawn on
-the CPU and on a GPU differ (the two generators are different algorithms); a
-model folder is always written from CPU draws.
+is drawn from N(0, initializer_range) and rounded to bfloat16, norm weights are 1.
+The generator is counter based: element i of a tensor is a function of (seed,
+tensor name, i) alone, computed with integer arithmetic, one table look-up and one
+multiplication, so the values depend neither on the order of creation nor on the
+device: a model drawn on a GPU equals the folder written from the CPU bit for bit.
 """
 from __future__ import annotations
 
 import hashlib
 import json
+import math
 import os
 
 import torch
@@ -23,6 +24,37 @@ from .store import TensorReq, WeightSource
 def _tensor_seed(seed: int, name: str) -> int:
     h = hashlib.sha256(f"{seed}:{name}".encode("utf-8")).digest()
     return int.from_bytes(h[:8], "little") & 0x7FFF_FFFF_FFFF_FFFF
+
+
+def _i64(c: int) -> int:
+    """A 64-bit constant as the signed integer that torch's int64 holds."""
+    return c - (1 << 64) if c >= (1 << 63) else c
+
+
+_TABLE = None
+
+
+def _normal_table() -> torch.Tensor:
+    """Inverse normal distribution function at the 65,536 bin centres (float32, computed once on the CPU in
+    float64): a draw is one of these values, chosen by 16 hashed bits."""
+    global _TABLE
+    if _TABLE is None:
+        u = (torch.arange(65536, dtype=torch.float64) + 0.5) / 65536.0
+        _TABLE = (math.sqrt(2.0) * torch.erfinv(2.0 * u - 1.0)).to(torch.float32)
+    return _TABLE
+
+
+def counter_normal(tensor_seed: int, start: int, n: int, std: float, device) -> torch.Tensor:
+    """float32 [n]: the draws number start .. start + n - 1 of the stream `tensor_seed`.  Integer mixing
+    (64-bit multiplications wrap and shifts are made logical by a mask: the same on every device), 16 bits
+    pick the table entry."""
+    i = torch.arange(start, start + n, dtype=torch.int64, device=device)
+    z = i * _i64(0x9E3779B97F4A7C15) + tensor_seed
+    z = (z ^ ((z >> 30) & ((1 << 34) - 1))) * _i64(0xBF58476D1CE4E5B9)
+    z = (z ^ ((z >> 27) & ((1 << 37) - 1))) * _i64(0x94D049BB133111EB)
+    z = z ^ ((z >> 31) & ((1 << 33) - 1))
+    idx = (z >> 48) & 0xFFFF
+    return _normal_table().to(device)[idx] * std
 
 
 class RandomSource(WeightSource):
@@ -52,18 +84,13 @@ class RandomSource(WeightSource):
         device = torch.device(device)
         if r.init == "ones":
             return torch.ones(r.shape, dtype=self.dtype, device=device)
-        g = torch.Generator(device=device)
-        g.manual_seed(_tensor_seed(self.seed, name))
-        if device.type == "cpu":
-            t = torch.empty(r.shape, dtype=torch.float32).normal_(0.0, self.std, generator=g)
-            return t.to(self.dtype)
+        ts = _tensor_seed(self.seed, name)
         out = torch.empty(r.shape, dtype=self.dtype, device=device)
         flat = out.view(-1)
-        step = 1 << 28                     # bound the float32 staging buffer
+        step = 1 << 26                     # bound the int64 staging buffers
         for i in range(0, flat.numel(), step):
             n = min(step, flat.numel() - i)
-            flat[i:i + n] = torch.empty(n, dtype=torch.float32, device=device).normal_(
-                0.0, self.std, generator=g).to(self.dtype)
+            flat[i:i + n] = counter_normal(ts, i, n, self.std, device).to(self.dtype)
         return out
 
 

@@ -9,6 +9,7 @@ reader keeps dtype and shape as well, so that every tensor can be checked.
 """
 from __future__ import annotations
 
+import difflib
 import json
 import mmap
 import os
@@ -17,6 +18,22 @@ from dataclasses import dataclass
 
 import numpy as np
 import torch
+
+
+def nearest_name(name: str, names) -> str:
+    """The name among `names` that most resembles `name`, or '' if nothing is close.  A wrong prefix is the
+    usual mistake, so the longest shared tail of dotted components decides first, if it singles out one name."""
+    names = [n for n in names if n != name]
+    parts = name.split(".")
+    for k in range(len(parts) - 1, 1, -1):
+        tail = ".".join(parts[-k:])
+        hits = [n for n in names if n == tail or n.endswith("." + tail)]
+        if hits:
+            if len(hits) == 1:
+                return hits[0]
+            break
+    close = difflib.get_close_matches(name, names, n=1, cutoff=0.8)
+    return close[0] if close else ""
 
 
 class SafetensorsError(RuntimeError):
@@ -105,7 +122,8 @@ class SafetensorsDir:
 
     def entry(self, name: str) -> TensorEntry:
         if name not in self.entries:
-            raise SafetensorsError(f"safetensors: tensor not found: {name}")
+            near = nearest_name(name, self.entries)
+            raise SafetensorsError(f"safetensors: tensor not found: {name}" + (f" (did you mean {near}?)" if near else ""))
         return self.entries[name]
 
     def tensor(self, name: str) -> torch.Tensor:

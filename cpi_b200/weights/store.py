@@ -17,7 +17,7 @@ from typing import Iterable, Optional
 
 import torch
 
-from .safetensors_io import SafetensorsDir
+from .safetensors_io import SafetensorsDir, nearest_name
 
 
 class WeightsError(RuntimeError):
@@ -149,7 +149,9 @@ def check_source(reqs: list, source: WeightSource, ignored_prefixes: tuple = (),
     lines = ["the weights do not match the model's configuration:"]
     if missing:
         lines.append(f"  missing tensors ({len(missing)}):")
-        lines += [f"    {n}  expected shape {list(wanted[n].shape)}" for n in sorted(missing)]
+        for n in sorted(missing):
+            near = nearest_name(n, unexpected)
+            lines.append(f"    {n}  expected shape {list(wanted[n].shape)}" + (f"  (did you mean {near}?)" if near else ""))
     if unexpected:
         lines.append(f"  unexpected tensors ({len(unexpected)}):")
         lines += [f"    {n}  shape {list(source.shape(n))}" for n in sorted(unexpected)]

@@ -180,6 +180,27 @@ def test_first_tokens_of_a_sequence(name, dtype):
     compare_with_plain(model_dir(name), {"whole": t, "single": t}, rp, dtype)
 
 
+def test_random_weights_drawn_on_the_gpu_equal_the_folder_written_on_the_cpu():
+    """The generator is counter based: the same (seed, name, element) gives the same bits on both devices, so a
+    model drawn in place and one read from its folder give the same logits bit for bit."""
+    from cpi_b200.engine import Engine
+    from cpi_b200.engine.model import tensor_requirements
+    from cpi_b200.weights.random_init import RandomSource
+    cfg, seed = tiny.config("B"), 11
+    a = Engine.from_random(cfg, seed=seed, dtype="bfloat16", max_tokens=256)
+    b = Engine.from_model_dir(tiny.make_model_dir("B", seed=seed), dtype="bfloat16", max_tokens=256)
+    src = RandomSource(tensor_requirements(a.spec), seed, a.spec.initializer_range)
+    for n in src.names():
+        assert torch.equal(src.get(n, "cuda").cpu(), src.get(n, "cpu")), n
+    t = tiny.random_tokens(40, a.spec.vocab_size, 3)
+    outs = []
+    for e in (a, b):
+        rp = Replay(e)
+        rp.step([("x", t, [len(t) - 1])])
+        outs.append(rp.logits["x"][len(t) - 1])
+    assert torch.equal(outs[0], outs[1])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_weights_stored_in_float32_stay_float32(dtype):
     """A model folder whose tensors are F32: they are kept in 32-bit, and both precisions still match."""
@@ -201,7 +222,10 @@ def test_weights_stored_in_float32_stay_float32(dtype):
 def test_long_context_across_the_chunk_boundary_both_kernel_families_agree():
     """Head size 128, chunk 8192, temperature floor 8192: a 9,000-token prompt (its tiles straddle the
     chunk boundary and run as two pieces) and decoding from 8,150 across position 8,192, once on the
-    tensor-core kernels and once on the general ones."""
+    tensor-core kernels and once on the general ones.  With one expert per token a near-tie of two router
+    logits can fall either way in bfloat16, and then the row is another function of its input: rows whose
+    expert choices differ between the two runs are set aside (they must be few; that such choices are
+    near-ties is checked against the plain router in the other tests)."""
     from cpi_b200.engine import Engine, StepEntry
     from cpi_b200.parts import attention, linear
     cfg = {
@@ -221,26 +245,35 @@ def test_long_context_across_the_chunk_boundary_both_kernel_families_agree():
         linear.use_tensor_cores = fast
         try:
             e = Engine.from_model_dir(d, dtype="bfloat16", max_tokens=9216 + 8320, max_seqs=2, max_seq_len=9216)
-            e.use_graphs = fast
+            cap = e.capture_routing(True)
+            chosen = lambda: torch.cat([torch.cat([x.cpu() for x in cap[l]]) for l in sorted(cap)], 1)
             s = e.acquire_slot()
             rows = [e.step([StepEntry(s, long_prompt, [8191, 8192, 8999])]).float().cpu()]
+            experts = [chosen()[[8191, 8192, 8999]]]
             e.release_slot(s)
             s = e.acquire_slot()
             e.step([StepEntry(s, dec[:8150], [])])
             for t in dec[8150:]:
+                for lst in cap.values():
+                    lst.clear()
                 rows.append(e.step([StepEntry(s, [t], [0])]).float().cpu())
+                experts.append(chosen())
             e.release_slot(s)
             e.check_device_errors()
             e.cache.check_consistency()
-            outs[fast] = torch.cat(rows)
+            outs[fast] = (torch.cat(rows), torch.cat(experts))
             del e
         finally:
             attention.use_tensor_core_kernels = True
             linear.use_tensor_cores = True
-    a, b = outs[True], outs[False]
+    (a, ea), (b, eb) = outs[True], outs[False]
+    same = (ea == eb).all(-1)
+    assert float(same.float().mean()) >= 0.95, f"{int((~same).sum())} of {len(same)} rows chose other experts"
+    a, b = a[same], b[same]
     scale = float(b.abs().max())
     err = float((a - b).abs().max()) / scale
-    print(f"long context: tensor-core vs general kernels, worst relative difference {err:.3e}")
+    print(f"long context: tensor-core vs general kernels, worst relative difference {err:.3e} "
+          f"({int((~same).sum())} rows with other experts set aside)")
     assert err <= 3e-2
     assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.9
 

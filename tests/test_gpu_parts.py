@@ -230,7 +230,7 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
                      head=PartSpec("linear_head", {"weight": "emb.weight"}), initializer_range=0.1)
     reqs = tensor_requirements(spec)
     src = RandomSource(reqs, 3, 0.1)
-    drawn = {n: src.get(n, "cpu") for n in src.names()}       # draws on the CPU and on a GPU differ: use one
+    drawn = {n: src.get(n, "cpu") for n in src.names()}
     W = {n: t.float() for n, t in drawn.items()}
     e = Engine(spec, DictSource(drawn), dtype="float32", max_tokens=512)
     assert not e.cache.groups and len(e.cache.state) == 4          # no keys or values, two states per entry

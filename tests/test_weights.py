@@ -88,6 +88,40 @@ def test_random_source_is_order_independent_and_seeded():
     assert not torch.equal(first, c.get(name, "cpu"))
 
 
+def test_random_draws_are_counter_based():
+    """Element i of a tensor depends on (seed, name, i) alone: any cut of the stream gives the same values, and
+    they are normal with the asked deviation."""
+    from cpi_b200.weights.random_init import counter_normal
+    x = counter_normal(777, 0, 1 << 18, 0.05, "cpu")
+    assert torch.equal(counter_normal(777, 12345, 100, 0.05, "cpu"), x[12345:12445])
+    assert abs(float(x.mean())) < 5e-4 and abs(float(x.std()) - 0.05) < 5e-4
+    assert abs(float(((x / 0.05) ** 4).mean()) - 3.0) < 0.1          # the fourth moment of a normal
+    assert abs(float((x[1:] * x[:-1]).mean())) < 2e-5                # neighbours do not correlate
+    # the integer mixing against plain Python arithmetic modulo 2^64
+    from cpi_b200.weights.random_init import _normal_table
+    m = (1 << 64) - 1
+    for i in (0, 1, 4097, (1 << 18) - 1):
+        z = (i * 0x9E3779B97F4A7C15 + 777) & m
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+        z ^= z >> 31
+        assert float(x[i]) == float(_normal_table()[z >> 48] * 0.05)
+
+
+def test_missing_names_come_with_the_nearest_found_name(tmp_path):
+    d = tiny.make_model_dir("A")
+    _, spec = spec_from_model_dir(d)
+    reqs = tensor_requirements(spec)
+    src = SafetensorsSource(d)
+    tensors = {("language_model." + n if "layers.1." in n else n): src.get(n, "cpu") for n in src.names()}
+    with pytest.raises(WeightsError) as e:
+        check_source(reqs, DictSource(tensors), ())
+    assert ("model.layers.1.self_attn.o_proj.weight  expected shape [64, 64]  "
+            "(did you mean language_model.model.layers.1.self_attn.o_proj.weight?)") in str(e.value)
+    with pytest.raises(Exception, match=r"tensor not found: model\.norm\.weigth \(did you mean model\.norm\.weight\?\)"):
+        src.dir.entry("model.norm.weigth")
+
+
 def test_one_error_lists_missing_unexpected_and_wrong_shapes():
     d = tiny.make_model_dir("A")
     _, spec = spec_from_model_dir(d)
