@@ -37,18 +37,21 @@ class Model:
 
     @classmethod
     def load(cls, model_dir: str, *, dtype="bfloat16", max_batch: int = 1, max_context: int = 2048,
-             max_tokens: Optional[int] = None, device="cuda:0", page_size: int = 64) -> "Model":
+             max_tokens: Optional[int] = None, device="cuda:0", page_size: int = 64,
+             config_overrides: Optional[dict] = None) -> "Model":
         """`max_batch` sequences of up to `max_context` positions each (the reference's EngineOptions
-        names, include/engine/llama_engine.hpp:67-68); `max_tokens` bounds the cache instead when given."""
-        eng = Engine.from_model_dir(model_dir, dtype=dtype, device=device,
+        names, include/engine/llama_engine.hpp:67-68); `max_tokens` bounds the cache instead when given.
+        `config_overrides`: config.json keys that replace the file's, e.g. {"rope_theta": 1e6} or a
+        preset of `cpi_b200.config.llama4.PRESETS`."""
+        eng = Engine.from_model_dir(model_dir, config_overrides, dtype=dtype, device=device,
                                     **cls._cache_args(max_batch, max_context, max_tokens, page_size))
         return cls(eng, max_batch)
 
     @classmethod
     def random(cls, config_json: dict, seed: int = 0, *, dtype="bfloat16", max_batch: int = 1,
                max_context: int = 2048, max_tokens: Optional[int] = None, device="cuda:0",
-               page_size: int = 64) -> "Model":
-        eng = Engine.from_random(config_json, seed, dtype=dtype, device=device,
+               page_size: int = 64, config_overrides: Optional[dict] = None) -> "Model":
+        eng = Engine.from_random(config_json, seed, config_overrides, dtype=dtype, device=device,
                                  **cls._cache_args(max_batch, max_context, max_tokens, page_size))
         return cls(eng, max_batch)
 
@@ -64,6 +67,25 @@ class Model:
 
     def generate_requests(self, requests: Sequence[GenerationRequest], on_token=None) -> list:
         return self.generator.generate(requests, on_token)
+
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], logits="last"):
+        """One step of the engine on sequences that the caller manages: `slots` from `acquire_slot()`,
+        `tokens[i]` the next tokens of slot i (all prompts, or one token each).  `logits`: "last" (one row per
+        sequence), "all", or a list of places per sequence.  Returns float32 logits [rows, vocab] on the
+        device, valid until the next step.  Give slots back with `release_slot()`."""
+        if logits == "last":
+            want = [[len(t) - 1] for t in tokens]
+        elif logits == "all":
+            want = [list(range(len(t))) for t in tokens]
+        else:
+            want = [list(w) for w in logits]
+        return self.engine.step([StepEntry(int(s), list(t), w) for s, t, w in zip(slots, tokens, want)])
+
+    def acquire_slot(self) -> int:
+        return self.engine.acquire_slot()
+
+    def release_slot(self, slot: int) -> None:
+        self.engine.release_slot(slot)
 
     def next_token_logits(self, prompt: Sequence[int]):
         """Float32 logits [vocab] after the prompt (the reference's inspect_next_logits,

@@ -3,12 +3,19 @@
 Flags keep the reference's names and meanings where it has them (src/app/main_cli.cpp:195-343):
 positional model folder, --tokens, --max-new (16), --temp (0.8), --max-context (2048), --top-k (40),
 --top-p (0.9), --repeat-penalty (1.0), --no-repeat-ngram (0), --eos-token (-1 disables),
---inspect-next-topk, --trace-steps, --benchmark, --benchmark-reps, --benchmark-warmup; the
-LLAMA_INFER_* environment variables give defaults (:45-80, :190-193).  Output lines: "Output tokens:"
-(prompt + generated, src/app/main_modes.cpp:507-513), "[perf]" (:549-559), "[bench]" (:590-606).
-Exit codes: 1 argument error, 2 fatal error (src/main.cpp:67, :248).  Text prompts and tokenisers are
-outside this library: prompts are token ids.  Added here: --tokens-file, --batch-file, --stop-ids,
---seed, --dtype, --random.
+--rope-theta, --inspect-next-topk, --trace-steps, --benchmark, --benchmark-reps, --benchmark-warmup,
+--benchmark-phases, --interactive; the LLAMA_INFER_* environment variables give defaults (:45-80,
+:190-193).  Output lines: "Output tokens:" (prompt + generated, src/app/main_modes.cpp:507-513), "[perf]"
+or "[perf-avg]" (:549-559), "[bench]" or "[bench-avg] reps=" (:560-606), "[bench-phase]" or
+"[bench-phase-avg]" (:576-617).  Exit codes: 1 argument error, 2 fatal error (src/main.cpp:67, :248).
+Text prompts and tokenisers are outside this library: prompts are token ids, so --prompt, --tokenizer
+and --stop-text are answered with an argument error that names --tokens and --stop-ids, and --cpu with
+a fatal error (there is no CPU path).  --interactive speaks the reference's line-by-line JSON protocol
+(src/app/main_modes.cpp:46-270) with token ids in place of text: a request {"id", "tokens", "max_new",
+"temp", "stop_ids", "shutdown"}, events "start", "delta" {"tokens": [id]}, "metrics" {"token_index"},
+"done" {"tokens", "elapsed_ms", "generated_tokens", "tok_per_s"}, "error" {"error"}.
+Added here: --tokens-file, --batch-file, --stop-ids, --seed, --dtype, --random, --preset, --rope-pairing,
+--qk-norm-order, --qk-norm-scope, --router-gate, --dump-logits.
 """
 from __future__ import annotations
 
@@ -17,6 +24,10 @@ import json
 import os
 import sys
 import time
+
+from ..config.llama4 import PRESETS, QK_NORM_ORDERS, QK_NORM_SCOPES, ROPE_PAIRINGS, ROUTER_GATES
+
+PHASES = ("rmsnorm", "qkv", "kv_store", "attention", "wo", "mlp", "moe_router", "moe_expert", "moe_merge", "lm_head")
 
 
 def _env(name, cast, default):
@@ -61,7 +72,30 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--benchmark", action="store_true")
     p.add_argument("--benchmark-reps", type=int, default=1)
     p.add_argument("--benchmark-warmup", type=int, default=0)
+    p.add_argument("--benchmark-phases", action="store_true", help="also time the phases of the decode steps")
+    p.add_argument("--rope-theta", type=float, default=None, help="replaces config.json's rope_theta")
+    p.add_argument("--preset", choices=sorted(PRESETS), default=None,
+                   help="a named set of the options below (and, for reference_compat, of the layer pattern)")
+    p.add_argument("--rope-pairing", choices=ROPE_PAIRINGS, default=None)
+    p.add_argument("--qk-norm-order", choices=QK_NORM_ORDERS, default=None)
+    p.add_argument("--qk-norm-scope", choices=QK_NORM_SCOPES, default=None)
+    p.add_argument("--router-gate", choices=ROUTER_GATES, default=None)
+    p.add_argument("--dump-logits", metavar="FILE",
+                   help="write the logits after each prompt as little-endian float32 [prompts, vocab]")
+    p.add_argument("--interactive", action="store_true", help="requests as JSON lines on standard input")
+    p.add_argument("--cpu", action="store_true", help=argparse.SUPPRESS)
+    for flag in ("--prompt", "--tokenizer", "--stop-text", "--system-prompt"):
+        p.add_argument(flag, default=None, help=argparse.SUPPRESS)
     return p
+
+
+def config_overrides(a) -> dict:
+    """The config.json keys that the command line replaces: the preset first, single options over it."""
+    out = dict(PRESETS[a.preset]) if a.preset else {}
+    for key in ("rope_theta", "rope_pairing", "qk_norm_order", "qk_norm_scope", "router_gate"):
+        if getattr(a, key) is not None:
+            out[key] = getattr(a, key)
+    return out
 
 
 def validate(a) -> None:
@@ -70,6 +104,15 @@ def validate(a) -> None:
         raise SystemExit("argument error: " + msg)
     if not a.model_dir and not a.random:
         bad("a model folder (or --random CONFIG.json) is required")
+    for flag, instead in (("prompt", "--tokens / --tokens-file"), ("tokenizer", "--tokens / --tokens-file"),
+                          ("system_prompt", "--tokens / --tokens-file"), ("stop_text", "--stop-ids")):
+        if getattr(a, flag) is not None:
+            bad(f"--{flag.replace('_', '-')} needs a tokeniser, which this library does not have: give token ids "
+                f"with {instead}")
+    if a.rope_theta is not None and not a.rope_theta > 0:
+        bad("--rope-theta must be > 0")
+    if a.benchmark_phases or a.benchmark_reps != 1 or a.benchmark_warmup != 0:
+        a.benchmark = True                     # as the reference's parser does (src/app/main_cli.cpp:255-265)
     if a.max_new < 1:
         bad("--max-new must be >= 1")
     if a.max_context < 1:
@@ -109,8 +152,11 @@ def main(argv=None) -> int:
         print(f"argument error: {e}", file=sys.stderr)
         return 1
     try:
+        if a.cpu:
+            raise RuntimeError("--cpu: this library has no CPU path; the model runs on its CUDA kernels only")
         from ..api import Model
-        kw = dict(dtype=a.dtype, max_batch=len(prompts), max_context=a.max_context)
+        kw = dict(dtype=a.dtype, max_batch=len(prompts), max_context=a.max_context,
+                  config_overrides=config_overrides(a))
         if a.random:
             with open(a.random) as f:
                 model = Model.random(json.load(f), a.seed, **kw)
@@ -124,8 +170,18 @@ def main(argv=None) -> int:
         else:
             stops = [a.eos_token]
         stops += extra_stops
+        gen_kw = dict(max_new=a.max_new, temperature=a.temp, top_k=a.top_k, top_p=a.top_p,
+                      repetition_penalty=a.repeat_penalty, no_repeat_ngram_size=a.no_repeat_ngram,
+                      seed=a.seed, stop_ids=stops)
+        if a.interactive:
+            return interactive(model, gen_kw, sys.stdin, sys.stdout)
         print(f"[info] {spec.architecture} layers={len(spec.layers)} hidden={spec.hidden_size} "
               f"vocab={spec.vocab_size} dtype={a.dtype} prompts={len(prompts)}")
+        if a.dump_logits:
+            import numpy as np
+            rows = [model.next_token_logits(p).float().cpu().numpy() for p in prompts]
+            np.stack(rows).astype("<f4").tofile(a.dump_logits)
+            print(f"[info] logits after {len(rows)} prompt(s) written to {a.dump_logits}")
         if a.inspect_next_topk > 0:
             import torch
             lg = model.next_token_logits(prompts[0])
@@ -138,34 +194,104 @@ def main(argv=None) -> int:
             res = model.generate([prompts[0]], max_new=a.trace_steps, temperature=0.0, stop_ids=[])
             for step, t in enumerate(res[0].tokens):
                 print(f"  step={step} choose id={t}")
-        gen_kw = dict(max_new=a.max_new, temperature=a.temp, top_k=a.top_k, top_p=a.top_p,
-                      repetition_penalty=a.repeat_penalty, no_repeat_ngram_size=a.no_repeat_ngram,
-                      seed=a.seed, stop_ids=stops)
         for _ in range(a.benchmark_warmup if a.benchmark else 0):
             model.generate(prompts, **gen_kw)
         reps = a.benchmark_reps if a.benchmark else 1
+        repeated = a.benchmark and (a.benchmark_reps > 1 or a.benchmark_warmup > 0)
         tot_ms = pre_ms = dec_ms = 0.0
+        gen = 0
         for _ in range(reps):
             t0 = time.perf_counter()
             results = model.generate(prompts, **gen_kw)
             tot_ms += (time.perf_counter() - t0) * 1e3
             pre_ms += model.stats().prefill_ms
             dec_ms += model.stats().decode_ms
+            gen += model.stats().generated_tokens
         for p, r in zip(prompts, results):
             print("Output tokens:" + "".join(f" {t}" for t in list(p) + r.tokens))
         st = model.stats()
-        gen = st.generated_tokens
-        tot_ms, pre_ms, dec_ms = tot_ms / reps, pre_ms / reps, dec_ms / reps
-        print(f"[perf] generated_tokens={gen} elapsed_ms={tot_ms:.2f} tok_per_s={1e3 * gen / max(tot_ms, 1e-9):.2f}")
+        gen, tot_ms, pre_ms, dec_ms = gen // reps, tot_ms / reps, pre_ms / reps, dec_ms / reps
+        rate = lambda n, ms: 1e3 * n / ms if n > 0 and ms > 0 else 0.0
+        print(f"[perf{'-avg' if repeated else ''}] generated_tokens={gen} elapsed_ms={tot_ms:.2f} "
+              f"tok_per_s={rate(gen, tot_ms):.2f}")
         if a.benchmark:
             pt = max(st.prompt_tokens - len(prompts), 0)
-            print(f"[bench] prefill_tokens={pt} prefill_ms={pre_ms:.2f} "
-                  f"prefill_tok_per_s={1e3 * pt / max(pre_ms, 1e-9):.2f} decode_tokens={gen} "
-                  f"decode_ms={dec_ms:.2f} decode_tok_per_s={1e3 * gen / max(dec_ms, 1e-9):.2f}")
+            line = (f"prefill_tokens={pt} prefill_ms={pre_ms:.2f} prefill_tok_per_s={rate(pt, pre_ms):.2f} "
+                    f"decode_tokens={gen} decode_ms={dec_ms:.2f} decode_tok_per_s={rate(gen, dec_ms):.2f}")
+            if repeated:
+                print(f"[bench-avg] reps={reps} {line} total_ms={tot_ms:.2f} total_tok_per_s={rate(gen, tot_ms):.2f}")
+            else:
+                print(f"[bench] {line}")
+        if a.benchmark_phases:
+            # a run of its own: with the phase brackets on, steps run eagerly and on one stream, which
+            # must not disturb the figures above
+            timer = model.engine.profile_phases(True)
+            try:
+                for _ in range(reps):
+                    model.generate(prompts, **gen_kw)
+                ms = timer.collect().get("decode", {})
+            finally:
+                model.engine.profile_phases(False)
+            print(f"[bench-phase{'-avg' if repeated else ''}]"
+                  + "".join(f" {name}_ms={ms.get(name, 0.0) / reps:.2f}" for name in PHASES))
         return 0
     except Exception as e:                                    # noqa: BLE001  (the reference: catch, print, 2)
         print(f"fatal: {type(e).__name__}: {e}", file=sys.stderr)
         return 2
+
+
+def interactive(model, defaults: dict, inp, out) -> int:
+    """Requests as JSON lines, answered with event lines (src/app/main_modes.cpp:46-270), on token ids."""
+    def event(kind, rid, **extra):
+        body = {"type": kind}
+        if rid:
+            body["id"] = rid
+        body.update(extra)
+        out.write(json.dumps(body, separators=(",", ":")) + "\n")
+        out.flush()
+
+    for line in inp:
+        line = line.strip()
+        if not line:
+            continue
+        rid = ""
+        try:
+            req = json.loads(line)
+            if not isinstance(req, dict):
+                raise ValueError("a request is a JSON object")
+            rid = str(req.get("id", ""))
+            if req.get("shutdown", False):
+                event("done", rid, tokens=[], elapsed_ms=0)
+                break
+            tokens = req.get("tokens")
+            if not isinstance(tokens, list) or not tokens:
+                raise ValueError("interactive request missing 'tokens'")
+            kw = dict(defaults)
+            kw["max_new"] = max(1, int(req.get("max_new", defaults["max_new"])))
+            kw["temperature"] = max(0.0, float(req.get("temp", defaults["temperature"])))
+            if "stop_ids" in req:
+                kw["stop_ids"] = [int(t) for t in req["stop_ids"]]
+            stops = set(kw["stop_ids"] or ())
+            sent = []
+
+            def on_token(_request, token):
+                # a stop token ends the answer and is not part of it (:196-199)
+                if token in stops:
+                    return False
+                sent.append(int(token))
+                event("delta", rid, tokens=[int(token)])
+                event("metrics", rid, metrics={"token_index": len(sent)})
+                return True
+
+            t0 = time.perf_counter()
+            event("start", rid)
+            model.generate([[int(t) for t in tokens]], on_token=on_token, **kw)
+            ms = int((time.perf_counter() - t0) * 1e3)
+            event("done", rid, tokens=sent, elapsed_ms=ms, generated_tokens=len(sent),
+                  tok_per_s=round(1e3 * len(sent) / ms, 2) if ms > 0 and sent else 0.0)
+        except Exception as e:                                # noqa: BLE001  (an error event, and on to the next line)
+            event("error", rid, error=f"{type(e).__name__}: {e}")
+    return 0
 
 
 if __name__ == "__main__":

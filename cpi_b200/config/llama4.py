@@ -60,6 +60,16 @@ QK_NORM_ORDERS = ("after_rope", "before_rope")
 QK_NORM_SCOPES = ("rope_layers", "all_layers")
 ROUTER_GATES = ("sigmoid_input", "sigmoid_output", "none")
 
+# Named sets of overrides.  "llama4": the library's defaults.  "reference_compat": what the reference's
+# Llama4 engines compute (src/engine/llama4_cpu_engine.cpp:296-329): head norm before the rotation and on
+# every layer, every layer rotates and sees all keys, no temperature on the queries, no gate value.
+PRESETS = {
+    "llama4": {"qk_norm_order": "after_rope", "qk_norm_scope": "rope_layers", "router_gate": "sigmoid_input"},
+    "reference_compat": {"qk_norm_order": "before_rope", "qk_norm_scope": "all_layers", "router_gate": "none",
+                         "nope_layer_interval": 0, "no_rope_layers": None, "layer_types": None,
+                         "attention_chunk_size": 0, "attn_temperature_tuning": False},
+}
+
 
 @dataclass(frozen=True)
 class Llama4TextConfig:

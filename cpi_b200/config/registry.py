@@ -50,9 +50,24 @@ def architecture_of(raw_config: dict) -> Architecture:
     return get_architecture(archs[0])
 
 
-def spec_from_model_dir(model_dir: str):
+def apply_overrides(raw_config: dict, overrides: dict | None) -> dict:
+    """A copy of a config.json dictionary with `overrides` written over its keys, in the nested
+    `text_config` object when the file has one (that is where such a file keeps the decoder's keys).
+    The way options of a command line (the reference's --rope-theta, src/app/main_cli.cpp:280-281)
+    and named presets reach the typed configuration: as config.json keys, checked like the file's own."""
+    if not overrides:
+        return raw_config
+    out = dict(raw_config)
+    if isinstance(out.get("text_config"), dict):
+        out["text_config"] = {**out["text_config"], **overrides}
+    else:
+        out.update(overrides)
+    return out
+
+
+def spec_from_model_dir(model_dir: str, overrides: dict | None = None):
     """(typed configuration, ModelSpec) of the model folder's config.json."""
-    raw = read_config_json(model_dir)
+    raw = apply_overrides(read_config_json(model_dir), overrides)
     arch = architecture_of(raw)
     cfg = arch.parse_config(raw)
     spec = arch.build_spec(cfg)

@@ -16,10 +16,11 @@ from typing import Optional, Sequence
 import torch
 
 from ..cache import CacheManager
-from ..config.registry import architecture_of, spec_from_model_dir
+from ..config.registry import apply_overrides, architecture_of, spec_from_model_dir
 from ..config.spec import ModelSpec
 from ..csrc import lib as K
 from ..parts import Workspace
+from .. import phases
 from ..weights import RandomSource, SafetensorsSource
 from .batch import BatchStager
 from .model import DecoderModel
@@ -71,11 +72,13 @@ class Engine:
         self._graphs = {}
         self.graph_kernel_launches = 0       # kernels run by graph replays (they are not host launches)
         self._routing_capture = False
+        self._phase_timer = None
 
     # ---- construction ----------------------------------------------------------------------------
     @classmethod
-    def from_model_dir(cls, model_dir: str, **kw) -> "Engine":
-        cfg, spec = spec_from_model_dir(model_dir)
+    def from_model_dir(cls, model_dir: str, config_overrides: Optional[dict] = None, **kw) -> "Engine":
+        """`config_overrides`: config.json keys that replace the file's (for instance {"rope_theta": 1e6})."""
+        cfg, spec = spec_from_model_dir(model_dir, config_overrides)
         src = SafetensorsSource(model_dir)
         try:
             return cls(spec, src, config=cfg, **kw)
@@ -83,9 +86,10 @@ class Engine:
             src.close()
 
     @classmethod
-    def from_random(cls, config_json: dict, seed: int = 0, **kw) -> "Engine":
+    def from_random(cls, config_json: dict, seed: int = 0, config_overrides: Optional[dict] = None, **kw) -> "Engine":
         """A model with random weights drawn on the device (nothing is written to disk)."""
         from .model import tensor_requirements
+        config_json = apply_overrides(config_json, config_overrides)
         arch = architecture_of(config_json)
         cfg = arch.parse_config(config_json)
         spec = arch.build_spec(cfg)
@@ -166,7 +170,9 @@ class Engine:
         n_new = [len(t) for t in toks]
         starts = self.cache.prepare_step(slots, n_new)
         decode = max(n_new) == 1
-        if decode and self.use_graphs and not self._routing_capture:
+        if self._phase_timer is not None:
+            self._phase_timer.kind = "decode" if decode else "prefill"
+        if decode and self.use_graphs and not self._routing_capture and self._phase_timer is None:
             logits = self._run_decode_graph(slots, starts, toks, wants, device_tokens)
         else:
             batch = self.stager.stage(slots, starts, toks, wants, self.dtype)
@@ -226,6 +232,14 @@ class Engine:
                 if on:
                     out[i] = ff.capture
         return out
+
+    def profile_phases(self, on: bool = True):
+        """Starts (or stops) per-phase device timing of every step (the reference's profile_decode_phases,
+        include/engine/llama_engine.hpp:65-98).  While on, steps run eagerly on one stream.  Returns the
+        timer; `timer.collect()` gives {"prefill" | "decode": {phase: milliseconds}} summed over the steps."""
+        self._phase_timer = phases.PhaseTimer() if on else None
+        phases.install(self._phase_timer)
+        return self._phase_timer
 
     def check_device_errors(self) -> None:
         """Raises if a kernel flagged a bad input since the last check (synchronises)."""

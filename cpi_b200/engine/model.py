@@ -10,6 +10,7 @@ from ..csrc import lib as K
 from ..parts import base as parts_base
 from ..parts import Workspace, build_part
 from ..parts.linear import project
+from ..phases import phase
 from ..weights.store import TensorReq, check_source
 
 
@@ -115,7 +116,8 @@ class DecoderModel:
         """Runs the step's tokens through every run entry; returns float32 logits [n_want, vocab]."""
         T, H = batch.n_tokens, self.spec.hidden_size
         x = self.ws.get("residual", (T, H), torch.float32)
-        K.embedding(batch.tokens, self.embedding, x, self.err_flag)
+        with phase("embedding"):
+            K.embedding(batch.tokens, self.embedding, x, self.err_flag)
         for i, e in enumerate(self.spec.run_order):
             layer = self.layers[e.layer]
             owner = i if e.cache_of is None else e.cache_of
@@ -124,8 +126,10 @@ class DecoderModel:
         R = batch.n_want
         logits = self.ws.get("logits", (R, self.spec.vocab_size), torch.float32)   # valid until the next step
         if R:
-            xn = self.final_norm(x, self.dtype, rows=batch.want_rows)
-            project(xn, self.head, logits)
+            with phase("rmsnorm"):
+                xn = self.final_norm(x, self.dtype, rows=batch.want_rows)
+            with phase("lm_head"):
+                project(xn, self.head, logits)
         return logits
 
 

@@ -18,6 +18,7 @@ import torch
 
 from ..cache.manager import KVRequirement
 from ..csrc import lib as K
+from ..phases import phase
 from ..weights.store import TensorReq
 from .base import Mixer, build_part, register_mixer
 from .linear import MODE_ADD, project
@@ -86,18 +87,22 @@ class AttentionMixer(Mixer):
         T = h.shape[0]
         dt = h.dtype
         qkv = self.ws.get("attn_qkv", (T, self.w_qkv.shape[0]), dt)
-        project(h, self.w_qkv, qkv)
+        with phase("qkv"):
+            project(h, self.w_qkv, qkv)
         k_cache, v_cache, table, page_size = cache.kv()
         q = self.ws.get("attn_q", (T, self.nh * self.d), dt)
-        K.qkv_post(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
-                   batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
-                   inv_freq=self.position.inv_freq, interleaved=self.position.interleaved,
-                   qk_norm=self.qk_norm, norm_before_rope=self.norm_before_rope,
-                   norm_eps=self.qk_norm_eps, temperature=self.temperature,
-                   write_kv=self.has_kv and cache.owns)
+        with phase("kv_store"):          # head norm, rotation, temperature and the write into the cache: one kernel
+            K.qkv_post(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
+                       batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
+                       inv_freq=self.position.inv_freq, interleaved=self.position.interleaved,
+                       qk_norm=self.qk_norm, norm_before_rope=self.norm_before_rope,
+                       norm_eps=self.qk_norm_eps, temperature=self.temperature,
+                       write_kv=self.has_kv and cache.owns)
         att = self.ws.get("attn_out", (T, self.nh * self.d), dt)
-        self.attend(q, att, k_cache, v_cache, table, page_size, batch)
-        project(att, self.w_o, residual, MODE_ADD)
+        with phase("attention"):
+            self.attend(q, att, k_cache, v_cache, table, page_size, batch)
+        with phase("wo"):
+            project(att, self.w_o, residual, MODE_ADD)
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]

@@ -2,6 +2,7 @@
 (the order of src/engine/llama4_cpu_engine.cpp:300-329)."""
 from __future__ import annotations
 
+from ..phases import phase
 from .base import Block, register_block
 
 
@@ -12,7 +13,9 @@ class PreNormBlock(Block):
         super().__init__(spec, prefix)
 
     def run(self, layer, residual, batch, cache):
-        h = layer.mixer_norm(residual, batch.dtype)
+        with phase("rmsnorm"):
+            h = layer.mixer_norm(residual, batch.dtype)
         layer.mixer.forward(h, residual, batch, cache)
-        h2 = layer.feed_forward_norm(residual, batch.dtype)
+        with phase("rmsnorm"):
+            h2 = layer.feed_forward_norm(residual, batch.dtype)
         layer.feed_forward.forward(h2, residual, batch)

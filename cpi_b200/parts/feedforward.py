@@ -20,6 +20,7 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib as K
+from ..phases import active as phases_active, phase
 from ..weights.store import TensorReq
 from .base import FeedForward, register_feed_forward
 from .linear import MODE_ADD, MODE_STORE, MODE_SWIGLU, project
@@ -54,8 +55,9 @@ class DenseSwiGLU(FeedForward):
 
     def forward(self, h, residual, batch):
         a = self.ws.get("ffn_act", (h.shape[0], self.inter), h.dtype)
-        project(h, self.w_gate_up, a, MODE_SWIGLU)
-        project(a, self.w_down, residual, MODE_ADD)
+        with phase("mlp"):
+            project(h, self.w_gate_up, a, MODE_SWIGLU)
+            project(a, self.w_down, residual, MODE_ADD)
 
 
 @register_feed_forward("moe_swiglu")
@@ -116,7 +118,7 @@ class MoESwiGLU(FeedForward):
         T, E, Kk = h.shape[0], self.n_experts, self.top_k
         ws, i32, f32 = self.ws, torch.int32, torch.float32
         forked = None
-        if self.shared is not None and self.overlap_shared and h.is_cuda:
+        if self.shared is not None and self.overlap_shared and h.is_cuda and phases_active() is None:
             if self._side_stream is None:
                 self._side_stream = torch.cuda.Stream(device=h.device)
             fork = torch.cuda.Event()
@@ -137,32 +139,37 @@ class MoESwiGLU(FeedForward):
         # rows sorted by expert, so that each expert reads a contiguous block (when rows are 16-byte multiples)
         sortable = (h.shape[1] * h.element_size()) % 16 == 0 and h.stride(0) * h.element_size() % 16 == 0
         sorted_h = ws.get("moe_in", (M, self.hidden), h.dtype) if sortable else None
-        gathered = K.moe_route(h, self.w_router, idx, gate, logits, offsets, row_token, row_scale, row_of_slot,
-                               top_k=Kk, sigmoid_gate=self.gate_mode != "none", sorted_h=sorted_h)
+        with phase("moe_router"):
+            gathered = K.moe_route(h, self.w_router, idx, gate, logits, offsets, row_token, row_scale, row_of_slot,
+                                   top_k=Kk, sigmoid_gate=self.gate_mode != "none", sorted_h=sorted_h)
         if self.capture is not None:
             self.capture.append(idx.clone())
         hint = max(1, -(-M // E))
         act = ws.get("moe_act", (M, self.inter), h.dtype)
         in_scale = row_scale if self.gate_mode == "sigmoid_input" else None
-        if sortable:
-            if not gathered:
-                K.gather_rows(h, row_token, sorted_h)
-            project(sorted_h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, row_scale=in_scale,
-                    group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
-        else:
-            project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token, row_scale=in_scale,
-                    group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
-        out_scale = row_scale if self.gate_mode == "sigmoid_output" else None
-        if Kk == 1 and forked is None:
-            project(act, self.w_down, residual, MODE_ADD, m_rows=M, out_rows=row_token, row_scale=out_scale,
-                    group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
-        else:
-            y = ws.get("moe_y", (M, self.hidden), f32)
-            project(act, self.w_down, y, MODE_STORE, m_rows=M, row_scale=out_scale,
-                    group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+        with phase("moe_expert"):
+            if sortable:
+                if not gathered:
+                    K.gather_rows(h, row_token, sorted_h)
+                project(sorted_h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, row_scale=in_scale,
+                        group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+            else:
+                project(h, self.w_gate_up, act, MODE_SWIGLU, m_rows=M, a_rows=row_token, row_scale=in_scale,
+                        group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+            out_scale = row_scale if self.gate_mode == "sigmoid_output" else None
+            direct = Kk == 1 and forked is None
+            if direct:
+                project(act, self.w_down, residual, MODE_ADD, m_rows=M, out_rows=row_token, row_scale=out_scale,
+                        group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+            else:
+                y = ws.get("moe_y", (M, self.hidden), f32)
+                project(act, self.w_down, y, MODE_STORE, m_rows=M, row_scale=out_scale,
+                        group_offsets=offsets, n_groups=E, rows_per_group_hint=hint)
+        if not direct:
             if forked is not None:
                 torch.cuda.current_stream().wait_event(forked)
-            K.moe_combine(residual, y, row_of_slot, top_k=Kk)
+            with phase("moe_merge"):
+                K.moe_combine(residual, y, row_of_slot, top_k=Kk)
         if forked is not None:
             return
         if self.shared is not None:

@@ -134,3 +134,27 @@ def test_run_order_validation():
     for bad in [(RunEntry(7),), (RunEntry(0, cache_of=0),), (RunEntry(0), RunEntry(1, cache_of=0), RunEntry(2, cache_of=1))]:
         with pytest.raises(ValueError):
             dataclasses.replace(s, run_order=bad).validate()
+
+
+def test_overrides_and_presets():
+    """Overrides are config.json keys written over the file's (inside text_config when the file nests them),
+    and go through the same checks."""
+    from cpi_b200.config.llama4 import PRESETS
+    from cpi_b200.config.registry import apply_overrides, architecture_of
+    for name in ("A", "B"):
+        raw = tiny.config(name)
+        arch = architecture_of(raw)
+        assert apply_overrides(raw, None) is raw and apply_overrides(raw, {}) is raw
+        new = apply_overrides(raw, {"rope_theta": 12345.0, **PRESETS["reference_compat"]})
+        assert new is not raw and arch.parse_config(raw).rope_theta != 12345.0       # the input is not touched
+        cfg = arch.parse_config(new)
+        assert cfg.rope_theta == 12345.0 and cfg.router_gate == "none" and cfg.qk_norm_order == "before_rope"
+        assert cfg.attention_chunk_size == 0 and not cfg.attn_temperature_tuning
+        assert all(cfg.layer_uses_rope(i) and cfg.layer_has_qk_norm(i) == cfg.use_qk_norm
+                   for i in range(cfg.num_hidden_layers))
+        spec = arch.build_spec(cfg)
+        assert all(l.mixer.params["window"]["kind"] == "full" for l in spec.layers)
+        back = arch.parse_config(apply_overrides(new, PRESETS["llama4"]))
+        assert (back.qk_norm_order, back.qk_norm_scope, back.router_gate) == ("after_rope", "rope_layers", "sigmoid_input")
+        with pytest.raises(ConfigError, match="router_gate"):
+            arch.parse_config(apply_overrides(raw, {"router_gate": "softmax"}))

@@ -245,3 +245,44 @@ def test_one_step_ahead_loop_is_left_for_callbacks_and_history_options():
     assert len(calls) == 6
     g.generate([GenerationRequest([1], 3)])
     assert len(calls) == 6                        # plain requests run ahead: sample_device, not sample
+
+
+def test_command_line_argument_errors_and_interactive_protocol(capsys):
+    """What the command line decides without a GPU: flags that need a tokeniser are argument errors (exit 1)
+    that name the flag to use, --cpu is a fatal error (exit 2), and the interactive loop's events."""
+    import io
+    import json
+    from cpi_b200.cli import llama_infer as cli
+    for argv, word in ((["m", "--prompt", "hi"], "--tokens"), (["m", "--stop-text", "x"], "--stop-ids"),
+                       (["m", "--tokenizer", "t.json"], "tokeniser"), (["m", "--rope-theta", "0"], "--rope-theta"),
+                       ([], "model folder"), (["m", "--preset", "nope"], "")):
+        assert cli.main(argv) == 1
+        assert word in capsys.readouterr().err
+    assert cli.main(["m", "--cpu"]) == 2 and "no CPU path" in capsys.readouterr().err
+    a = cli.build_parser().parse_args(["m", "--preset", "reference_compat", "--router-gate", "sigmoid_output",
+                                       "--rope-theta", "1e6", "--benchmark-phases"])
+    cli.validate(a)
+    assert a.benchmark and cli.config_overrides(a)["router_gate"] == "sigmoid_output"
+    assert cli.config_overrides(a)["qk_norm_order"] == "before_rope" and cli.config_overrides(a)["rope_theta"] == 1e6
+    assert cli.config_overrides(cli.build_parser().parse_args(["m"])) == {}
+
+    class FakeModel:
+        def generate(self, prompts, on_token=None, max_new=0, stop_ids=(), **kw):
+            self.kw = dict(kw, max_new=max_new, stop_ids=stop_ids)
+            for t in range(10, 10 + max_new):
+                if t in stop_ids or not on_token(0, t):
+                    break
+
+    m, out = FakeModel(), io.StringIO()
+    lines = [json.dumps({"id": "a", "tokens": [1, 2], "max_new": 3, "temp": -1}), "", "not json",
+             json.dumps({"id": "b", "tokens": [1], "stop_ids": [11]}), json.dumps({"shutdown": True}),
+             json.dumps({"id": "late", "tokens": [1]})]
+    defaults = dict(max_new=4, temperature=0.8, top_k=40, top_p=0.9, repetition_penalty=1.0, no_repeat_ngram_size=0,
+                    seed=0, stop_ids=[12])
+    assert cli.interactive(m, defaults, io.StringIO("\n".join(lines) + "\n"), out) == 0
+    ev = [json.loads(l) for l in out.getvalue().splitlines()]
+    assert [e["type"] for e in ev] == ["start", "delta", "metrics", "delta", "metrics", "done", "error", "start",
+                                       "delta", "metrics", "done", "done"]
+    assert ev[5]["tokens"] == [10, 11] and ev[5]["id"] == "a"       # the default stop id 12 ended it
+    assert ev[10]["tokens"] == [10] and "id" not in ev[11]
+    assert m.kw["temperature"] == 0.8 and m.kw["max_new"] == 4      # the second request ran on the defaults

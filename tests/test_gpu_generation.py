@@ -122,6 +122,119 @@ def test_command_line_prints_the_reference_lines(dirs):
     assert bad.returncode == 2 and "fatal" in bad.stderr
 
 
+def test_command_line_overrides_presets_phases_and_logits(dirs, tmp_path):
+    """--preset and --rope-theta reach the configuration (the plain implementation is given the same keys),
+    --dump-logits writes the rows after the prompts, repeated runs print the -avg lines and --benchmark-phases
+    one figure for each of the reference's phase names."""
+    import numpy as np
+    from cpi_b200.config.llama4 import PRESETS
+    d = dirs["A"]
+    f = str(tmp_path / "logits.f32")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama_infer"), d, "--tokens", "9,8,7,6,5",
+                        "--max-new", "5", "--temp", "0", "--dtype", "float32", "--eos-token", "-1",
+                        "--preset", "reference_compat", "--rope-theta", "10000", "--rope-pairing", "interleaved",
+                        "--benchmark-reps", "2", "--benchmark-phases", "--dump-logits", f],
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    c, W = P.read_config(d), P.read_weights(d)
+    c.update(PRESETS["reference_compat"], rope_theta=10000.0, rope_pairing="interleaved")
+    want = P.greedy_generate(c, W, [9, 8, 7, 6, 5], 5)
+    lines = r.stdout.splitlines()
+    out = [l for l in lines if l.startswith("Output tokens:")][0]
+    assert out.split(":")[1].split() == [str(t) for t in [9, 8, 7, 6, 5] + want]
+    plain_logits = P.forward(c, W, [9, 8, 7, 6, 5])[-1]
+    got = torch.from_numpy(np.fromfile(f, dtype="<f4").reshape(1, -1))[0]
+    assert float((got - plain_logits).abs().max()) <= 2e-4 * float(plain_logits.abs().max())
+    # the overrides matter: without them the same prompt gives other logits
+    assert float((P.forward(P.read_config(d), W, [9, 8, 7, 6, 5])[-1] - plain_logits).abs().max()) > 1e-2
+    assert any(l.startswith("[perf-avg] generated_tokens=5 ") for l in lines)
+    assert any(l.startswith("[bench-avg] reps=2 prefill_tokens=4 ") and "total_tok_per_s=" in l for l in lines)
+    phase = [l for l in lines if l.startswith("[bench-phase-avg] ")]
+    assert len(phase) == 1
+    fields = dict(x.split("=") for x in phase[0].split()[1:])
+    assert list(fields) == [n + "_ms" for n in ("rmsnorm", "qkv", "kv_store", "attention", "wo", "mlp", "moe_router",
+                                                "moe_expert", "moe_merge", "lm_head")]
+    for name in ("rmsnorm_ms", "qkv_ms", "kv_store_ms", "attention_ms", "wo_ms", "moe_router_ms", "moe_expert_ms",
+                 "lm_head_ms"):
+        assert float(fields[name]) > 0.0, name
+
+
+def test_run_llama4_prompt_script(dirs):
+    d = dirs["B"]
+    c, W = P.read_config(d), P.read_weights(d)
+    want = P.greedy_generate(c, W, [7, 7, 2], 8)
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "run_llama4_prompt"), d, "7,7,2", "--max-new", "8",
+                        "--dtype", "float32", "--stop-ids", str(want[4])], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    lines = r.stdout.splitlines()
+    first = want.index(want[4])
+    assert [l for l in lines if l.startswith("Output tokens:")][0].split(":")[1].split() == \
+        [str(t) for t in [7, 7, 2] + want[:first + 1]]                  # the stop token ends generation and is kept
+    assert [l for l in lines if l.startswith("Answer tokens:")][0].split(":")[1].split() == \
+        [str(t) for t in want[:first]]
+    text = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "run_llama4_prompt"), d, "hello there"],
+                          capture_output=True, text=True, timeout=300)
+    assert text.returncode == 1 and "token ids" in text.stderr
+
+
+def test_interactive_mode_speaks_json_lines(dirs):
+    import json
+    d = dirs["B"]
+    c, W = P.read_config(d), P.read_weights(d)
+    want = P.greedy_generate(c, W, [3, 1, 4, 1, 5], 6)
+    requests = [{"id": "r1", "tokens": [3, 1, 4, 1, 5], "max_new": 6, "temp": 0, "stop_ids": []},
+                {"id": "r2", "tokens": [3, 1, 4, 1, 5], "max_new": 6, "temp": 0, "stop_ids": [want[2]]},
+                {"id": "r3", "max_new": 2},
+                {"id": "bye", "shutdown": True},
+                {"id": "never", "tokens": [1]}]
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "llama_infer"), d, "--interactive", "--dtype",
+                        "float32", "--max-context", "64"], input="".join(json.dumps(q) + "\n" for q in requests),
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr
+    ev = [json.loads(l) for l in r.stdout.splitlines()]
+    by = lambda rid: [e for e in ev if e.get("id") == rid]
+    assert [e["type"] for e in by("r1")] == ["start"] + ["delta", "metrics"] * 6 + ["done"]
+    assert [e["tokens"][0] for e in by("r1") if e["type"] == "delta"] == want
+    assert [e["metrics"]["token_index"] for e in by("r1") if e["type"] == "metrics"] == [1, 2, 3, 4, 5, 6]
+    done = by("r1")[-1]
+    assert done["tokens"] == want and done["generated_tokens"] == 6 and done["elapsed_ms"] >= 0
+    assert by("r2")[-1]["tokens"] == want[:want.index(want[2])]          # the stop token is not part of the answer
+    assert [e["type"] for e in by("r3")] == ["error"] and "tokens" in by("r3")[0]["error"]
+    assert [e["type"] for e in by("bye")] == ["done"] and not by("never")
+
+
+def test_phase_timer_on_the_engine(dirs):
+    """Phases are timed for prefill and decode steps; switching the timer off brings the graphs back, and
+    the logits are the same with and without it."""
+    from cpi_b200.engine import Engine, StepEntry
+    e = Engine.from_model_dir(tiny.make_model_dir("C"), dtype="bfloat16", max_tokens=256)
+    t = tiny.random_tokens(30, 777, 5)
+
+    def run():
+        s = e.acquire_slot()
+        rows = [e.step([StepEntry(s, t[:20], [19])]).clone()]
+        for x in t[20:]:
+            rows.append(e.step([StepEntry(s, [x], [0])]).clone())
+        e.release_slot(s)
+        return torch.cat(rows)
+
+    plain_run = run()
+    assert e._graphs
+    timer = e.profile_phases(True)
+    timed = run()
+    ms = timer.collect()
+    e.profile_phases(False)
+    assert torch.equal(plain_run, timed)
+    assert set(ms) == {"prefill", "decode"}
+    for kind in ms:
+        assert {"embedding", "rmsnorm", "qkv", "kv_store", "attention", "wo", "mlp", "moe_router", "moe_expert",
+                "moe_merge", "lm_head"} == set(ms[kind]), ms[kind].keys()
+        assert all(v > 0 for v in ms[kind].values())
+    from cpi_b200 import phases
+    assert phases.active() is None
+    assert torch.equal(run(), plain_run)
+
+
 def test_trace_run_program(dirs, tmp_path):
     """bin/trace_run on a two-request trace, in float32, against the plain implementation."""
     import json
