@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the Llama4 Scout-sized model with random weights on one B200.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch 8] [--context 4096]
+    python bench.py --workload maverick4 | long131k      (two further workloads, a JSON line of their own)
 
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.  `value` is decoded tokens per
 second, timed on the device with CUDA events around exactly K engine steps (host token ids in, arg-max
@@ -8,6 +9,13 @@ on the device); `e2e` is the same through the Python entry point (`Model.generat
 step's token ids copied from pinned host memory and the sampled ids read back.  Between timed
 iterations nothing is flushed: one decode step reads tens of GB of weights, far more than the L2 holds.
 For N > 1 GPUs it prints one line that says the library is single-GPU and exits with 2.
+`phases` holds device milliseconds per phase of one prefill of 2,048 tokens and of one decode step, taken
+after everything else with the steps run eagerly on one stream (so their sum exceeds the step times above).
+
+`--workload maverick4`: 4 layers with Llama4 Maverick's sizes (dense and 128-expert layers alternate), 32
+prompts of 64 to 2,048 tokens, 128 new tokens each.  `--workload long131k`: 12 Scout layers, one prompt of
+131,072 tokens (prefilled in pieces), 256 new tokens.  Both run through `Model.generate` and are timed with
+its wall-clock phases, second of two runs.
 """
 from __future__ import annotations
 
@@ -234,6 +242,27 @@ def run(args) -> dict:
             m, _, _ = timed_decode(b, k, max(3, warm))
             points[f"decode_b{b}"] = round(b * k / (m / 1e3), 2)
 
+    # ---- where the time goes: phases of one prefill and of one decode step (eager, one stream) ---------
+    timer = eng.profile_phases(True)
+    for it in range(2):                                      # the first pass warms the eager paths up
+        timer.reset()
+        s = eng.acquire_slot()
+        eng.step([StepEntry(s, toks(pre_n), [pre_n - 1])])
+        eng.release_slot(s)
+    pre_ph = dict(timer.collect().get("prefill", {}))
+    slots = [eng.acquire_slot() for _ in range(B)]
+    eng.step([StepEntry(x, toks(ctx - 8), []) for x in slots])
+    eng.step([StepEntry(x, toks(1), [0]) for x in slots])
+    timer.reset()
+    for _ in range(4):
+        eng.step([StepEntry(x, toks(1), [0]) for x in slots])
+    for x in slots:
+        eng.release_slot(x)
+    ph = timer.collect()
+    eng.profile_phases(False)
+    phases = {"prefill_ms": {k: round(v, 3) for k, v in pre_ph.items()},
+              "decode_ms": {k: round(v / 4, 3) for k, v in ph.get("decode", {}).items()}}
+
     return {
         "metric": "decode tok/s @ batch 8 (Llama4 Scout layer sizes, bf16, random weights)",
         "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
@@ -256,9 +285,59 @@ def run(args) -> dict:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
         "points": points,
+        "phases": phases,
         "clocks": clock_rec,
         "build_s": round(build_s, 1),
     }
+
+
+def run_workload(args) -> dict:
+    """BASELINE's two further workloads through the Python entry point."""
+    import random
+
+    import torch
+    from cpi_b200.api import Model
+    cfg = dict(SCOUT)
+    if args.workload == "maverick4":
+        cfg.update(num_hidden_layers=4, interleave_moe_layer_step=2, num_local_experts=128)
+        cfg["rope_scaling"] = dict(cfg["rope_scaling"], factor=8.0)
+        rnd = random.Random(0)
+        lens, new = [rnd.randint(64, 2048) for _ in range(32)], 128
+    else:
+        cfg.update(num_hidden_layers=12)
+        lens, new = [131072], 256
+    model = Model.random(cfg, seed=0, dtype="bfloat16", max_batch=len(lens), max_context=max(lens) + new + 64,
+                         device="cuda:0")
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    clocks = ClockSampler()
+    for it in range(2):
+        if it == 1:
+            clocks.start()
+        torch.cuda.synchronize()
+        t0 = time.time()
+        res = model.generate(prompts, max_new=new, temperature=0.0, stop_ids=[])
+        torch.cuda.synchronize()
+        total = time.time() - t0
+    clock_rec = clocks.stop()
+    model.engine.check_device_errors()
+    st = model.stats()
+    n_new = sum(len(r.tokens) for r in res)
+    return {"metric": f"tokens/s through Model.generate, workload {args.workload} (bf16, random weights)",
+            "value": round((n_new - len(lens)) / (st.decode_ms / 1e3), 1), "unit": "decoded tok/s", "n_gpus": 1,
+            "higher_is_better": True, "dtype": "bf16", "impl": "cpi_b200",
+            "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)",
+            "config": {"model": args.workload, "layers": cfg["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                       "experts": cfg["num_local_experts"], "moe_layer_step": cfg["interleave_moe_layer_step"],
+                       "dense_inter": cfg["intermediate_size_mlp"], "expert_inter": cfg["intermediate_size"],
+                       "vocab": cfg["vocab_size"], "prompts": len(lens), "prompt_tokens": sum(lens),
+                       "longest_prompt": max(lens), "new_tokens_each": new, "parallelism": "single-gpu"},
+            "prefill": {"value": round(sum(lens) / (st.prefill_ms / 1e3), 1), "tokens": sum(lens),
+                        "ms": round(st.prefill_ms, 2)},
+            "decode": {"steps": st.decode_steps, "ms": round(st.decode_ms, 2),
+                       "ms_per_step": round(st.decode_ms / max(st.decode_steps, 1), 3)},
+            "total_s": round(total, 3), "device_memory_gb": round(torch.cuda.max_memory_allocated() / 1e9, 1),
+            "clocks": clock_rec}
 
 
 def main() -> int:
@@ -271,6 +350,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k"], default="scout24")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -281,7 +361,7 @@ def main() -> int:
         print(json.dumps({"error": "cpi_b200 is a single-GPU library: run with --gpus 1", "n_gpus": args.gpus}))
         return 2
     args.warmup = max(args.warmup, 3)
-    print(json.dumps(run(args)))
+    print(json.dumps(run(args) if args.workload == "scout24" else run_workload(args)))
     return 0
 
 
