@@ -7,9 +7,11 @@
 // 30 us (SwiGLU into rows 16 KB apart) against 2 us for reading tensor memory.  So the tile is turned
 // in shared memory instead: each thread drops its feature's values at stage[token][feature] (a warp
 // writes 32 neighbouring words: no bank conflicts), and after a barrier each warp copies whole token
-// rows of 128 features with 16-byte (float32) or 8-byte (bfloat16) accesses per lane; the
-// read-modify-write of the ADD epilogue keeps four rows in flight.  Arithmetic and its order are those
-// of the direct epilogue: out = old + acc * scale, or silu(g * scale) * (u * scale).
+// rows of 128 features with 16-byte (float32) or 8-byte (bfloat16) accesses per lane.  ADD of whole
+// rows hands each turned row to the copy engine, which adds it into the output in the L2
+// (cp.reduce.async.bulk, 512 bytes a row); a tile at the edge of N reads, adds and writes with several
+// rows in flight.  Arithmetic and its order are those of the direct epilogue: out = old + acc * scale, or
+// silu(g * scale) * (u * scale).
 #pragma once
 #include "common.cuh"
 
@@ -42,6 +44,16 @@ __device__ __forceinline__ bool staged_ok(const void* out, long ldo, int n_valid
   return n_valid_t >= 32 && (ldo % (16 / (int)sizeof(TO))) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
 }
 
+// ADD of whole float32 rows: the copy engine adds a turned row (128 features, 512 bytes of shared memory)
+// into the output row in the L2, so no thread waits for the old values.  One writer per element and launch:
+// the sum is old + acc as before.
+__device__ __forceinline__ void bulk_add_f32(float* dst, const float* src_smem, uint32_t bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+               ::"l"(dst), "r"(static_cast<uint32_t>(__cvta_generic_to_shared(src_smem))), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+
 // Barriers of the turning: all threads of the CTA, or a named barrier over the calling threads only
 // (a kernel whose other warps are busy with the next tile).
 struct CtaSync { __device__ __forceinline__ void operator()() const { __syncthreads(); } };
@@ -69,10 +81,16 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
   constexpr int R = MODE == kAdd ? 16 : 8;              // rows in flight per warp (the read-modify-write waits on its loads)
   const int n = n0 + PER * lane;
   const bool whole = n + PER <= N;
+  // all 128 features of the tile exist: rows leave through the copy engine's add (see bulk_add_f32)
+  const bool bulk = MODE == kAdd && sizeof(TO) == 4 && n0 + 128 <= N &&
+                    (reinterpret_cast<uintptr_t>(stage_mem) & 15) == 0;
 #pragma unroll 1
   for (int p0 = 0; p0 < n_cols; p0 += STAGE_COLS) {      // one pass per STAGE_COLS columns
   const int p1 = min(p0 + STAGE_COLS, n_cols), v1 = min(p0 + STAGE_COLS, n_valid_t);
-  if (p0 > 0) sync();                                    // the previous pass has been copied out
+  if (p0 > 0) {
+    if (bulk) bulk_wait_read();                          // the copy engine has read this thread's rows of the pass before
+    sync();                                              // the previous pass has been copied out
+  }
 #pragma unroll 1
   for (int c = p0; c < p1; c += 16) {
     float v[16], u[16];
@@ -87,6 +105,17 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
     }
 #pragma unroll
     for (int j = 0; j < 16; ++j) stage[(c - p0 + j) * 128 + row] = Stage<TO>::put(v[j]);
+  }
+  if (bulk) {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the stage is read through the async proxy
+    sync();
+    for (int col = p0 + row; col < v1; col += 128) {
+      const int lr = t0 + col;
+      bulk_add_f32(reinterpret_cast<float*>(out) + (size_t)(out_rows ? out_rows[lr] : lr) * ldo + n0,
+                   reinterpret_cast<const float*>(stage) + (size_t)(col - p0) * 128, 512);
+    }
+    bulk_commit();
+    continue;
   }
   sync();
   // Phase B.  A warp copies rows warp, warp + 4, ...; R rows per round, all their global loads first.
@@ -141,6 +170,7 @@ __device__ __forceinline__ void staged(void* stage_mem, Ld ld16, LdU ld16u, int 
     }
   }
   }
+  if (bulk) bulk_wait_read();                            // the stage may be written again; the sums land before the grid ends
 }
 
 }  // namespace epi

@@ -659,7 +659,10 @@ extern "C" int cpi_gemm_tc_pair(const void* x, long ldx, const void* w, void* ou
   dim3 grid(N / tc2::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), 1);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc_pair: too many token tiles (%u)", grid.y);
   const int cap = bn <= 128 ? 128 : 256;
-  const bool persistent = g_persistent == 2 || (g_persistent == 1 && (mode == tc2::kSwiglu || (mode == tc2::kAdd && T >= 4096)));
+  // (ADD: the persistent kernel wins where the mainloop is short against the epilogue; measured at 8,192 tokens
+  // with the copy engine's add: K = 5120 314 against 321 us, K = 8192 513 against 495 us)
+  const bool persistent = g_persistent == 2 || (g_persistent == 1 && (mode == tc2::kSwiglu ||
+                                                (mode == tc2::kAdd && T >= 4096 && K <= 6144)));
   const int n_slots = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
   const bool persistent_groups = (g_persistent == 2 || (g_persistent == 1 && mode == tc2::kSwiglu)) && n_groups > 0 &&
                                  n_slots <= tc2::kMaxSlots;      // (measured: 2 % faster for SwiGLU, slower for STORE)
