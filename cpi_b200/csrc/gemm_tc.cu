@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   pdl_wait();                                    // before any global read or write of this thread
   bool ok = mbar_wait(&accum_bar, 0, abort_flag);
   fence_after_sync();
-  ok = __syncthreads_and(ok && !abort_s) != 0;            // one verdict for the CTA
+  ok = __syncthreads_and(ok && !abort_s) != 0;            // one decision for the CTA
 
   const int row = warp * 32 + lane;                       // accumulator lane = output feature n0 + row
   const int n = n0 + row;
@@ -560,8 +560,8 @@ struct Variant {
   static constexpr int ACC = MODE == kSwiglu ? 2 : 1;
   static constexpr int STAGE = ACC * BM * BK * 2 + BN * BK * 2;
   // two CTAs per SM where the stages stay deep enough: one's epilogue then runs under the other's loads
-  static constexpr int BUDGET = (BN <= 32 || (BN == 64 && ACC == 1)) ? 108 * 1024 : 196 * 1024;
-  static constexpr int S0 = BUDGET / STAGE;
+  static constexpr int SMEM_LIMIT = (BN <= 32 || (BN == 64 && ACC == 1)) ? 108 * 1024 : 196 * 1024;
+  static constexpr int S0 = SMEM_LIMIT / STAGE;
   static constexpr int STAGES = S0 > 8 ? 8 : (S0 < 2 ? 2 : S0);
   static constexpr int SMEM = STAGES * STAGE + 1024;
   using Kernel = void (*)(const CUtensorMap, const CUtensorMap, Params);

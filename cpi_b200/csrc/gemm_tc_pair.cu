@@ -261,7 +261,7 @@ __global__ void __launch_bounds__(128) gemm_tc_pair_kernel(const __grid_constant
   pdl_wait();
   bool ok = mbar_wait(&accum_bar, 0, abort_flag);
   fence_after_sync();
-  ok = __syncthreads_and(ok && !abort_s) != 0;                   // one verdict for the CTA
+  ok = __syncthreads_and(ok && !abort_s) != 0;                   // one decision for the CTA
   const int row = warp * 32 + lane;
   const int n = n0 + row;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_persistent_kernel(const __gr
       const int n_cols = min(BN, (n_valid_t + 15) & ~15);
       const int b = j % NB;
       mbar_wait(&acc_full[b], (j / NB) & 1, abort_flag);
-      // one verdict for the four warps (a named barrier has no time limit: nobody may leave alone); it also
+      // one decision for the four warps (a named barrier has no time limit: nobody may leave alone); it also
       // keeps the turning buffer of the tile before from being overwritten while a warp still copies it out
       asm volatile("bar.sync 1, 128;" ::: "memory");
       if (abort_s) break;
@@ -571,8 +571,8 @@ static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p,
   // One accumulator: half the shared memory per pair, so that two pairs share an SM pair and the epilogue
   // of one runs under the matrix product of the other (measured 1.4x).  Two accumulators fill the tensor
   // memory: one pair per SM pair, with all the stages.
-  constexpr int BUDGET = ACC == 1 ? 108 * 1024 : 196 * 1024;
-  constexpr int S0 = BUDGET / STAGE;
+  constexpr int SMEM_LIMIT = ACC == 1 ? 108 * 1024 : 196 * 1024;
+  constexpr int S0 = SMEM_LIMIT / STAGE;
   constexpr int STAGES = S0 > 8 ? 8 : S0;
   constexpr int SMEM = STAGES * STAGE + 1024;
   auto kern = gemm_tc_pair_kernel<BN, MODE, TO, STAGES>;
