@@ -6,8 +6,10 @@ on the tiny configuration "R" (tests/tiny.py), for comparison with tests/plain_l
 It compiles src/engine/llama4_cpu_engine.cpp, src/model/safetensors_loader.cpp and
 src/platform/mmap_file.cpp of the reference with ref_harness.cpp (g++, CUDA headers only, no CUDA
 library), writes the tiny model to a temporary folder, runs the harness token by token and stores the
-tokens, the logits at every position and a digest of the weights.  The test skips, rather than fails,
-when the weights drawn here no longer have that digest (another torch version's generator).
+tokens, the logits at every position and a digest of the weights.  The random weights come from the
+library's counter-based generator (integer mixing and a table look-up), so they do not depend on torch's
+own generators; should the digest differ all the same (the table's last bits, from another erfinv), the test
+skips rather than fails: run this script again.
 """
 import hashlib
 import os

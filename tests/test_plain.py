@@ -18,7 +18,8 @@ def test_plain_matches_reference_cpu_engine():
     d = tiny.make_model_dir("R")
     with open(os.path.join(d, "model.safetensors"), "rb") as f:
         if hashlib.sha256(f.read()).hexdigest() != str(g["digest"]):
-            pytest.skip("this torch draws other random weights than the golden file was made with")
+            pytest.skip("the random weights drawn here differ from those the golden file was made with: "
+                        "run tests/golden/make_golden.py again")
     c, W = P.read_config(d), P.read_weights(d)
     logits = P.forward(c, W, g["tokens"].tolist()).numpy()
     err = np.abs(logits - g["logits"]).max()
