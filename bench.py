@@ -238,8 +238,8 @@ def run(args) -> dict:
     points = {}
     if not args.skip_points:
         for b in (1, 64):
-            k = max(4, steps // 2)
-            m, _, _ = timed_decode(b, k, max(3, warm))
+            k = max(4, steps if b == 1 else steps // 2)          # batch-1 steps are short: time more of them
+            m, _, _ = timed_decode(b, k, max(3, warm) + (4 if b == 1 else 0))
             points[f"decode_b{b}"] = round(b * k / (m / 1e3), 2)
 
     # ---- where the time goes: phases of one prefill and of one decode step (eager, one stream) ---------
