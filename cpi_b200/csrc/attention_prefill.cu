@@ -393,22 +393,22 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       auto pass = [&](const float ref) {
         const float nref = -ref;
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, ls4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t raw[2][32];
+        uint32_t raw[BKV / 32][32];
         // The whole row is read for its maximum (so that the two halves of a row decide alike without
         // talking to each other: no barrier per tile, and the halves drift apart, one's exponentials
         // under the other's waits), the exponentials are taken of this thread's half only.  Chunk order:
         // the other half's two chunks first, then this half's.
         const int first = (half ^ 1) * HC;
-        tmem_ld32_issue(s_row + first, raw[0]);
+        // all four loads go out together: their latencies overlap, and one wait covers them
+#pragma unroll
+        for (int cc = 0; cc < BKV / 32; ++cc) tmem_ld32_issue(s_row + (cc < 2 ? first : c0) + (cc & 1) * 32, raw[cc]);
+        tmem_wait_ld();
 #pragma unroll
         for (int cc = 0; cc < BKV / 32; ++cc) {
           const int c = ((cc < 2 ? first : c0) + (cc & 1) * 32);     // column of this chunk within the tile
-          tmem_wait_ld();                                  // chunk cc has arrived
-          if (cc + 1 < BKV / 32)
-            tmem_ld32_issue(s_row + (cc + 1 < 2 ? first : c0) + ((cc + 1) & 1) * 32, raw[(cc + 1) & 1]);
           float v[32];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[cc & 1][e]);
+          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[cc][e]);
           if (no_mask) {
 #pragma unroll
             for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
