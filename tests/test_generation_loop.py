@@ -286,3 +286,23 @@ def test_command_line_argument_errors_and_interactive_protocol(capsys):
     assert ev[5]["tokens"] == [10, 11] and ev[5]["id"] == "a"       # the default stop id 12 ended it
     assert ev[10]["tokens"] == [10] and "id" not in ev[11]
     assert m.kw["temperature"] == 0.8 and m.kw["max_new"] == 4      # the second request ran on the defaults
+
+
+def test_bench_refuses_more_than_one_gpu_and_names_the_reference_arm():
+    """What bench.py answers without touching a GPU: one line and exit code 2 for N > 1, and the reference
+    arm's `unavailable` line with exit code 0."""
+    import json
+    import os
+    import subprocess
+    import sys
+    bench = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py")
+    many = subprocess.run([sys.executable, bench, "--gpus", "4", "--steps", "2", "--warmup", "1"],
+                          capture_output=True, text=True, timeout=120)
+    assert many.returncode == 2
+    lines = [l for l in many.stdout.splitlines() if l.strip()]
+    assert len(lines) == 1 and json.loads(lines[0])["n_gpus"] == 4 and "single-GPU" in lines[0]
+    ref = subprocess.run([sys.executable, bench, "--impl", "reference", "--gpus", "1"], capture_output=True, text=True,
+                         timeout=120)
+    assert ref.returncode == 0
+    rec = json.loads(ref.stdout.strip())
+    assert rec["impl"] == "reference" and rec["unavailable"]
