@@ -21,7 +21,7 @@ All bookkeeping is on the host; tables are mirrored to the device before a step.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Optional
 
 import torch

@@ -11,7 +11,6 @@ launches with CUDA events and prints the median with the bytes or flops the laun
 from __future__ import annotations
 
 import argparse
-import math
 import sys
 
 import torch

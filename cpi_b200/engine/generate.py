@@ -13,7 +13,7 @@ sampler through one, so its decisions can be tested without a device.
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, Optional, Sequence
 
 from ..sampling.params import SamplingParams, GREEDY

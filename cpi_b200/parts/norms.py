@@ -1,8 +1,6 @@
 """RMS norm: y = x * rsqrt(mean(x^2) + eps) * w  (src/engine/llama4_cpu_engine.cpp:47-62)."""
 from __future__ import annotations
 
-import torch
-
 from ..csrc import lib as K
 from ..weights.store import TensorReq
 from .base import Norm, register_norm

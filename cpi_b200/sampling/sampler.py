@@ -11,7 +11,6 @@ from __future__ import annotations
 import torch
 
 from ..csrc import lib as K
-from .params import SamplingParams
 
 
 def banned_by_ngram(history: list, n: int) -> list:

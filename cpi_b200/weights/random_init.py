@@ -18,7 +18,7 @@ import os
 import torch
 
 from .safetensors_io import write_safetensors
-from .store import TensorReq, WeightSource
+from .store import WeightSource
 
 
 def _tensor_seed(seed: int, name: str) -> int:

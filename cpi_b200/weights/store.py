@@ -13,7 +13,7 @@ Storage dtypes: BF16 stays bfloat16; F32 stays float32; F16 is widened to float3
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Iterable, Optional
+from typing import Iterable
 
 import torch
 

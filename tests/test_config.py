@@ -1,5 +1,4 @@
 """Typed configuration, registry and spec."""
-import copy
 import json
 import os
 import tempfile

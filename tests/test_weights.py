@@ -1,6 +1,5 @@
 """safetensors reading and writing, the model's tensor list, and the one error for every mismatch."""
 import json
-import os
 import struct
 
 import pytest

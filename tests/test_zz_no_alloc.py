@@ -9,7 +9,6 @@ entry point, which takes its scratch from the caller.  It also checks that a req
 built-in array is refused.  The file name sorts last on purpose: a run that stops at the first failure
 has then already run every other test.
 """
-import ctypes
 from ctypes import c_float, c_int, c_long, c_void_p
 
 import pytest

@@ -3,7 +3,6 @@ stays inside what the reference's own engine computes, and helpers that write mo
 from __future__ import annotations
 
 import copy
-import os
 import tempfile
 
 import torch
