@@ -306,3 +306,23 @@ def test_bench_refuses_more_than_one_gpu_and_names_the_reference_arm():
     assert ref.returncode == 0
     rec = json.loads(ref.stdout.strip())
     assert rec["impl"] == "reference" and rec["unavailable"]
+
+
+def test_compare_logits_measures():
+    import torch
+    from cpi_b200.engine.drift import compare_logits
+    ref = torch.tensor([[0.0, 5.0, 4.0, 3.0, -1.0, 2.0], [9.0, 1.0, 2.0, 3.0, 4.0, 5.0]])
+    same = compare_logits(ref, ref, 3)
+    assert same["top1_match"] == 1.0 and same["overlap_at_k"] == 1.0 and same["mean_abs"] == 0.0 and same["max_abs"] == 0.0
+    other = ref.clone()
+    other[0, 1], other[0, 2] = 4.0, 5.5            # row 0: another best token, the same three best
+    other[1, 5], other[1, 1] = 0.0, 8.0            # row 1: the same best token, one of its three best replaced
+    m = compare_logits(ref, other, 3)
+    assert m["top1_match"] == 0.5 and abs(m["overlap_at_k"] - (1.0 + 2.0 / 3.0) / 2) < 1e-6
+    assert abs(m["max_abs"] - 7.0) < 1e-6 and abs(m["mean_abs"] - (1.0 + 1.5 + 5.0 + 7.0) / 12) < 1e-6
+    assert compare_logits(ref[0], ref[0], 100)["overlap_at_k"] == 1.0       # one row, k larger than the vocabulary
+    bad = ref.clone()
+    bad[0, 0] = float("nan")
+    assert compare_logits(ref, bad, 3)["max_abs"] == float("inf")
+    with pytest.raises(ValueError):
+        compare_logits(ref, ref[:, :4])

@@ -3,7 +3,7 @@ import pytest
 import torch
 
 import tiny
-from helpers import Replay, compare_with_plain
+from helpers import Replay, compare_with_plain, tolerances
 
 pytestmark = pytest.mark.gpu
 
@@ -278,23 +278,26 @@ def test_long_context_across_the_chunk_boundary_both_kernel_families_agree():
     assert float((a.argmax(-1) == b.argmax(-1)).float().mean()) > 0.9
 
 
+SCOUT_TWO_LAYERS = {
+    "architectures": ["Llama4ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 5120,
+    "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192,
+    "intermediate_size_mlp": 16384, "num_local_experts": 3, "num_experts_per_tok": 1,
+    "interleave_moe_layer_step": 1, "vocab_size": 20011, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+                     "original_max_position_embeddings": 8192},
+    "nope_layer_interval": 2, "attention_chunk_size": 8192, "use_qk_norm": True,
+    "attn_temperature_tuning": True, "floor_scale": 8192, "attn_scale": 0.1,
+    "tie_word_embeddings": False, "initializer_range": 0.02,
+}
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_scout_layer_sizes_against_plain(dtype):
     """The layer sizes that the benchmark runs (width 5120, 40 / 8 heads of 128, experts of 8192, llama3
     scaling, chunk and temperature floor 8192) in two layers (one with rotation, one without), with three
     experts and a vocabulary that is no multiple of anything: an unequal batch, then decoding."""
     import shutil
-    cfg = {
-        "architectures": ["Llama4ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 5120,
-        "num_attention_heads": 40, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192,
-        "intermediate_size_mlp": 16384, "num_local_experts": 3, "num_experts_per_tok": 1,
-        "interleave_moe_layer_step": 1, "vocab_size": 20011, "rms_norm_eps": 1e-5, "rope_theta": 500000.0,
-        "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
-                         "original_max_position_embeddings": 8192},
-        "nope_layer_interval": 2, "attention_chunk_size": 8192, "use_qk_norm": True,
-        "attn_temperature_tuning": True, "floor_scale": 8192, "attn_scale": 0.1,
-        "tie_word_embeddings": False, "initializer_range": 0.02,
-    }
+    cfg = SCOUT_TWO_LAYERS
     from cpi_b200.engine import Engine
     if "scout" not in _dirs:
         _dirs["scout"] = tiny.make_model_dir(cfg, seed=11)
@@ -314,3 +317,53 @@ def test_scout_layer_sizes_against_plain(dtype):
     finally:
         if dtype == "bfloat16":
             shutil.rmtree(_dirs.pop("scout"), ignore_errors=True)
+
+
+@pytest.mark.parametrize("which", ["C", "scout"])
+def test_bfloat16_drift_against_float32(which):
+    """The reference's measure of a reduced-precision path (tools/moe_cuda_bench.py:177-212): is the best token
+    the same, how many of the five best tokens are shared, mean and largest absolute difference -- of the
+    bfloat16 path against the float32 path on the same weights, prompt rows and decoded rows.  Rows where the
+    two precisions chose other experts (near-ties of the router, checked against the plain router elsewhere)
+    are counted and set aside."""
+    from cpi_b200.engine import Engine, StepEntry
+    from cpi_b200.engine.drift import compare_logits
+    if which == "scout":
+        if "scout" not in _dirs:
+            _dirs["scout"] = tiny.make_model_dir(SCOUT_TWO_LAYERS, seed=11)
+        d, vocab = _dirs["scout"], SCOUT_TWO_LAYERS["vocab_size"]
+    else:
+        d, vocab = model_dir("C"), 777
+    prompt, more = tiny.random_tokens(150, vocab, 21), tiny.random_tokens(24, vocab, 22)
+    rows, experts = {}, {}
+    for dtype in ("float32", "bfloat16"):
+        e = Engine.from_model_dir(d, dtype=dtype, max_tokens=256)
+        cap = e.capture_routing(True)
+        chosen = lambda: torch.cat([torch.cat([x.cpu() for x in cap[l]]) for l in sorted(cap)], 1)
+        s = e.acquire_slot()
+        out = [e.step([StepEntry(s, prompt, list(range(len(prompt))))]).float().cpu()]
+        ex = [chosen()]
+        for t in more:
+            for lst in cap.values():
+                lst.clear()
+            out.append(e.step([StepEntry(s, [t], [0])]).float().cpu())
+            ex.append(chosen())
+        e.release_slot(s)
+        e.check_device_errors()
+        rows[dtype], experts[dtype] = torch.cat(out), torch.cat(ex)
+        del e
+    same = (experts["float32"] == experts["bfloat16"]).all(-1)
+    flipped = (~same).nonzero().flatten().tolist()
+    # a position whose expert differs has other keys and values in the layers above, so the rows after it in the
+    # sequence differ by more than rounding too (measured: twice the typical row): the figures are taken of the
+    # rows before the first such position
+    clean = flipped[0] if flipped else len(same)
+    assert clean >= 40 and len(flipped) <= 0.1 * len(same), flipped
+    m = compare_logits(rows["float32"][:clean], rows["bfloat16"][:clean], 5)
+    print(f"bfloat16 against float32 ({which}): rows {flipped} of {len(same)} chose other experts; of the {clean} rows "
+          f"before them: best token the same in {m['top1_match']:.3f}, five best shared {m['overlap_at_k']:.3f}, "
+          f"mean |d| {m['mean_abs']:.3e}, max |d| {m['max_abs']:.3e}; logits: spread {m['ref_std']:.3e}, "
+          f"largest {m['ref_max_abs']:.3e}")
+    assert m["max_abs"] <= tolerances("bfloat16")[0] * m["ref_max_abs"]       # the suite's bound for a bfloat16 row
+    assert m["mean_abs"] <= 0.02 * m["ref_std"]
+    assert m["top1_match"] >= 0.9 and m["overlap_at_k"] >= 0.9
