@@ -326,3 +326,33 @@ def test_compare_logits_measures():
     assert compare_logits(ref, bad, 3)["max_abs"] == float("inf")
     with pytest.raises(ValueError):
         compare_logits(ref, ref[:, :4])
+
+
+def test_step_batch_layout_on_the_host():
+    """What a step's index arrays hold for an unequal batch: packed tokens, each token's sequence and
+    position, wanted rows as packed indices, and the query tiles of a prefill (128 tokens of one sequence
+    at most, the tile with the most keys first)."""
+    import torch
+    from cpi_b200.engine.batch import BatchStager
+    st = BatchStager("cpu")
+    toks = [list(range(100, 400)), [7, 8, 9], list(range(1000, 1130))]            # 300, 3 and 130 new tokens
+    starts, slots = [0, 50, 200], [4, 0, 9]
+    wants = [[0, 299], [], [129]]
+    b = st.stage(slots, starts, toks, wants, torch.float32)
+    assert (b.n_tokens, b.n_seqs, b.n_want, b.max_new, b.is_decode) == (433, 3, 3, 300, False)
+    assert b.tokens.tolist() == toks[0] + toks[1] + toks[2]
+    assert b.token_seq.tolist() == [0] * 300 + [1] * 3 + [2] * 130
+    assert b.token_pos.tolist() == list(range(300)) + [50, 51, 52] + list(range(200, 330))
+    assert b.seq_slot.tolist() == slots and b.seq_start.tolist() == starts and b.seq_new.tolist() == [300, 3, 130]
+    assert b.want_rows.tolist() == [0, 299, 303 + 129]
+    tiles = list(zip(b.tile_tok0.tolist(), b.tile_rows.tolist()))
+    assert sorted(tiles) == [(0, 128), (128, 128), (256, 44), (300, 3), (303, 128), (431, 2)]
+    ends = [b.token_pos[t0 + r - 1].item() + 1 for t0, r in tiles]                   # keys each tile may see
+    assert ends == sorted(ends, reverse=True) and b.n_q_tiles == 6
+    assert b.ctx_bucket == 512 and st.bytes_staged == 4 * (3 * 433 + 3 * 3 + 3 + 2 * 6)
+    d = st.stage([4, 9], [300, 330], [[5], [6]], [[0], [0]], torch.float32)
+    assert d.is_decode and d.n_q_tiles == 0 and d.token_pos.tolist() == [300, 330] and d.want_rows.tolist() == [0, 1]
+    assert b.tokens.tolist() == toks[0] + toks[1] + toks[2]                         # the ring: the step before is intact
+    big = st.stage([1], [0], [list(range(5000))], [[4999]], torch.float32)          # the buffers grow
+    assert big.n_tokens == 5000 and big.tokens[-1].item() == 4999 and big.ctx_bucket == 8192
+    assert BatchStager.words_needed(8, 8, 8) == 56
