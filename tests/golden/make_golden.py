@@ -1,5 +1,6 @@
-"""Makes tests/golden/tiny_r_reference.npz: logits of kurulav1/cpi's own, unmodified Llama4 CPU engine
-on the tiny configuration "R" (tests/tiny.py), for comparison with tests/plain_llama4.py.
+"""Makes tests/golden/tiny_r_reference.npz and tiny_r2_reference.npz: logits of kurulav1/cpi's own, unmodified
+Llama4 CPU engine on the tiny configurations "R" and "R2" (tests/tiny.py), for comparison with
+tests/plain_llama4.py.
 
     python tests/golden/make_golden.py REFERENCE_ROOT        (a checkout of kurulav1/cpi)
 
@@ -42,21 +43,21 @@ def main():
     cmd = ["g++", "-std=c++20", "-O2", "-mavx2", "-mfma", "-fopenmp", f"-I{ref}/include",
            "-I/usr/local/cuda/include", os.path.join(HERE, "ref_harness.cpp"), *srcs, "-o", exe]
     subprocess.run(cmd, check=True)
-    d = tiny.make_model_dir("R")
-    c = tiny.config("R")["text_config"]
-    rs = c["rope_scaling"]
-    tokens = tiny.random_tokens(48, c["vocab_size"], 77)
-    out = os.path.join(work, "logits.f32")
-    args = [exe, d, out, c["vocab_size"], c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"],
-            c["head_dim"], c["num_hidden_layers"], c["num_local_experts"], c["intermediate_size"],
-            c["intermediate_size"], rs["original_max_position_embeddings"], c["rope_theta"], rs["factor"],
-            rs["low_freq_factor"], rs["high_freq_factor"], *tokens]
-    subprocess.run([str(a) for a in args], check=True)
-    logits = np.fromfile(out, dtype="<f4").reshape(len(tokens), c["vocab_size"])
-    np.savez_compressed(os.path.join(HERE, "tiny_r_reference.npz"), tokens=np.array(tokens, dtype=np.int32),
-                        logits=logits.astype(np.float16 if False else np.float32),
-                        digest=np.array(weights_digest(d)))
-    print("wrote tiny_r_reference.npz", logits.shape, "max |logit|", float(np.abs(logits).max()))
+    for name, n_tokens, file in (("R", 48, "tiny_r_reference.npz"), ("R2", 70, "tiny_r2_reference.npz")):
+        d = tiny.make_model_dir(name)
+        c = tiny.config(name)["text_config"]
+        rs = c["rope_scaling"]
+        tokens = tiny.random_tokens(n_tokens, c["vocab_size"], 77)
+        out = os.path.join(work, f"logits_{name}.f32")
+        args = [exe, d, out, c["vocab_size"], c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"],
+                c["head_dim"], c["num_hidden_layers"], c["num_local_experts"], c["intermediate_size"],
+                c["intermediate_size"], rs["original_max_position_embeddings"], c["rope_theta"], rs["factor"],
+                rs["low_freq_factor"], rs["high_freq_factor"], *tokens]
+        subprocess.run([str(a) for a in args], check=True)
+        logits = np.fromfile(out, dtype="<f4").reshape(len(tokens), c["vocab_size"])
+        np.savez_compressed(os.path.join(HERE, file), tokens=np.array(tokens, dtype=np.int32),
+                            logits=logits.astype(np.float32), digest=np.array(weights_digest(d)))
+        print("wrote", file, logits.shape, "max |logit|", float(np.abs(logits).max()))
 
 
 if __name__ == "__main__":

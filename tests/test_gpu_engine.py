@@ -32,7 +32,9 @@ def vocab(name):
     return c.get("text_config", c)["vocab_size"]
 
 
-CASES = [(n, d) for n in ("A", "B") for d in ("float32", "bfloat16")] + [("C", "bfloat16")]
+# R2 lies inside what the reference's own engine computes: the plain implementation is checked against that engine at
+# this point (tests/test_plain.py), so these cases tie the kernels to the reference's code and not only to its formulas
+CASES = [(n, d) for n in ("A", "B", "R2") for d in ("float32", "bfloat16")] + [("C", "bfloat16")]
 
 
 @pytest.mark.parametrize("name,dtype", CASES)
@@ -71,7 +73,7 @@ def test_unequal_batches_one_after_another(name, dtype):
     """Batches of unequal prompts whose shorter requests end earlier; the cache is sized for one batch,
     so the second and third batch run in slots and pages that the first one gave back."""
     shapes = {"A": [(5, 24), (17, 9), (40, 24)], "B": [(1, 16), (9, 3), (33, 16), (70, 7)],
-              "C": [(150, 20), (3, 8), (260, 20), (64, 1)]}[name]
+              "C": [(150, 20), (3, 8), (260, 20), (64, 1)], "R2": [(7, 12), (29, 5), (50, 18)]}[name]
     need = sum(-(-(p + d) // 64) * 64 for p, d in shapes)
     e = engine(name, dtype, max_tokens=need)
     all_reqs = {}

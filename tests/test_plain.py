@@ -9,13 +9,15 @@ import torch
 import plain_llama4 as P
 import tiny
 
-GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "tiny_r_reference.npz")
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
 
-def test_plain_matches_reference_cpu_engine():
-    """Logits of kurulav1/cpi's unmodified llama4_cpu_engine.cpp (made by tests/golden/make_golden.py)."""
-    g = np.load(GOLDEN)
-    d = tiny.make_model_dir("R")
+@pytest.mark.parametrize("name,file", [("R", "tiny_r_reference.npz"), ("R2", "tiny_r2_reference.npz")])
+def test_plain_matches_reference_cpu_engine(name, file):
+    """Logits of kurulav1/cpi's unmodified llama4_cpu_engine.cpp (made by tests/golden/make_golden.py) at two
+    points that differ in every size the reference's engine lets one choose."""
+    g = np.load(os.path.join(GOLDEN, file))
+    d = tiny.make_model_dir(name)
     with open(os.path.join(d, "model.safetensors"), "rb") as f:
         if hashlib.sha256(f.read()).hexdigest() != str(g["digest"]):
             pytest.skip("the random weights drawn here differ from those the golden file was made with: "

@@ -72,7 +72,26 @@ TINY_C = {
     "tie_word_embeddings": False, "max_position_embeddings": 4096, "initializer_range": 0.03,
 }
 
-CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "R": (TINY_R, 2), "C": (TINY_C, 3)}
+# R2: a second point inside what the reference's engine computes, other in every size it lets one choose:
+# flat config, wider, more heads in groups of two, fewer layers, three experts of a width that is no power of
+# two, another vocabulary, another RoPE base, factor and band edges, a short original context.
+TINY_R2 = {
+    "architectures": ["Llama4ForConditionalGeneration"],
+    "text_config": {
+        "num_hidden_layers": 2, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 3,
+        "head_dim": 16, "intermediate_size": 80, "intermediate_size_mlp": 80,
+        "num_local_experts": 3, "num_experts_per_tok": 1, "interleave_moe_layer_step": 1,
+        "vocab_size": 300, "rms_norm_eps": 1e-5, "rope_theta": 10000.0,
+        "rope_scaling": {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 2.0,
+                         "high_freq_factor": 6.0, "original_max_position_embeddings": 32},
+        "nope_layer_interval": 0, "attention_chunk_size": 0, "use_qk_norm": True,
+        "attn_temperature_tuning": False, "max_position_embeddings": 1024, "initializer_range": 0.05,
+        "qk_norm_order": "before_rope", "qk_norm_scope": "all_layers", "router_gate": "none",
+    },
+    "tie_word_embeddings": False,
+}
+
+CONFIGS = {"A": (TINY_A, 0), "B": (TINY_B, 1), "R": (TINY_R, 2), "C": (TINY_C, 3), "R2": (TINY_R2, 4)}
 
 
 def config(name: str) -> dict:
