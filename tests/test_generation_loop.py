@@ -356,3 +356,13 @@ def test_step_batch_layout_on_the_host():
     big = st.stage([1], [0], [list(range(5000))], [[4999]], torch.float32)          # the buffers grow
     assert big.n_tokens == 5000 and big.tokens[-1].item() == 4999 and big.ctx_bucket == 8192
     assert BatchStager.words_needed(8, 8, 8) == 56
+
+
+def test_run_llama4_prompt_helpers():
+    """The chat frame is the reference script's (tools/run_llama4_prompt.py:13-23): system and user turns closed
+    by <|eot|>, the assistant's header left open; the answer is cut at the first stop id."""
+    from cpi_b200.cli.run_llama4_prompt import chat_frame, cut_at_stop
+    text = chat_frame("Be brief.", "Hi")
+    assert text == ("<|begin_of_text|><|header_start|>system<|header_end|>\n\nBe brief.<|eot|>"
+                    "<|header_start|>user<|header_end|>\n\nHi<|eot|><|header_start|>assistant<|header_end|>\n\n")
+    assert cut_at_stop([4, 5, 9, 6, 9], {9}) == [4, 5] and cut_at_stop([4, 5], {9}) == [4, 5] and cut_at_stop([], {1}) == []
