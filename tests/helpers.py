@@ -43,7 +43,10 @@ class Replay:
                 self.logits.setdefault(rid, {})[start + w] = out[r]
                 r += 1
         for layer, lst in self.cap.items():
-            idx = lst[0].cpu()
+            # a step larger than the engine's max_step_tokens runs as pieces, each of which records its own
+            # tokens' choices; the pieces follow the packed order, so joined they are the step's
+            idx = torch.cat([x.cpu() for x in lst])
+            assert idx.shape[0] == sum(n for _, _, n, _ in layout)
             t = 0
             for rid, start, n, _ in layout:
                 for i in range(n):
@@ -93,3 +96,53 @@ def compare_with_plain(model_dir, requests, replay, dtype, positions=None):
             assert err <= rtol, (f"request {rid} position {p}: logits differ from the plain implementation "
                                  f"by {err:.3e} of max |logit| (tolerance {rtol:.1e}, dtype {dtype})")
     return worst
+
+
+# ---- the three schedules of the replay tests -----------------------------------------------------------
+def run_whole(rp, reqs):
+    """Each request alone, its whole token list in one step, logits at every position."""
+    for rid, toks in reqs.items():
+        rp.step([(rid, toks, list(range(len(toks))))])
+        rp.end(rid)
+
+
+def run_tail(rp, reqs, tail=32):
+    """Each request alone: all but the last `tail` tokens in one step, the rest one by one.  Returns the
+    positions whose logits were recorded."""
+    positions = {}
+    for rid, toks in reqs.items():
+        n = len(toks)
+        head = n - tail
+        assert head >= 1
+        rp.step([(rid, toks[:head], [head - 1])])
+        for i in range(head, n):
+            rp.step([(rid, [toks[i]], [0])])
+        rp.end(rid)
+        positions[rid] = list(range(head - 1, n))
+    return positions
+
+
+def run_batched(rp, batches):
+    """batches: a list of {rid: (tokens, prompt_len)}.  In a batch all requests start together with their
+    prompts, then bring one token each per step; a request whose tokens are used up ends and leaves the
+    batch.  Batch follows batch on the same engine, so slots and pages are used again.  Returns the
+    positions whose logits were recorded."""
+    e = rp.e
+    positions = {}
+    for reqs in batches:
+        rp.step([(rid, t[:p], [p - 1]) for rid, (t, p) in reqs.items()])
+        live = dict(reqs)
+        step = 0
+        while live:
+            for rid in [r for r, (t, p) in live.items() if p + step >= len(t)]:
+                rp.end(rid)
+                del live[rid]
+            if not live:
+                break
+            rp.step([(rid, [t[p + step]], [0]) for rid, (t, p) in live.items()])
+            step += 1
+        e.cache.check_consistency()
+        assert e.cache.free_slots == e.cache.max_slots
+        for rid, (t, p) in reqs.items():
+            positions[rid] = list(range(p - 1, len(t)))
+    return positions
