@@ -209,29 +209,55 @@ class CacheManager:
         self._free_slots.append(slot)
 
     # ---- steps ---------------------------------------------------------------------------------
-    def prepare_step(self, slots: list, n_new: list) -> list:
-        """Hold pages for the new positions of each sequence; returns the start position of each."""
-        if len(set(slots)) != len(slots):
-            raise CacheError("a step names the same slot twice")
-        starts = []
-        for s, n in zip(slots, n_new):
-            if not (0 <= s < self.max_slots) or not self._live[s]:
-                raise CacheError(f"slot {s} is stepped but is not live")
-            if n < 1:
-                raise CacheError(f"slot {s}: a step must bring at least one token")
-            if self.lengths[s] + n > self.max_seq_len:
-                raise CacheError(f"slot {s}: {self.lengths[s]} + {n} positions exceed the longest "
-                                 f"sequence the cache was sized for ({self.max_seq_len})")
-            starts.append(self.lengths[s])
-        done = []
-        try:
+    def check_room(self, pieces: list) -> None:
+        """Raises, having changed nothing, unless the cache can hold what `pieces` bring: a list of
+        (slots, n_new) that will run one after the other (a single step is one piece).  Per group the pages
+        are counted as the steps would take and give them back, windows included, in the same order."""
+        ps = self.page_size
+        lengths: dict = {}
+        for slots, n_new in pieces:
+            if len(set(slots)) != len(slots):
+                raise CacheError("a step names the same slot twice")
             for s, n in zip(slots, n_new):
-                for g in self.groups:
-                    g.ensure(s, self.lengths[s], n)
-                done.append(s)
-        except CacheFull:
-            raise CacheFull(f"the cache is full: {self.tokens_held()} of {self.n_pages * self.page_size} "
-                            f"positions are held by {len(self.live_slots())} sequences") from None
+                if not (0 <= s < self.max_slots) or not self._live[s]:
+                    raise CacheError(f"slot {s} is stepped but is not live")
+                if n < 1:
+                    raise CacheError(f"slot {s}: a step must bring at least one token")
+                at = lengths.get(s, self.lengths[s])
+                if at + n > self.max_seq_len:
+                    raise CacheError(f"slot {s}: {at} + {n} positions exceed the longest sequence the cache "
+                                     f"was sized for ({self.max_seq_len})")
+                lengths[s] = at + n
+        for g in self.groups:
+            free = g.pool.free_count
+            held: dict = {}
+            at: dict = {}
+            for slots, n_new in pieces:
+                for s, n in zip(slots, n_new):
+                    h = held.setdefault(s, set(g.blocks[s]))
+                    length = at.get(s, self.lengths[s])
+                    first = g.req.first_needed_position(length) // ps
+                    gone = {b for b in h if b < first}
+                    free += len(gone)
+                    h -= gone
+                    for b in range(length // ps, (length + n - 1) // ps + 1):
+                        if b not in h:
+                            h.add(b)
+                            free -= 1
+                    if free < 0:
+                        raise CacheFull(f"the cache is full: {self.tokens_held()} of {self.n_pages * ps} "
+                                        f"positions are held by {len(self.live_slots())} sequences and the step "
+                                        f"needs more than the rest")
+                    at[s] = length + n
+
+    def prepare_step(self, slots: list, n_new: list) -> list:
+        """Hold pages for the new positions of each sequence; returns the start position of each.  Either
+        every sequence of the step gets its pages or nothing changes."""
+        self.check_room([(slots, n_new)])
+        starts = [self.lengths[s] for s in slots]
+        for s, n in zip(slots, n_new):
+            for g in self.groups:
+                g.ensure(s, self.lengths[s], n)
         for g in self.groups:
             g.sync_tables()
         return starts

@@ -150,6 +150,8 @@ class Engine:
             pieces.append(cur)
         if any(sorted(w) != w for w in wants):
             raise ValueError("a step larger than max_step_tokens needs each entry's `want` in ascending order")
+        # all pieces together must fit before the first one runs: a step is run whole or not at all
+        self.cache.check_room([([c[0] for c in piece], [len(c[1]) for c in piece]) for piece in pieces])
         outs = [self._run([c[0] for c in piece], [c[1] for c in piece], [c[2] for c in piece]).clone()
                 for piece in pieces]
         return torch.cat(outs, dim=0)

@@ -130,3 +130,32 @@ def test_random_workload_never_loses_a_page():
         m.release(s)
     m.check_consistency()
     assert all(g.pool.free_count == g.pool.n_pages for g in m.groups) and m.free_slots == m.max_slots
+
+
+def test_a_step_that_does_not_fit_takes_nothing():
+    """A step either gets the pages of all its sequences or leaves the cache as it was; and a step that will run
+    as several pieces is refused before its first piece."""
+    m = CacheManager({0: KVRequirement(2, 16), 1: KVRequirement(2, 16, "chunk", 32)}, {}, max_tokens=64, max_seqs=3,
+                     page_size=16, device="cpu", dtype=__import__("torch").float32)
+    a, b, c = m.acquire(), m.acquire(), m.acquire()
+    m.prepare_step([a], [20]); m.commit_step([a], [20])            # two of four pages
+    held = [g.pages_held() for g in m.groups]
+    with pytest.raises(CacheFull):
+        m.prepare_step([b, c], [16, 17])                          # b would fit, c would not
+    assert [g.pages_held() for g in m.groups] == held
+    assert m.lengths[b] == 0 and m.lengths[c] == 0
+    m.check_consistency()
+    with pytest.raises(CacheFull):
+        m.check_room([([b], [16]), ([c], [10]), ([c], [8])])      # the third piece would need a fifth page
+    assert [g.pages_held() for g in m.groups] == held
+    m.check_room([([b], [16]), ([c], [10]), ([c], [6])])
+    with pytest.raises(CacheError, match="longest"):
+        m.check_room([([b], [40]), ([b], [40])])
+    # a windowed group gives pages back between pieces: 80 positions of one sequence pass through the chunk
+    # group's four pages, but not through the group that keeps everything
+    w = CacheManager({0: KVRequirement(2, 16, "chunk", 32)}, {}, max_tokens=64, max_seqs=1, max_seq_len=160,
+                     page_size=16, device="cpu", dtype=__import__("torch").float32)
+    s = w.acquire()
+    w.check_room([([s], [40]), ([s], [40]), ([s], [40])])
+    with pytest.raises(CacheFull):
+        w.check_room([([s], [120])])                              # one piece holds all its pages at once
