@@ -1,8 +1,8 @@
-"""cpi_b200: a small model library with generation of its own for the Llama4 text decoder on one B200."""
-from .config import ConfigError, Llama4TextConfig, ModelSpec, spec_from_model_dir
+"""cpi_b200: a small model library with generation of its own on one B200."""
+from .config import ConfigError, ModelSpec, spec_from_model_dir
 from .weights import WeightsError, write_random_model
 
-__all__ = ["ConfigError", "Llama4TextConfig", "ModelSpec", "spec_from_model_dir", "WeightsError",
+__all__ = ["ConfigError", "ModelSpec", "spec_from_model_dir", "WeightsError",
            "write_random_model", "Engine", "StepEntry", "Model", "generate"]
 
 

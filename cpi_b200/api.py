@@ -20,13 +20,13 @@ __all__ = ["Model", "generate", "GenerationResult", "SamplingParams"]
 
 
 class Model:
-    def __init__(self, engine: Engine, max_batch: int):
+    def __init__(self, engine: Engine, max_batch: int, max_context: Optional[int] = None):
         self.engine = engine
         self.max_batch = max_batch
         self.sampler = Sampler(engine.device, engine.spec.vocab_size)
         self.generator = Generator(engine, self.sampler, max_batch=max_batch,
                                    default_stop_ids=engine.spec.stop_token_ids,
-                                   bos_token_id=engine.spec.bos_token_id)
+                                   bos_token_id=engine.spec.bos_token_id, max_context=max_context)
 
     # ---- construction ----------------------------------------------------------------------------
     @staticmethod
@@ -41,11 +41,13 @@ class Model:
              config_overrides: Optional[dict] = None) -> "Model":
         """`max_batch` sequences of up to `max_context` positions each (the reference's EngineOptions
         names, include/engine/llama_engine.hpp:67-68); `max_tokens` bounds the cache instead when given.
+        The cache is sized in whole pages, but generation keeps to `max_context` itself: a longer prompt
+        is an error and a sequence ends when it reaches it.
         `config_overrides`: config.json keys that replace the file's, e.g. {"rope_theta": 1e6} or a
-        preset of `cpi_b200.config.llama4.PRESETS`."""
+        preset of `cpi_b200.config.registry.cli_presets()`."""
         eng = Engine.from_model_dir(model_dir, config_overrides, dtype=dtype, device=device,
                                     **cls._cache_args(max_batch, max_context, max_tokens, page_size))
-        return cls(eng, max_batch)
+        return cls(eng, max_batch, max_context)
 
     @classmethod
     def random(cls, config_json: dict, seed: int = 0, *, dtype="bfloat16", max_batch: int = 1,
@@ -53,7 +55,7 @@ class Model:
                page_size: int = 64, config_overrides: Optional[dict] = None) -> "Model":
         eng = Engine.from_random(config_json, seed, config_overrides, dtype=dtype, device=device,
                                  **cls._cache_args(max_batch, max_context, max_tokens, page_size))
-        return cls(eng, max_batch)
+        return cls(eng, max_batch, max_context)
 
     # ---- use -------------------------------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_new: int = 16, temperature: float = 0.8,

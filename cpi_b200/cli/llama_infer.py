@@ -7,15 +7,19 @@ positional model folder, --tokens, --max-new (16), --temp (0.8), --max-context (
 --benchmark-phases, --interactive; the LLAMA_INFER_* environment variables give defaults (:45-80,
 :190-193).  Output lines: "Output tokens:" (prompt + generated, src/app/main_modes.cpp:507-513), "[perf]"
 or "[perf-avg]" (:549-559), "[bench]" or "[bench-avg] reps=" (:560-606), "[bench-phase]" or
-"[bench-phase-avg]" (:576-617).  Exit codes: 1 argument error, 2 fatal error (src/main.cpp:67, :248).
+"[bench-phase-avg]" (:576-617).  Exit codes: 1 argument error, 2 fatal error, 3 another instance is running
+(src/main.cpp:51-55, :67, :248): like the reference, a process holds an exclusive lock on the file that
+LLAMA_INFER_LOCK_PATH names (default /tmp/llama_infer_single_instance.lock, src/app/main_helpers.cpp:24,
+:151-193) from its start to its end.
 Text prompts and tokenisers are outside this library: prompts are token ids, so --prompt, --tokenizer
 and --stop-text are answered with an argument error that names --tokens and --stop-ids, and --cpu with
 a fatal error (there is no CPU path).  --interactive speaks the reference's line-by-line JSON protocol
 (src/app/main_modes.cpp:46-270) with token ids in place of text: a request {"id", "tokens", "max_new",
 "temp", "stop_ids", "shutdown"}, events "start", "delta" {"tokens": [id]}, "metrics" {"token_index"},
 "done" {"tokens", "elapsed_ms", "generated_tokens", "tok_per_s"}, "error" {"error"}.
-Added here: --tokens-file, --batch-file, --stop-ids, --seed, --dtype, --random, --preset, --rope-pairing,
---qk-norm-order, --qk-norm-scope, --router-gate, --dump-logits.
+Added here: --tokens-file, --batch-file, --stop-ids, --seed, --dtype, --random, --dump-logits, --preset and
+the options that the registered architectures declare (for instance --rope-pairing, --qk-norm-order,
+--qk-norm-scope, --router-gate); they reach the model as config.json keys.
 """
 from __future__ import annotations
 
@@ -25,7 +29,7 @@ import os
 import sys
 import time
 
-from ..config.llama4 import PRESETS, QK_NORM_ORDERS, QK_NORM_SCOPES, ROPE_PAIRINGS, ROUTER_GATES
+from ..config.registry import cli_options, cli_presets
 
 PHASES = ("rmsnorm", "qkv", "kv_store", "attention", "wo", "mlp", "moe_router", "moe_expert", "moe_merge", "lm_head")
 
@@ -49,7 +53,7 @@ def parse_tokens(csv: str) -> list:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="llama_infer", description="Generate token ids with a Llama4 model folder.")
+    p = argparse.ArgumentParser(prog="llama_infer", description="Generate token ids with a model folder.")
     p.add_argument("model_dir", nargs="?", help="folder with config.json and *.safetensors")
     p.add_argument("--random", metavar="CONFIG.json", help="draw random weights for this configuration instead")
     p.add_argument("--tokens", default="1,2,3", help="prompt token ids, comma separated")
@@ -73,13 +77,13 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--benchmark-reps", type=int, default=1)
     p.add_argument("--benchmark-warmup", type=int, default=0)
     p.add_argument("--benchmark-phases", action="store_true", help="also time the phases of the decode steps")
-    p.add_argument("--rope-theta", type=float, default=None, help="replaces config.json's rope_theta")
-    p.add_argument("--preset", choices=sorted(PRESETS), default=None,
-                   help="a named set of the options below (and, for reference_compat, of the layer pattern)")
-    p.add_argument("--rope-pairing", choices=ROPE_PAIRINGS, default=None)
-    p.add_argument("--qk-norm-order", choices=QK_NORM_ORDERS, default=None)
-    p.add_argument("--qk-norm-scope", choices=QK_NORM_SCOPES, default=None)
-    p.add_argument("--router-gate", choices=ROUTER_GATES, default=None)
+    p.add_argument("--preset", choices=sorted(cli_presets()), default=None,
+                   help="a named set of config.json keys that an architecture registers")
+    for flag, key, kind, text in cli_options():       # what the registered architectures let a command line set
+        if isinstance(kind, tuple):
+            p.add_argument(flag, dest="cfg_" + key, choices=kind, default=None, help=text)
+        else:
+            p.add_argument(flag, dest="cfg_" + key, type=kind, default=None, help=text)
     p.add_argument("--dump-logits", metavar="FILE",
                    help="write the logits after each prompt as little-endian float32 [prompts, vocab]")
     p.add_argument("--interactive", action="store_true", help="requests as JSON lines on standard input")
@@ -91,10 +95,10 @@ def build_parser() -> argparse.ArgumentParser:
 
 def config_overrides(a) -> dict:
     """The config.json keys that the command line replaces: the preset first, single options over it."""
-    out = dict(PRESETS[a.preset]) if a.preset else {}
-    for key in ("rope_theta", "rope_pairing", "qk_norm_order", "qk_norm_scope", "router_gate"):
-        if getattr(a, key) is not None:
-            out[key] = getattr(a, key)
+    out = dict(cli_presets()[a.preset]) if a.preset else {}
+    for _flag, key, _kind, _text in cli_options():
+        if getattr(a, "cfg_" + key, None) is not None:
+            out[key] = getattr(a, "cfg_" + key)
     return out
 
 
@@ -109,7 +113,8 @@ def validate(a) -> None:
         if getattr(a, flag) is not None:
             bad(f"--{flag.replace('_', '-')} needs a tokeniser, which this library does not have: give token ids "
                 f"with {instead}")
-    if a.rope_theta is not None and not a.rope_theta > 0:
+    theta = getattr(a, "cfg_rope_theta", None)
+    if theta is not None and not theta > 0:
         bad("--rope-theta must be > 0")
     if a.benchmark_phases or a.benchmark_reps != 1 or a.benchmark_warmup != 0:
         a.benchmark = True                     # as the reference's parser does (src/app/main_cli.cpp:255-265)
@@ -129,7 +134,49 @@ def validate(a) -> None:
         bad("--benchmark-reps must be >= 1 and --benchmark-warmup >= 0")
 
 
+class SingleInstance:
+    """The reference's guard (src/app/main_helpers.cpp:151-193): an exclusive, non-blocking lock on a file,
+    held while the process runs.  `acquire` answers False when another process holds it (or the file cannot
+    be opened), as the reference's does."""
+
+    def __init__(self, path=None):
+        self.path = path or os.environ.get("LLAMA_INFER_LOCK_PATH") or "/tmp/llama_infer_single_instance.lock"
+        self._fd = None
+
+    def acquire(self) -> bool:
+        import fcntl
+        try:
+            fd = os.open(self.path, os.O_CREAT | os.O_RDWR, 0o644)
+        except OSError:
+            return False
+        try:
+            fcntl.flock(fd, fcntl.LOCK_EX | fcntl.LOCK_NB)
+        except OSError:
+            os.close(fd)
+            return False
+        self._fd = fd
+        return True
+
+    def release(self) -> None:
+        if self._fd is not None:
+            import fcntl
+            fcntl.flock(self._fd, fcntl.LOCK_UN)
+            os.close(self._fd)
+            self._fd = None
+
+
 def main(argv=None) -> int:
+    guard = SingleInstance()
+    if not guard.acquire():
+        print("Another llama_infer instance is already running.", file=sys.stderr)
+        return 3
+    try:
+        return _main(argv)
+    finally:
+        guard.release()
+
+
+def _main(argv=None) -> int:
     parser = build_parser()
     try:
         a = parser.parse_args(argv)

@@ -9,14 +9,10 @@ carries a number of its own.
 """
 from __future__ import annotations
 
-import json
-import os
 from dataclasses import asdict, dataclass
 from typing import Any, Optional
 
-
-class ConfigError(ValueError):
-    """A config.json value is missing, of the wrong type, or inconsistent."""
+from .common import ConfigError, read_config_json, token_id_list
 
 
 @dataclass(frozen=True)
@@ -69,6 +65,17 @@ PRESETS = {
                          "nope_layer_interval": 0, "no_rope_layers": None, "layer_types": None,
                          "attention_chunk_size": 0, "attn_temperature_tuning": False},
 }
+
+
+# What a command line may set of this architecture besides its presets: (flag, config.json key, type or choices,
+# help).  --rope-theta is the reference's own flag (src/app/main_cli.cpp:280-281).
+CLI_OPTIONS = (
+    ("--rope-theta", "rope_theta", float, "replaces config.json's rope_theta"),
+    ("--rope-pairing", "rope_pairing", ROPE_PAIRINGS, "which elements of a head a rotation pairs"),
+    ("--qk-norm-order", "qk_norm_order", QK_NORM_ORDERS, "head norm before or after the rotation"),
+    ("--qk-norm-scope", "qk_norm_scope", QK_NORM_SCOPES, "head norm on the rotating layers or on all"),
+    ("--router-gate", "router_gate", ROUTER_GATES, "where the router's sigmoid gate is applied"),
+)
 
 
 @dataclass(frozen=True)
@@ -205,13 +212,7 @@ class Llama4TextConfig:
                     original_max_position_embeddings=int(rs["original_max_position_embeddings"]))
             except KeyError as e:
                 raise ConfigError(f"config.json: rope_scaling is missing key {e}") from None
-        eos = d.get("eos_token_id")
-        if eos is None:
-            eos_ids: tuple = ()
-        elif isinstance(eos, (list, tuple)):
-            eos_ids = tuple(int(x) for x in eos)
-        else:
-            eos_ids = (int(eos),)
+        eos_ids = token_id_list(d.get("eos_token_id"), "config.json: 'eos_token_id'")
         bos = d.get("bos_token_id")
         extras = {}
         for key, allowed in (("rope_pairing", ROPE_PAIRINGS), ("qk_norm_order", QK_NORM_ORDERS),
@@ -294,17 +295,3 @@ class Llama4TextConfig:
 def _check_int(key: str, v: Any) -> None:
     if isinstance(v, bool) or not isinstance(v, int):
         raise ConfigError(f"config.json: '{key}' must be an integer, got {v!r}")
-
-
-def read_config_json(model_dir: str) -> dict:
-    path = os.path.join(model_dir, "config.json")
-    if not os.path.isfile(path):
-        raise ConfigError(f"no config.json in model folder '{model_dir}'")
-    with open(path, "r", encoding="utf-8") as f:
-        try:
-            raw = json.load(f)
-        except json.JSONDecodeError as e:
-            raise ConfigError(f"{path}: not valid JSON ({e})") from None
-    if not isinstance(raw, dict):
-        raise ConfigError(f"{path}: top level must be an object")
-    return raw

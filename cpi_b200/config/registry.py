@@ -1,6 +1,6 @@
 """One registry from an architecture's name (config.json `architectures[0]`) to its model.
 
-The reference picks its Llama4 engine by "the path is a folder with *.safetensors"
+The reference picks its safetensors engine by "the path is a folder with *.safetensors"
 (src/main.cpp:169-174, src/app/main_helpers.cpp:464-486) and knows no names.
 Here an architecture registers, under each name it answers to, a function that
 reads config.json into its typed configuration and one that turns that
@@ -11,7 +11,9 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Any, Callable
 
-from .llama4 import ConfigError, read_config_json
+import dataclasses
+
+from .common import ConfigError, generation_stop_ids, read_config_json
 from .spec import ModelSpec
 
 
@@ -20,6 +22,10 @@ class Architecture:
     name: str
     parse_config: Callable[[dict], Any]        # raw config.json dict -> typed configuration
     build_spec: Callable[[Any], ModelSpec]     # typed configuration -> ModelSpec
+    # named sets of config.json keys that a command line or a caller may write over the file's
+    presets: dict = dataclasses.field(default_factory=dict)
+    # single config.json keys a command line may set: (flag, key, type or tuple of choices, help)
+    cli_options: tuple = ()
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -72,9 +78,35 @@ def spec_from_model_dir(model_dir: str, overrides: dict | None = None):
     cfg = arch.parse_config(raw)
     spec = arch.build_spec(cfg)
     spec.validate()
+    more = tuple(t for t in generation_stop_ids(model_dir) if t not in spec.stop_token_ids)
+    if more:
+        spec = dataclasses.replace(spec, stop_token_ids=tuple(spec.stop_token_ids) + more)
     return cfg, spec
 
 
+def cli_presets() -> dict:
+    """{preset name: {config.json key: value}} over all registered architectures."""
+    _ensure_builtin()
+    out: dict = {}
+    for arch in _ARCHITECTURES.values():
+        for name, keys in arch.presets.items():
+            if out.setdefault(name, keys) != keys:
+                raise ConfigError(f"two architectures register different presets named '{name}'")
+    return out
+
+
+def cli_options() -> list:
+    """The (flag, key, type or choices, help) options of all registered architectures, each flag once."""
+    _ensure_builtin()
+    seen, out = set(), []
+    for arch in _ARCHITECTURES.values():
+        for opt in arch.cli_options:
+            if opt[0] not in seen:
+                seen.add(opt[0])
+                out.append(opt)
+    return out
+
+
 def _ensure_builtin() -> None:
-    # the built-in architectures register themselves on import
-    from ..models import llama4  # noqa: F401
+    # the built-in architectures register themselves when the package of architectures is imported
+    from .. import models  # noqa: F401

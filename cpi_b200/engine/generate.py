@@ -1,8 +1,10 @@
 """The generation loop above the step function.
 
 Reference loop for one prompt (src/engine/llama4_cuda_engine.cu:541-621): run the prompt, then
-repeat { sample; append; stop if the token is the end token (it is kept in the output); stop if the
-callback says so; stop at max_new; stop when the context is full; run the token }.  Here the same order
+repeat { sample; append; hand the token to the callback (the end token too) and stop if it says so; stop
+if the token is the end token (it is kept in the output); stop at max_new; stop when the context is full
+(a prompt longer than max_context is an error, :549-551; pos + 1 >= max_context ends it, :602-604); run the
+token }.  Here the same order
 of decisions holds per sequence, for batches of unequal prompts that start together: a sequence that
 stops leaves the next step's batch and gives its slot back at once, and when more requests are given
 than fit, batch follows batch in slots that the previous one freed.
@@ -74,9 +76,13 @@ def plan_batches(requests: Sequence[GenerationRequest], *, max_batch: int, token
 
 class Generator:
     def __init__(self, engine, sampler, *, max_batch: int, default_stop_ids: Sequence[int] = (),
-                 bos_token_id: Optional[int] = None, step_entry=None):
+                 bos_token_id: Optional[int] = None, step_entry=None, max_context: Optional[int] = None):
+        """`max_context`: the most positions a sequence may reach (the caller's own figure: the cache may
+        hold a few more, since it is sized in whole pages); default: what the cache holds per sequence."""
         self.engine, self.sampler = engine, sampler
         self.max_batch = max_batch
+        self.max_context = min(int(max_context), engine.cache.max_seq_len) if max_context is not None \
+            else engine.cache.max_seq_len
         self.default_stop_ids = tuple(default_stop_ids)
         self.bos_token_id = bos_token_id
         if step_entry is None:
@@ -106,7 +112,7 @@ class Generator:
             reqs.append(GenerationRequest(prompt, r.max_new, r.sampling, r.stop_ids))
         cache = self.engine.cache
         batches = plan_batches(reqs, max_batch=self.max_batch, token_capacity=cache.n_pages * cache.page_size,
-                               page_size=cache.page_size, max_seq_len=cache.max_seq_len)
+                               page_size=cache.page_size, max_seq_len=self.max_context)
         self.stats = GenerationStats()
         results: list = [None] * len(reqs)
         for batch in batches:
@@ -121,7 +127,7 @@ class Generator:
                 and hasattr(self.sampler, "sample_device"):
             return self._run_batch_pipelined(idxs, reqs, results)
         eng = self.engine
-        max_len = eng.cache.max_seq_len
+        max_len = self.max_context
         live = list(idxs)
         slot = {i: eng.acquire_slot() for i in live}
         out = {i: [] for i in live}
@@ -147,9 +153,11 @@ class Generator:
                     out[i].append(tok)
                     self.stats.generated_tokens += 1
                     reason = None
+                    # the callback sees every token, the end token too, before the end-token check (:593-598)
+                    go_on = on_token(i, tok) if on_token is not None else True
                     if tok in stops[i]:
                         reason = "stop_token"
-                    elif on_token is not None and not on_token(i, tok):
+                    elif not go_on:
                         reason = "callback"
                     elif len(out[i]) >= reqs[i].max_new:
                         reason = "max_new"
@@ -196,7 +204,7 @@ class Generator:
         one are known on the host.  A request that turns out to have ended on a stop token has then been
         run for one token too many; that token is dropped and the others' results do not depend on it."""
         eng, sampler = self.engine, self.sampler
-        max_len = eng.cache.max_seq_len
+        max_len = self.max_context
         live = list(idxs)
         slot = {i: eng.acquire_slot() for i in live}
         out = {i: [] for i in live}

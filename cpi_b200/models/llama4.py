@@ -15,7 +15,7 @@ src/engine/llama4_cpu_engine.cpp:293-333):
 """
 from __future__ import annotations
 
-from ..config.llama4 import Llama4TextConfig
+from ..config.llama4 import CLI_OPTIONS, PRESETS, Llama4TextConfig
 from ..config.registry import Architecture, register_architecture
 from ..config.spec import LayerSpec, ModelSpec, PartSpec, RunEntry
 
@@ -110,4 +110,4 @@ def build_spec(cfg: Llama4TextConfig) -> ModelSpec:
 
 
 for _name in ("Llama4ForConditionalGeneration", "Llama4ForCausalLM"):
-    register_architecture(Architecture(_name, Llama4TextConfig.from_json_dict, build_spec))
+    register_architecture(Architecture(_name, Llama4TextConfig.from_json_dict, build_spec, PRESETS, CLI_OPTIONS))

@@ -6,7 +6,8 @@ import tempfile
 import pytest
 
 import tiny
-from cpi_b200.config import (ConfigError, Llama4TextConfig, get_architecture, registered_architectures,
+from cpi_b200.config.llama4 import Llama4TextConfig
+from cpi_b200.config import (ConfigError, get_architecture, registered_architectures,
                              spec_from_model_dir, architecture_of, RunEntry)
 from cpi_b200.models.llama4 import build_spec
 

@@ -121,7 +121,18 @@ def test_callback_stops_after_the_token_is_appended_and_stop_token_wins():
     r = g.generate([GenerationRequest([3], 9), GenerationRequest([5], 9)], cb)
     assert r[0].tokens == [4, 5] and r[0].finish_reason == "callback"
     assert r[1].tokens == [6] and r[1].finish_reason == "stop_token"
-    assert (1, 6) not in seen                     # the stop check comes before the callback
+    assert (1, 6) in seen and (0, 5) in seen      # the callback sees the end token too; the reason stays the token
+
+
+def test_max_context_is_the_callers_figure_not_the_cache_rounded_up():
+    e = FakeEngine(max_seq_len=128, page_size=64, n_pages=8)       # a cache of whole pages: 128 positions
+    g = gen(e, max_batch=1, max_context=100)
+    r = g.generate([GenerationRequest(list(range(40)), 500)])
+    assert r[0].finish_reason == "capacity" and len(r[0].tokens) == 61      # 40 + 61 - 1 == 100 positions run
+    assert len(e.steps) == 61
+    with pytest.raises(ValueError, match="longest"):
+        g.generate([GenerationRequest(list(range(101)), 2)])
+    g.generate([GenerationRequest(list(range(100)), 2)])
 
 
 def test_capacity_stop():
