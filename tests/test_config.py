@@ -158,3 +158,23 @@ def test_overrides_and_presets():
         assert (back.qk_norm_order, back.qk_norm_scope, back.router_gate) == ("after_rope", "rope_layers", "sigmoid_input")
         with pytest.raises(ConfigError, match="router_gate"):
             arch.parse_config(apply_overrides(raw, {"router_gate": "softmax"}))
+
+
+def test_stop_ids_of_generation_config_json_join_the_models(tmp_path):
+    """`eos_token_id` of generation_config.json (one id or a list) is added to config.json's; a folder without the
+    file keeps config.json's alone; a value that is no id is an error that names the file."""
+    import json as js
+    from cpi_b200.config.common import generation_stop_ids
+    d = tmp_path / "m"
+    d.mkdir()
+    (d / "config.json").write_text(js.dumps(tiny.config("A")))           # eos_token_id [3, 5]
+    assert spec_from_model_dir(str(d))[1].stop_token_ids == (3, 5)
+    (d / "generation_config.json").write_text(js.dumps({"eos_token_id": [5, 9, 11], "temperature": 0.6}))
+    assert spec_from_model_dir(str(d))[1].stop_token_ids == (3, 5, 9, 11)
+    (d / "generation_config.json").write_text(js.dumps({"eos_token_id": 7}))
+    assert generation_stop_ids(str(d)) == (7,)
+    (d / "generation_config.json").write_text(js.dumps({"eos_token_id": "</s>"}))
+    with pytest.raises(ConfigError, match="generation_config.json"):
+        spec_from_model_dir(str(d))
+    (d / "generation_config.json").write_text(js.dumps({"temperature": 0.6}))
+    assert spec_from_model_dir(str(d))[1].stop_token_ids == (3, 5)

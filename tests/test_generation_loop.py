@@ -299,6 +299,45 @@ def test_command_line_argument_errors_and_interactive_protocol(capsys):
     assert m.kw["temperature"] == 0.8 and m.kw["max_new"] == 4      # the second request ran on the defaults
 
 
+def test_command_line_is_one_instance_at_a_time(tmp_path, monkeypatch, capsys):
+    """While one process holds the lock file, a second start ends with exit code 3 and the reference's sentence
+    (src/main.cpp:51-55); when the first has ended the lock is free again."""
+    import fcntl
+    import os
+    from cpi_b200.cli import llama_infer as cli
+    lock = str(tmp_path / "instance.lock")
+    monkeypatch.setenv("LLAMA_INFER_LOCK_PATH", lock)
+    fd = os.open(lock, os.O_CREAT | os.O_RDWR, 0o644)
+    fcntl.flock(fd, fcntl.LOCK_EX | fcntl.LOCK_NB)
+    assert cli.main(["m", "--cpu"]) == 3
+    assert "Another llama_infer instance is already running." in capsys.readouterr().err
+    fcntl.flock(fd, fcntl.LOCK_UN)
+    os.close(fd)
+    assert cli.main(["m", "--cpu"]) == 2          # the lock is free: the run gets as far as its own error
+    g = cli.SingleInstance()
+    assert g.acquire() and not cli.SingleInstance().acquire()
+    g.release()
+    assert cli.SingleInstance().acquire()
+
+
+def test_command_line_options_come_from_the_registered_architectures():
+    """The command line knows no architecture: presets and model options are what the registry's entries declare,
+    and an architecture registered from outside brings its own."""
+    from cpi_b200.cli import llama_infer as cli
+    from cpi_b200.config import registry
+    flags = {o[0] for o in registry.cli_options()}
+    assert {"--rope-theta", "--rope-pairing", "--qk-norm-order", "--qk-norm-scope", "--router-gate"} <= flags
+    assert {"llama4", "reference_compat"} <= set(registry.cli_presets())
+    toy = registry.Architecture("ToyForTests", lambda raw: raw, lambda cfg: None, {"toy_preset": {"toy_width": 3}},
+                                (("--toy-depth", "toy_depth", int, "layers of the toy"),))
+    registry.register_architecture(toy)
+    try:
+        a = cli.build_parser().parse_args(["m", "--preset", "toy_preset", "--toy-depth", "5"])
+        assert cli.config_overrides(a) == {"toy_width": 3, "toy_depth": 5}
+    finally:
+        registry._ARCHITECTURES.pop("ToyForTests")
+
+
 def test_bench_refuses_more_than_one_gpu_and_names_the_reference_arm():
     """What bench.py answers without touching a GPU: one line and exit code 2 for N > 1, and the reference
     arm's `unavailable` line with exit code 0."""
