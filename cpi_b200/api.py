@@ -74,7 +74,9 @@ class Model:
         """One step of the engine on sequences that the caller manages: `slots` from `acquire_slot()`,
         `tokens[i]` the next tokens of slot i (all prompts, or one token each).  `logits`: "last" (one row per
         sequence), "all", or a list of places per sequence.  Returns float32 logits [rows, vocab] on the
-        device, valid until the next step.  Give slots back with `release_slot()`."""
+        device, valid until the next step.  Give slots back with `release_slot()`.  What a kernel flags (a token
+        id outside the vocabulary, a wait that ran out) is raised by the next step or by
+        `engine.check_device_errors()`, which waits for the device."""
         if logits == "last":
             want = [[len(t) - 1] for t in tokens]
         elif logits == "all":
@@ -94,7 +96,9 @@ class Model:
         src/engine/llama4_cuda_engine.cu:623-674, without its top-k cut)."""
         s = self.engine.acquire_slot()
         try:
-            return self.engine.step([StepEntry(s, list(prompt), [len(prompt) - 1])])[0].clone()
+            row = self.engine.step([StepEntry(s, list(prompt), [len(prompt) - 1])])[0].clone()
+            self.engine.check_device_errors()
+            return row
         finally:
             self.engine.release_slot(s)
 

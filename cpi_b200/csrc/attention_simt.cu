@@ -323,7 +323,7 @@ extern "C" int cpi_qkv_post(const void* qkv, long qkv_stride, void* q_out, void*
   if (dtype == kBF16 && head_dim == 128 && !interleaved && qkv_stride % 8 == 0 && aligned16(qkv) && aligned16(q_out) &&
       (!write_kv || (aligned16(k_cache) && aligned16(v_cache))) && n_tokens <= 65535) {
     // enough blocks for two waves of the GPU, at most one block per 16 heads
-    int slices = (2 * 148 * 8 + n_tokens - 1) / n_tokens;
+    int slices = (2 * sm_count() * 8 + n_tokens - 1) / n_tokens;
     const int max_slices = (heads_total + 15) / 16;
     if (slices > max_slices) slices = max_slices;
     if (slices < 1) slices = 1;

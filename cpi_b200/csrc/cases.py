@@ -68,15 +68,9 @@ def case_gemm(a) -> None:
         offs[1:] = counts.cumsum(0)
         kw = dict(m_rows=T, group_offsets=offs.to(DEV), n_groups=G)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
-    if a.bn:
-        kw["force_bn"] = a.bn
-    if a.splits:
-        kw["force_splits"] = a.splits
     if a.persistent is not None:
         K.gemm_pair_persistent(a.persistent)
     fn = K.gemm_tc_pair if a.pair else K.gemm_tc
-    if a.pair:
-        kw.pop("force_bn", None); kw.pop("force_splits", None)
     if not fn(x, w, out, mode, **kw):
         sys.exit("this shape is outside what the tensor-core kernel takes")
     us = _timed(lambda: fn(x, w, out, mode, **kw), a.reps, flush)
@@ -196,8 +190,6 @@ def main() -> int:
     g.add_argument("--groups", type=int, default=0)
     g.add_argument("--pair", action="store_true", help="use the paired (two-SM) kernel")
     g.add_argument("--persistent", type=int, default=None, help="paired kernel: 2 a pair per SM pair works through the tiles, 0 a launch slot per tile, 1 by shape")
-    g.add_argument("--bn", type=int, default=0, help="force the token-tile width (tuning)")
-    g.add_argument("--splits", type=int, default=0, help="force the split-K count (tuning)")
     d = sub.add_parser("attention_decode")
     d.add_argument("--batch", type=int, default=8)
     d.add_argument("--context", type=int, default=4096)

@@ -18,6 +18,7 @@ enum DType : int { kF32 = 0, kBF16 = 1 };
 void set_error(const char* fmt, ...);
 void count_launch();                 // every kernel launch of the library is counted (cpi_launch_count)
 int check_launch(const char* what);
+int sm_count();                      // multiprocessors of the current device (1 when no device answers)
 
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }

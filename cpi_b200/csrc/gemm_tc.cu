@@ -16,18 +16,15 @@
 // accumulators: rows n and N + n of W; out = silu(g) * u).  Optional per-token scale, output row
 // scatter, and groups (routed experts): tokens [offsets[g], offsets[g+1]) use W[g].
 //
-// Split-K: when a launch has too few tiles to fill the GPU, the k range is cut into `splits` parts,
-// summed in split order (a fixed order: the result does not depend on arrival order).  Two ways:
-//  * cluster (up to 8 splits, token tiles up to 128): the CTAs of a tile form a thread-block cluster
-//    along z.  Each puts its raw accumulators into its own shared memory; after a cluster barrier every
-//    CTA sums a share of the tile's columns over all CTAs' shared memory (distributed shared memory
-//    loads) and applies the epilogue to them.  No global scratch, and the merge runs in parallel.
-//  * tickets: each CTA stores its raw accumulators into `partials`; the CTA that takes the last ticket
-//    of a tile sums the parts, applies the epilogue and resets the ticket.  `partials` and `tickets`
-//    are scratch the caller provides; tickets must be zero before the first launch and are left zero.
+// Split-K: when a launch has too few tiles to fill the GPU, the k range is cut into `splits` parts (up
+// to 8, token tiles up to 128), summed in split order (a fixed order: the result does not depend on
+// arrival order).  The CTAs of a tile form a thread-block cluster along z.  Each puts its raw
+// accumulators into its own shared memory; after a cluster barrier every CTA sums a share of the tile's
+// columns over all CTAs' shared memory (distributed shared memory loads) and applies the epilogue to
+// them.  No global scratch, and the merge runs in parallel.
 //
-// Every mbarrier wait is bounded: when it runs out the CTA raises `*error_flag`, stops issuing work,
-// lets copies in flight land, frees its tensor memory and returns.
+// Every mbarrier wait is bounded (`spin_limit` polls): when it runs out the CTA raises `*error_flag`,
+// stops issuing work, lets copies in flight land, frees its tensor memory and returns.
 #include "common.cuh"
 #include "gemm_epilogue.cuh"
 #include <cuda.h>
@@ -42,7 +39,7 @@ namespace tc {
 constexpr int BM = 128;          // output features per tile (MMA M)
 constexpr int BK = 64;           // k elements per stage: 128 bytes of bf16 = one swizzle row
 constexpr int UMMA_K = 16;
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 24;      // polls of one wait before a CTA gives up (launches may pass fewer)
 
 enum Mode : int { kStore = 0, kAdd = 1, kSwiglu = 2 };
 
@@ -55,11 +52,11 @@ struct Params {
   int bn;              // token rows per tile: a multiple of 16, at most the kernel's BN
   int N;               // output features
   int k_tiles;         // ceil(K / 64)
-  int splits, k_tiles_per_split;
-  float* partials; int* tickets;
+  int splits, k_tiles_per_split;   // splits > 1: the splits of a tile are one cluster along z
   int tiles_on_x;      // 1: blockIdx.x counts token tiles and blockIdx.y weight tiles (groups with many tokens)
-  int cluster_split;   // 1: the splits of a tile are one cluster along z and merge through shared memory
   int* error_flag;
+  uint32_t spin_limit; // polls of one barrier wait before the CTA gives up
+  uint32_t tx_extra;   // bytes added to what a stage's barrier expects (0 but in the test of the give-up path)
 };
 
 // ---------------------------------------------------------------------------------------------- PTX
@@ -82,8 +79,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait: false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023u) == 1023u && *abort_flag) return false;
   }
@@ -178,7 +176,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], accum_bar;
   __shared__ uint32_t tmem_base_s;
-  __shared__ int abort_s, ticket_s;
+  __shared__ int abort_s;
   __shared__ int offs_s[257], tiles_s[256], found_s[2];   // group offsets and tile counts (at most 256 groups)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -223,7 +221,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
   const int n_kt = kt_end - kt_begin;
   // only the boxes that hold rows of this tile are fetched (a group's tail tile may hold few)
   const int n_boxes = (min(p.bn, t_end - t0) + BOX_ROWS - 1) / BOX_ROWS;
-  const uint32_t stage_tx = ACC * A_BYTES + (uint32_t)n_boxes * BOX_BYTES;
+  const uint32_t stage_tx = ACC * A_BYTES + (uint32_t)n_boxes * BOX_BYTES + p.tx_extra;
 
   if (tid == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -257,7 +255,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
                     (kt_begin + i) * BK, t0 + b * BOX_ROWS);
     for (int i = n_early; i < n_kt; ++i) {
       const int s = i % STAGES;
-      if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag)) break;
+      if (i >= STAGES && !mbar_wait(&empty_bar[s], ((i / STAGES) - 1) & 1, abort_flag, p.spin_limit)) break;
       uint8_t* st = smem + (size_t)s * STAGE_BYTES;
       mbar_expect_tx(&full_bar[s], stage_tx);
       const int k = (kt_begin + i) * BK;
@@ -275,7 +273,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
     bool ok = true;
     for (int i = 0; i < n_kt && ok; ++i) {
       const int s = i % STAGES;
-      ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abort_flag);
+      ok = mbar_wait(&full_bar[s], (i / STAGES) & 1, abort_flag, p.spin_limit);
       if (!ok) break;
       fence_after_sync();
       const uint32_t a_addr = smem_u32(smem + (size_t)s * STAGE_BYTES);
@@ -294,7 +292,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
 
   // ---- epilogue: all four warps ----
   pdl_wait();                                    // before any global read or write of this thread
-  bool ok = mbar_wait(&accum_bar, 0, abort_flag);
+  bool ok = mbar_wait(&accum_bar, 0, abort_flag, p.spin_limit);
   fence_after_sync();
   ok = __syncthreads_and(ok && !abort_s) != 0;            // one decision for the CTA
 
@@ -373,7 +371,7 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         for (int j = 0; j < 16; ++j) emit(c + j, v[j], ACC == 2 ? u[j] : 0.f);
       }
     }
-  } else if (p.cluster_split) {
+  } else {
     // Every thread of every CTA of the cluster passes both barriers, whether its own waits held or not.
     if constexpr (BN <= 128) {
       static_assert((size_t)ACC * BN * BM * 4 <= (size_t)STAGES * STAGE_BYTES, "the stages must hold a tile of floats");
@@ -422,56 +420,6 @@ __global__ void __launch_bounds__(128) gemm_tc_kernel(const __grid_constant__ CU
         }
       }
       cluster_sync();                                     // nobody leaves while its shared memory is being read
-    }
-  } else if (ok) {
-    // raw accumulators -> partials[tile][split][acc][col][row]
-    const size_t tile_id = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
-    float* mine = p.partials + ((tile_id * p.splits + split) * ACC) * (size_t)(BN * BM);
-#pragma unroll 1
-    for (int a = 0; a < ACC; ++a)
-#pragma unroll 1
-      for (int c = 0; c < n_cols; c += 16) {
-        float v[16];
-        tmem_ld16(lane_addr + a * BN + c, v);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) mine[((size_t)a * BN + c + j) * BM + row] = v[j];
-      }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) ticket_s = atomicAdd(&p.tickets[tile_id], 1);
-    __syncthreads();
-    if (ticket_s == p.splits - 1) {
-      __threadfence();
-      const float* base = p.partials + (tile_id * p.splits * ACC) * (size_t)(BN * BM);
-      // Sum the parts in split order.  Eight columns and four splits are fetched at a time, so that up to
-      // 32 (64 with two accumulators) loads are in flight per thread instead of one.
-#pragma unroll 1
-      for (int c0 = 0; c0 < n_valid_t; c0 += 8) {
-        float v[8], u[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) { v[j] = 0.f; u[j] = 0.f; }
-#pragma unroll 1
-        for (int z0 = 0; z0 < p.splits; z0 += 4) {
-          float tv[4][8], tu[4][8];
-#pragma unroll
-          for (int zz = 0; zz < 4; ++zz) {
-            const bool live = z0 + zz < p.splits;
-            const float* pz = base + ((size_t)(z0 + zz) * ACC) * (size_t)(BN * BM);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              tv[zz][j] = live ? __ldcg(pz + (size_t)(c0 + j) * BM + row) : 0.f;
-              if (ACC == 2) tu[zz][j] = live ? __ldcg(pz + ((size_t)BN + c0 + j) * BM + row) : 0.f;
-            }
-          }
-#pragma unroll
-          for (int zz = 0; zz < 4; ++zz)
-#pragma unroll
-            for (int j = 0; j < 8; ++j) { v[j] += tv[zz][j]; if (ACC == 2) u[j] += tu[zz][j]; }
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) emit(c0 + j, v[j], u[j]);
-      }
-      if (tid == 0) p.tickets[tile_id] = 0;
     }
   }
 
@@ -633,7 +581,7 @@ struct Variant {
 
   static int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Params& p, dim3 grid, cudaStream_t stream) {
     if (!prepare()) return 1;
-    if (p.cluster_split) {
+    if (p.splits > 1) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = grid;
       cfg.blockDim = dim3(128);
@@ -684,11 +632,13 @@ static int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const
 
 using namespace cpi;
 
-// Whether split-K merges through a cluster's shared memory (default) or through tickets and global scratch.
-static int g_cluster_split = 1;
-extern "C" void cpi_gemm_tc_cluster_split(int on) { g_cluster_split = on; }
-extern "C" int cpi_gemm_tc_uses_cluster_split(int bn, int splits) {
-  return g_cluster_split && splits > 1 && splits <= 8 && bn <= 128;
+// Polls of one barrier wait before a CTA gives up, and bytes added to what each stage's barrier expects.  The
+// defaults are those of every ordinary launch; the test of the give-up path sets a short limit and a byte count
+// that the stage's loads do not reach, launches once, and sets them back.
+static uint32_t g_spin_limit = tc::kSpinLimit, g_tx_extra = 0;
+extern "C" void cpi_gemm_tc_wait_probe(int spin_limit, int tx_extra) {
+  g_spin_limit = spin_limit > 0 ? (uint32_t)spin_limit : tc::kSpinLimit;
+  g_tx_extra = tx_extra > 0 ? (uint32_t)tx_extra : 0;
 }
 
 extern "C" int cpi_gemm_tc_max_clusters(int bn, int swiglu, int size) { return tc::max_clusters_for(bn, swiglu != 0, size); }
@@ -713,6 +663,7 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
   while (bn < 256 && bn < rows_per_group) bn *= 2;
   if (swiglu && bn > 256) bn = 256;
   const int n_tiles = (N + tc::BM - 1) / tc::BM;
+  const long sms = sm_count();
   if (n_groups == 0 && T > 256) {
     // many tokens: one CTA per SM at a time, and a tile's time follows the operand bytes it pulls through
     // the L2 per k-step (128 or 256 weight rows + the token rows), so time ~ waves x (weight rows + width);
@@ -721,7 +672,7 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
     const int w_rows = swiglu ? 256 : 128;
     for (int cand = 256; cand >= 128; cand -= 16) {
       const long ctas = (long)n_tiles * ((T + cand - 1) / cand);
-      const long waves = (ctas + 147) / 148;
+      const long waves = (ctas + sms - 1) / sms;
       const long cost = waves * (cand + w_rows);
       if (best_cost < 0 || cost < best_cost) { best_cost = cost; bn = cand; }
     }
@@ -735,23 +686,13 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
   const int run_y = n_groups > 0 ? (T <= n_groups ? T : (T + bn - 1) / bn + n_groups / 2) : (T + bn - 1) / bn;
   const long ctas = (long)n_tiles * (run_y > 0 ? run_y : 1);
   const int max_by_k = k_tiles / 4 > 0 ? k_tiles / 4 : 1;     // at least 4 k-tiles per split
-  if (g_cluster_split && bn <= 128 && (bn & (bn - 1)) == 0) {
+  if (bn <= 128 && (bn & (bn - 1)) == 0) {
     // the splits of a tile are a cluster: the most splits (up to 8) whose clusters are all resident at
     // once, so that the launch is one wave (a launch of 1.1 waves takes as long as one of 2)
     for (int s = max_by_k < 8 ? max_by_k : 8; s >= 2; --s) {
       const int per_s = (k_tiles + s - 1) / s;
       if ((long)(s - 1) * per_s >= k_tiles) continue;           // would leave an empty split
       if (ctas <= tc::max_clusters_for(bn, swiglu != 0, s)) { splits = s; break; }
-    }
-  } else {
-    const long slots = bn <= 32 ? 2 * 148 : 148;              // resident CTAs: narrow token tiles fit two per SM
-    if (ctas < slots) {
-      // fill one wave and no more
-      splits = (int)(slots / ctas);
-      if (splits > max_by_k) splits = max_by_k;
-      if (splits > 8) splits = 8;
-      if (bn >= 64 && splits > 1) splits = 1;                   // wide token tiles: the merge of parts costs more than it saves
-      if (splits < 1) splits = 1;
     }
   }
   const int per = (k_tiles + splits - 1) / splits;
@@ -761,12 +702,11 @@ extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, i
 }
 
 // x [T, K] bf16 (row stride ldx elements), w [G or 1][N or 2N][K] bf16 contiguous, out [*, N].
-// partials: float32 scratch of at least tiles * splits * acc * bn * 128 elements (tiles = grid_x * grid_y);
-// tickets: int32 zeros, one per tile.  Both may be null when splits == 1.
+// `bn` and `splits` as cpi_gemm_tc_plan gives them (splits > 1 only with a power-of-two token tile up to 128).
 extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, int out_dtype, long ldo,
                            const int* out_rows, const float* row_scale, const int* group_offsets, int n_groups,
-                           int T, int N, int K, int mode, int bn, int splits, float* partials, long partials_elems,
-                           int* tickets, long tickets_elems, int* error_flag, cudaStream_t stream) {
+                           int T, int N, int K, int mode, int bn, int splits, int* error_flag,
+                           cudaStream_t stream) {
   if (T == 0 || N == 0) return 0;
   CPI_REQUIRE(T > 0 && N > 0 && K > 0, "gemm_tc: bad sizes T=%d N=%d K=%d", T, N, K);
   CPI_REQUIRE(K % 8 == 0 && ldx % 8 == 0, "gemm_tc: K (%d) and the activation row stride (%ld) must be multiples of 8", K, ldx);
@@ -791,19 +731,13 @@ extern "C" int cpi_gemm_tc(const void* x, long ldx, const void* w, void* out, in
   // token tiles: sum_g ceil(rows_g / bn) <= ceil(T / bn) + min(T, groups)
   dim3 grid((N + tc::BM - 1) / tc::BM, (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0), splits);
   CPI_REQUIRE(grid.y <= 65535, "gemm_tc: too many token tiles (%u)", grid.y);
-  const int cluster_split = cpi_gemm_tc_uses_cluster_split(cap, splits);
-  if (splits > 1 && !cluster_split) {
-    const long live_y = (T + bn - 1) / bn + (n_groups > 0 ? (T < n_groups ? T : n_groups) : 0);
-    const long tiles = (long)grid.x * live_y;
-    CPI_REQUIRE(bn == cap, "gemm_tc: split-K needs a power-of-two token tile, got %d", bn);
-    CPI_REQUIRE(partials && tickets && partials_elems >= tiles * splits * acc * bn * tc::BM && tickets_elems >= tiles,
-                "gemm_tc: split-K scratch is too small (tiles %ld, splits %d)", tiles, splits);
-  }
+  CPI_REQUIRE(splits == 1 || (splits <= 8 && bn == cap && cap <= 128),
+              "gemm_tc: %d splits need a power-of-two token tile of at most 128 rows, got %d", splits, bn);
   // (measured on 16 experts: 5 % faster for the two-accumulator product at 2,048 tokens, slower for the
   // one-accumulator product, whose token rows are the larger operand)
   const int tiles_on_x = mode == tc::kSwiglu && n_groups > 0 && T > 2 * n_groups && splits == 1 && grid.x <= 65535;
   if (tiles_on_x) { const unsigned gx = grid.x; grid.x = grid.y; grid.y = gx; }
-  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, partials, tickets, tiles_on_x, cluster_split, error_flag};
+  tc::Params p{out, ldo, out_rows, row_scale, group_offsets, n_groups, T, bn, N, k_tiles, splits, per, tiles_on_x, error_flag, g_spin_limit, g_tx_extra};
   if (mode == tc::kStore && out_dtype == kBF16) return tc::launch_bn<tc::kStore, __nv_bfloat16>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kStore && out_dtype == kF32) return tc::launch_bn<tc::kStore, float>(cap, mw, mx, p, grid, stream);
   if (mode == tc::kAdd) return tc::launch_bn<tc::kAdd, float>(cap, mw, mx, p, grid, stream);

@@ -627,13 +627,14 @@ extern "C" int cpi_gemm_tc_pair_plan(int T, int N, int K, int swiglu, int n_grou
   }
   if (T < 512) return 0;
   // one pair per two SMs at a time: time ~ waves x (weight rows + half the tile width) per SM
+  const long sm_pairs = cpi::sm_count() / 2 > 0 ? cpi::sm_count() / 2 : 1;
   long best_cost = -1;
   int bn = 0;
   const long pairs_x = N / 256;
   const int w_rows = swiglu ? 256 : 128;
   for (int cand = 256; cand >= 160; cand -= 32) {
     const long pairs = pairs_x * ((T + cand - 1) / cand);
-    const long waves = (pairs + 73) / 74;
+    const long waves = (pairs + sm_pairs - 1) / sm_pairs;
     const long cost = waves * (w_rows + cand / 2 + 16);
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; bn = cand; }
   }

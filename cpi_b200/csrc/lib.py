@@ -137,32 +137,31 @@ def gemm_simt(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=Non
           _p(group_offsets), c_int(n_groups), c_int(M), c_int(N), c_int(K), c_int(mode), c_int(hint), _stream())
 
 
-_tc_scratch = {}      # (device index, stream) -> {"partials", "tickets"}: kernels on different streams may overlap
-_tc_error = {}        # device index -> int32[1]
+_errors = {}          # device index -> int32[2]: [0] a tensor-core kernel gave up a wait, [1] a token id out of range
+
+
+def device_error_flags(device) -> torch.Tensor:
+    """int32[2] on the device that kernels write when something went wrong: word 0 is set to 1 by a tensor-core
+    kernel whose bounded barrier wait ran out, word 1 to 1 + t by the embedding kernel when token t of a step
+    was outside the vocabulary.  The engine reads and clears them."""
+    idx = torch.device(device).index or 0
+    if idx not in _errors:
+        _errors[idx] = torch.zeros(2, dtype=torch.int32, device=device)
+    return _errors[idx]
 
 
 def tc_error_flag(device) -> torch.Tensor:
     """int32[1] that a tensor-core kernel sets when one of its bounded waits ran out."""
-    idx = torch.device(device).index or 0
-    if idx not in _tc_error:
-        _tc_error[idx] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _tc_error[idx]
+    return device_error_flags(device)[0:1]
 
 
-def _tc_state(device):
-    idx = torch.device(device).index or 0
-    key = (idx, torch.cuda.current_stream(device).cuda_stream)
-    st = _tc_scratch.get(key)
-    if st is None:
-        st = {"partials": torch.empty(1 << 22, dtype=torch.float32, device=device),
-              "tickets": torch.zeros(1 << 16, dtype=torch.int32, device=device),
-              "error": tc_error_flag(device)}
-        _tc_scratch[key] = st
-    return st
+def sm_count() -> int:
+    """Multiprocessors of the current CUDA device."""
+    return int(load().cpi_sm_count())
 
 
 def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None, out_rows=None, row_scale=None,
-            group_offsets=None, n_groups=0, rows_per_group_hint=None, force_splits=None, force_bn=None) -> bool:
+            group_offsets=None, n_groups=0, rows_per_group_hint=None) -> bool:
     """The tcgen05 kernel for out[m, n] (+)= sum_k a[m, k] w[g(m)][n, k] in bfloat16 (see gemm_tc.cu).
 
     Returns False, having launched nothing, when the call is outside what the kernel takes (a row
@@ -194,39 +193,26 @@ def gemm_tc(a, w, out, mode=MODE_STORE, *, n_out=None, m_rows=None, a_rows=None,
     load().cpi_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(n_groups if grouped else 0),
                             c_int(int(mode == MODE_SWIGLU)), ctypes.byref(bn), ctypes.byref(splits),
                             ctypes.byref(live_y))
-    st = _tc_state(a.device)
-    if force_bn is not None:                 # tuning aid: override the planner
-        bn.value = force_bn
-        live_y.value = -(-T // force_bn) + (min(T, n_groups) if grouped else 0)
-    sp = splits.value if force_splits is None else force_splits
-    cap = 16
-    while cap < bn.value:
-        cap *= 2
-    if sp > 1 and not load().cpi_gemm_tc_uses_cluster_split(c_int(cap), c_int(sp)):
-        tiles = -(-N // 128) * live_y.value
-        need = tiles * sp * (2 if mode == MODE_SWIGLU else 1) * bn.value * 128
-        if need > (1 << 26):                 # keep the scratch modest: fewer splits instead
-            sp = 1
-        else:
-            global scratch_generation
-            if st["partials"].numel() < need:
-                st["partials"] = torch.empty(need, dtype=torch.float32, device=a.device)
-                scratch_generation += 1
-            if st["tickets"].numel() < tiles:
-                st["tickets"] = torch.zeros(tiles, dtype=torch.int32, device=a.device)
-                scratch_generation += 1
     _call("cpi_gemm_tc", _p(a), c_long(a.stride(0)), _p(w), _p(out), c_int(dtype_code(out.dtype)),
           c_long(out.stride(0)), _p(out_rows), _p(row_scale), _p(group_offsets), c_int(n_groups if grouped else 0),
-          c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn.value), c_int(sp), _p(st["partials"]),
-          c_long(st["partials"].numel()), _p(st["tickets"]), c_long(st["tickets"].numel()), _p(st["error"]),
-          _stream())
+          c_int(T), c_int(N), c_int(K), c_int(mode), c_int(bn.value), c_int(splits.value),
+          _p(tc_error_flag(a.device)), _stream())
     return True
 
 
-def gemm_cluster_split(on: bool) -> None:
-    """Split-K of `gemm_tc` merges through a cluster's shared memory (default) or, when off, through tickets
-    and global scratch (the older path, kept for comparison)."""
-    load().cpi_gemm_tc_cluster_split(c_int(int(on)))
+def gemm_tc_plan(T: int, N: int, K: int, n_groups: int = 0, swiglu: bool = False):
+    """(token rows per tile, k splits) that `gemm_tc` uses for a product of these sizes on this device."""
+    bn, splits, live_y = c_int(), c_int(), c_int()
+    load().cpi_gemm_tc_plan(c_int(T), c_int(N), c_int(K), c_int(n_groups), c_int(int(swiglu)), ctypes.byref(bn),
+                            ctypes.byref(splits), ctypes.byref(live_y))
+    return bn.value, splits.value
+
+
+def gemm_tc_wait_probe(spin_limit: int = 0, tx_extra: int = 0) -> None:
+    """For the test of the give-up path of `gemm_tc`: launches from now on poll each barrier at most
+    `spin_limit` times and expect `tx_extra` bytes more per stage than their loads bring, so that the wait runs
+    out, the kernel raises the error flag and returns.  (0, 0) puts the ordinary values back."""
+    load().cpi_gemm_tc_wait_probe(c_int(int(spin_limit)), c_int(int(tx_extra)))
 
 
 def gemm_pair_persistent(mode) -> None:

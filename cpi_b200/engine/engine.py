@@ -73,6 +73,12 @@ class Engine:
         self.graph_kernel_launches = 0       # kernels run by graph replays (they are not host launches)
         self._routing_capture = False
         self._phase_timer = None
+        # What kernels flag on the device (a tensor-core kernel that gave up a wait, a token outside the
+        # vocabulary) is copied to the host after every step, without waiting for it; the copy is looked at
+        # when a later step starts and whenever the caller has synchronised anyway (`check_device_errors`).
+        self._err_dev = K.device_error_flags(self.device)
+        self._err_host = torch.zeros(2, dtype=torch.int32, pin_memory=True)
+        self._err_event = None
 
     # ---- construction ----------------------------------------------------------------------------
     @classmethod
@@ -170,6 +176,7 @@ class Engine:
     def _run(self, slots, toks, wants, device_tokens=None) -> torch.Tensor:
         """Runs one piece; the returned logits live in a buffer that the next step overwrites."""
         n_new = [len(t) for t in toks]
+        self._raise_if_flagged(wait=False)          # what the step before last left, if its copy has arrived
         starts = self.cache.prepare_step(slots, n_new)
         decode = max(n_new) == 1
         if self._phase_timer is not None:
@@ -183,6 +190,9 @@ class Engine:
             logits = self.model.run(batch, self.cache)
         self.cache.commit_step(slots, n_new)
         self.steps_run += 1
+        self._err_host.copy_(self._err_dev, non_blocking=True)
+        self._err_event = torch.cuda.Event()
+        self._err_event.record()
         return logits
 
     def _run_decode_graph(self, slots, starts, toks, wants, device_tokens=None) -> torch.Tensor:
@@ -243,12 +253,27 @@ class Engine:
         phases.install(self._phase_timer)
         return self._phase_timer
 
+    def _raise_if_flagged(self, wait: bool) -> None:
+        ev = self._err_event
+        if ev is None or (not wait and not ev.query()):
+            return
+        ev.synchronize()
+        self._err_event = None
+        gave_up, token = int(self._err_host[0]), int(self._err_host[1])
+        if not (gave_up or token):
+            return
+        self._err_dev.zero_()
+        self._err_host.zero_()
+        if gave_up:
+            raise RuntimeError("a tensor-core kernel gave up waiting on one of its barriers; the results of the "
+                               "steps since the last check are invalid")
+        raise RuntimeError(f"embedding: token {token - 1} of a step was outside the vocabulary")
+
     def check_device_errors(self) -> None:
-        """Raises if a kernel flagged a bad input since the last check (synchronises)."""
-        if int(K.tc_error_flag(self.device).item()):
-            K.tc_error_flag(self.device).zero_()
-            raise RuntimeError("a tensor-core kernel gave up waiting on one of its barriers; results are invalid")
-        code = int(self.model.err_flag.item())
-        if code:
-            self.model.err_flag.zero_()
-            raise RuntimeError(f"embedding: token {code - 1} of a step was outside the vocabulary")
+        """Raises if a kernel flagged a bad input or gave up a wait since the last check.  Waits for the device:
+        `generate`, `Model.step` and the command lines call it where they have the results on the host anyway;
+        between such points every step looks at what the step before it left, without waiting."""
+        self._err_host.copy_(self._err_dev, non_blocking=True)
+        self._err_event = torch.cuda.Event()
+        self._err_event.record()
+        self._raise_if_flagged(wait=True)

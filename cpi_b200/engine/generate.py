@@ -115,9 +115,12 @@ class Generator:
                                page_size=cache.page_size, max_seq_len=self.max_context)
         self.stats = GenerationStats()
         results: list = [None] * len(reqs)
+        check = getattr(self.engine, "check_device_errors", None)
         for batch in batches:
             self._run_batch(batch, reqs, results, on_token)
             self.stats.batches += 1
+            if check is not None:       # the batch's tokens are on the host: what kernels flagged meanwhile is too
+                check()
         return results
 
     def _run_batch(self, idxs, reqs, results, on_token):

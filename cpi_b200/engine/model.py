@@ -93,7 +93,9 @@ class DecoderModel:
         for layer in self.layers:
             for p in layer.parts():
                 p.load(source, dev)
-        self.err_flag = torch.zeros(1, dtype=torch.int32, device=dev)
+        # the word of the device's error flags that the embedding kernel sets for a token outside the table
+        self.err_flag = K.device_error_flags(dev)[1:2] if torch.device(dev).type == "cuda" \
+            else torch.zeros(1, dtype=torch.int32, device=dev)
 
     # ---- cache needs -----------------------------------------------------------------------------
     def cache_requirements(self):

@@ -114,7 +114,7 @@ class AttentionMixer(Mixer):
             if self.window_kind != "full":
                 longest = min(longest, self.window_size + page_size)
             pages = -(-longest // page_size)
-            base, slots = batch.n_tokens * self.nkv, 3 * 148       # three blocks fit an SM
+            base, slots = batch.n_tokens * self.nkv, 3 * K.sm_count()       # three blocks fit an SM
             if base <= slots:
                 want = slots // base                                # one full wave and no more
             else:

@@ -146,3 +146,39 @@ def run_batched(rp, batches):
         for rid, (t, p) in reqs.items():
             positions[rid] = list(range(p - 1, len(t)))
     return positions
+
+
+class TraceOutput:
+    """What `bin/trace_run` wrote into a folder, in the shape `compare_with_plain` reads: logits per (request,
+    position) and, when the tool dumped them, expert choices per (request, layer, position)."""
+
+    def __init__(self, out_dir):
+        import json
+        import os
+        import numpy as np
+        with open(os.path.join(out_dir, "index.json")) as f:
+            idx = json.load(f)
+        V, layers, k = idx["vocab_size"], idx["routed_layers"], idx["top_k"]
+        self.logits, self.routing, self.steps = {}, {}, idx["steps"]
+        for st in idx["steps"]:
+            rows = sum(len(e["want"]) for e in st["entries"])
+            assert (st["file"] is not None) == (rows > 0)
+            if rows:
+                arr = np.fromfile(os.path.join(out_dir, st["file"]), dtype="<f4")
+                assert arr.size == rows * V, f"step {st['step']}: {arr.size} floats for {rows} rows"
+                lg = torch.from_numpy(arr.reshape(rows, V).copy())
+                r = 0
+                for e in st["entries"]:
+                    for w in e["want"]:
+                        self.logits.setdefault(e["id"], {})[e["start"] + w] = lg[r]
+                        r += 1
+            if st["routing"]:
+                T = sum(e["tokens"] for e in st["entries"])
+                ch = np.fromfile(os.path.join(out_dir, st["routing"]), dtype="<i4").reshape(len(layers), T, k)
+                t = 0
+                for e in st["entries"]:
+                    for i in range(e["tokens"]):
+                        for li, layer in enumerate(layers):
+                            self.routing.setdefault(e["id"], {}).setdefault(layer, {})[e["start"] + i] = \
+                                ch[li, t + i].tolist()
+                    t += e["tokens"]

@@ -416,3 +416,37 @@ def test_run_llama4_prompt_helpers():
     assert text == ("<|begin_of_text|><|header_start|>system<|header_end|>\n\nBe brief.<|eot|>"
                     "<|header_start|>user<|header_end|>\n\nHi<|eot|><|header_start|>assistant<|header_end|>\n\n")
     assert cut_at_stop([4, 5, 9, 6, 9], {9}) == [4, 5] and cut_at_stop([4, 5], {9}) == [4, 5] and cut_at_stop([], {1}) == []
+
+
+def test_replay_schedules_feed_every_token_once_and_in_order():
+    """The three schedules of the replay tool, on the host: every request's tokens come once and in order, a
+    step's requests all start or all go on by one token, a request ends with its last token, and the cache
+    figure is the most that is live at a time."""
+    from cpi_b200.engine import replay
+    reqs = {"a": list(range(100, 170)), "b": [7], "c": list(range(33)), "d": list(range(200, 264)), "e": [1, 2]}
+    for name, steps in (("whole", list(replay.schedule_whole(reqs))), ("tail", list(replay.schedule_tail(reqs, 32))),
+                        ("batched", list(replay.schedule_batched(reqs, 2, 32)))):
+        fed = {rid: [] for rid in reqs}
+        ended, live = [], set()
+        assert [s["step"] for s in steps] == list(range(len(steps)))
+        for s in steps:
+            kinds = set()
+            for e in s["entries"]:
+                assert e["id"] not in ended
+                kinds.add("start" if not fed[e["id"]] else "more")
+                if fed[e["id"]]:
+                    assert len(e["tokens"]) == 1
+                assert all(0 <= w < len(e["tokens"]) for w in e["want"])
+                fed[e["id"]] += e["tokens"]
+                live.add(e["id"])
+            assert len(kinds) == 1, f"{name}: a step mixes starting and continuing requests"
+            for rid in s["end"]:
+                assert fed[rid] == reqs[rid], f"{name}: {rid} ended before its last token"
+                ended.append(rid)
+                live.discard(rid)
+            if name == "batched":
+                assert len(live) <= 2
+        assert fed == reqs and sorted(ended) == sorted(reqs) and not live
+    assert replay.tokens_needed(replay.schedule_whole(reqs)) == 128
+    assert replay.tokens_needed(replay.schedule_batched(reqs, 2, 32)) == 128        # a grows to two pages after b has gone
+    assert replay.tokens_needed(replay.schedule_batched(reqs, 5, 32)) == 5 * 64     # all five start with a page each

@@ -266,7 +266,7 @@ def test_trace_run_program(dirs, tmp_path):
                        capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stderr
     assert r.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
-    assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "3.f32"]
+    assert sorted(os.listdir(out)) == ["0.f32", "1.f32", "3.f32", "index.json"]
     la, lb = P.forward(c, W, a).numpy(), P.forward(c, W, b).numpy()
     s0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, 1000)
     s1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(1, 1000)

@@ -237,37 +237,33 @@ def test_gemm_tensor_core_grouped(counts, bn_rows, mode):
     assert float((out.float() - ref).abs().max()) <= tol
 
 
-@pytest.mark.parametrize("cluster", [True, False])
-@pytest.mark.parametrize("T,N,Kd,splits", [(5, 384, 1024, 2), (16, 200, 2048, 8), (30, 256, 1280, 5), (64, 640, 1536, 3),
-                                           (100, 384, 2048, 7), (128, 128, 4096, 8)])
+@pytest.mark.parametrize("T,N,Kd", [(5, 384, 1024), (16, 200, 2048), (30, 256, 1280), (64, 640, 1536),
+                                    (100, 384, 2048), (128, 128, 4096)])
 @pytest.mark.parametrize("mode", [0, 1, 2])
-def test_gemm_tensor_core_split_k_both_merges(T, N, Kd, splits, mode, cluster):
-    """Split-K merged through a cluster's shared memory and through tickets: same product, and the same
-    bits from one launch to the next."""
+def test_gemm_tensor_core_split_k(T, N, Kd, mode):
+    """Products with so few tiles that the k range is cut (the splits of a tile are a cluster and meet in its
+    shared memory): the right product, and the same bits from one launch to the next."""
     a = rnd(T, Kd, dtype=torch.bfloat16)
     w = rnd(2 * N if mode == 2 else N, Kd, dtype=torch.bfloat16, seed=2, scale=Kd ** -0.5)
     scale = rnd(T, seed=5).abs()
     odt = torch.float32 if mode == 1 else torch.bfloat16
-    K().gemm_cluster_split(cluster)
-    try:
-        outs = []
-        for _ in range(3):
-            out = rnd(T, N, dtype=odt, seed=3)
-            ref = ref_gemm(a, w, mode, out.float().clone(), scale)
-            assert K().gemm_tc(a, w, out, mode, row_scale=scale, force_splits=splits)
-            torch.cuda.synchronize()
-            assert int(K().tc_error_flag(DEV)) == 0
-            outs.append(out)
-    finally:
-        K().gemm_cluster_split(True)
+    bn, splits = K().gemm_tc_plan(T, N, Kd, 0, mode == 2)
+    assert splits > 1, "the case is meant to split k"
+    outs = []
+    for _ in range(3):
+        out = rnd(T, N, dtype=odt, seed=3)
+        ref = ref_gemm(a, w, mode, out.float().clone(), scale)
+        assert K().gemm_tc(a, w, out, mode, row_scale=scale)
+        torch.cuda.synchronize()
+        assert int(K().tc_error_flag(DEV)) == 0
+        outs.append(out)
     tol = (2e-5 if odt == torch.float32 else 1e-2) * max(1.0, float(ref.abs().max()))
     assert float((outs[0].float() - ref).abs().max()) <= tol
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 
-@pytest.mark.parametrize("cluster", [True, False])
-def test_gemm_tensor_core_grouped_split_k(cluster):
-    """One token per expert (a decode step of batch 3 over 6 experts), the k range cut in 4."""
+def test_gemm_tensor_core_grouped_split_k():
+    """One token per expert (a decode step of batch 3 over 6 experts), the k range cut."""
     counts, N, Kd = [1, 0, 0, 1, 0, 1], 256, 2048
     G, M = len(counts), sum(counts)
     w = rnd(G, 2 * N, Kd, dtype=torch.bfloat16, seed=1, scale=Kd ** -0.5)
@@ -277,14 +273,46 @@ def test_gemm_tensor_core_grouped_split_k(cluster):
     acc = torch.einsum("mk,mnk->mn", a.float(), w.float()[grp])
     ref = acc[:, :N] / (1 + torch.exp(-acc[:, :N])) * acc[:, N:]
     out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
-    K().gemm_cluster_split(cluster)
-    try:
-        assert K().gemm_tc(a, w, out, 2, m_rows=M, group_offsets=offs, n_groups=G, force_splits=4)
-        torch.cuda.synchronize()
-    finally:
-        K().gemm_cluster_split(True)
+    assert K().gemm_tc_plan(M, N, Kd, G, True)[1] > 1
+    assert K().gemm_tc(a, w, out, 2, m_rows=M, group_offsets=offs, n_groups=G)
+    torch.cuda.synchronize()
     assert int(K().tc_error_flag(DEV)) == 0
     assert float((out.float() - ref).abs().max()) <= 1e-2 * max(1.0, float(ref.abs().max()))
+
+
+def test_a_wait_that_runs_out_raises_the_flag_and_the_next_launch_is_right():
+    """A tensor-core kernel never waits without a limit.  Here one small product is launched with a poll limit
+    of a few thousand and a barrier that expects 64 bytes more than its loads bring, so that the wait runs out:
+    the kernel must come back by itself with the error word set (nothing faults or hangs: the loads land, the
+    tensor memory is freed), `Engine.check_device_errors` must raise and clear it, and the same product launched
+    again in the ordinary way must be right."""
+    from cpi_b200.engine import Engine
+    T, N, Kd = 16, 128, 256
+    a = rnd(T, Kd, dtype=torch.bfloat16)
+    w = rnd(N, Kd, dtype=torch.bfloat16, seed=2, scale=Kd ** -0.5)
+    out = torch.zeros(T, N, dtype=torch.bfloat16, device=DEV)
+    assert K().gemm_tc_plan(T, N, Kd)[1] == 1
+    torch.cuda.synchronize()
+    assert int(K().tc_error_flag(DEV)) == 0
+    K().gemm_tc_wait_probe(4096, 64)
+    try:
+        assert K().gemm_tc(a, w, out, 0)
+        torch.cuda.synchronize()
+    finally:
+        K().gemm_tc_wait_probe(0, 0)
+    assert int(K().tc_error_flag(DEV)) == 1
+    import tiny
+    e = Engine.from_random(tiny.config("A"), seed=0, dtype="bfloat16", max_tokens=64)
+    with pytest.raises(RuntimeError, match="gave up waiting"):
+        e.check_device_errors()
+    e.check_device_errors()                                   # cleared
+    assert int(K().tc_error_flag(DEV)) == 0
+    out.zero_()
+    assert K().gemm_tc(a, w, out, 0)
+    torch.cuda.synchronize()
+    ref = ref_gemm(a, w, 0, out.float().clone(), None)
+    assert float((out.float() - ref).abs().max()) <= 1e-2 * max(1.0, float(ref.abs().max()))
+    assert int(K().tc_error_flag(DEV)) == 0
 
 
 def test_gemm_tensor_core_split_k_is_deterministic():
