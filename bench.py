@@ -3,15 +3,28 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--batch 8] [--context 4096]
     python bench.py --workload maverick4 | long131k      (two further workloads, a JSON line of their own)
 
+    python bench.py --workload cpu_baseline [--reference-root DIR]      (no GPU needed)
+
 Prints ONE JSON line.  A "step" is one decode step of the whole batch.  `value` is decoded tokens per
 second, timed on the device with CUDA events around exactly K engine steps (host token ids in, arg-max
 on the device); `e2e` is the same through the Python entry point (`Model.generate`), with every
-step's token ids copied from pinned host memory and the sampled ids read back.  Between timed
-iterations nothing is flushed: one decode step reads tens of GB of weights, far more than the L2 holds.
+step's token ids copied from pinned host memory and the sampled ids read back; `points` and `points_e2e`
+give both at batch 1 and 64.  Between timed iterations nothing is flushed: one decode step reads tens of
+GB of weights, far more than the L2 holds.  `roofline` divides the bytes the timed steps had to read by
+their time: every weight a step uses once -- with the experts that THOSE steps touched, counted by running
+the same prompts and token feed once more, untimed, with the routing recorded -- and the cache of the live
+requests.  `prefill` is one prompt of 2,048 tokens, `prefill_b8` eight of them in one call; `frac` divides
+the step's flops by its time and the burst bf16 peak, `frac_per_kernel` divides the time the step would
+take with every kernel at its own bound (contractions at the tensor peak, but the routed experts at the
+larger of that and the time to read their weights once per piece) by the measured time.
 For N > 1 GPUs it prints one line that says the library is single-GPU and exits with 2.
 `phases` holds device milliseconds per phase of one prefill of 2,048 tokens and of one decode step, taken
 after everything else with the steps run eagerly on one stream (so their sum exceeds the step times above).
 
+`--workload cpu_baseline` times, on the host's cores, the reference's own unmodified CPU engine (compiled from
+DIR with tests/golden/ref_harness.cpp, token by token as its generate loop runs it,
+src/engine/llama4_cpu_engine.cpp:516-566) and this repository's plain implementation at the two tiny
+configurations that lie inside what that engine computes.
 `--workload maverick4`: 4 layers with Llama4 Maverick's sizes (dense and 128-expert layers alternate), 32
 prompts of 64 to 2,048 tokens, 128 new tokens each.  `--workload long131k`: 12 Scout layers, one prompt of
 131,072 tokens (prefilled in pieces), 256 new tokens.  Both run through `Model.generate` and are timed with
@@ -139,6 +152,28 @@ def prefill_flops(c, layers, n_tokens) -> float:
     return layers * per_token * n_tokens + attn + 2.0 * V * H
 
 
+def prefill_bound_ms(c, layers, n_tokens, n_seqs, pieces, pk) -> float:
+    """Milliseconds a prefill of n_seqs prompts of n_tokens would take with every kernel at its own bound: the
+    contractions at the tensor peak, except the routed experts, which cannot be faster than reading every
+    expert's weights once per piece of the step; the head reads its matrix once."""
+    H, Q, KV = c["hidden_size"], c["num_attention_heads"] * c["head_dim"], c["num_key_value_heads"] * c["head_dim"]
+    I, V, K, E = c["intermediate_size"], c["vocab_size"], c["num_experts_per_tok"], c["num_local_experts"]
+    T = n_tokens * n_seqs
+    peak, hbm = pk["bf16_tflops"] * 1e12, pk["hbm_gbs"] * 1e9
+    dense = 2.0 * T * ((Q + 2 * KV) * H + H * Q + 3 * I * H + E * H)
+    routed_flops = 2.0 * T * K * 3 * I * H
+    routed_bytes = 2.0 * min(E, T * K) * 3 * I * H * pieces
+    attn = (prefill_flops(c, 1, n_tokens) - 2.0 * V * H - prefill_flops_linear(c, n_tokens)) * n_seqs
+    per_layer = (dense + attn) / peak + max(routed_flops / peak, routed_bytes / hbm)
+    return 1e3 * (layers * per_layer + 2.0 * V * H / hbm)
+
+
+def prefill_flops_linear(c, n_tokens) -> float:
+    H, Q, KV = c["hidden_size"], c["num_attention_heads"] * c["head_dim"], c["num_key_value_heads"] * c["head_dim"]
+    I, K = c["intermediate_size"], c["num_experts_per_tok"]
+    return 2.0 * ((Q + 2 * KV) * H + H * Q + 3 * I * H * (1 + K) + c["num_local_experts"] * H) * n_tokens
+
+
 def run(args) -> dict:
     import torch
     from cpi_b200.api import Model
@@ -163,84 +198,124 @@ def run(args) -> dict:
 
     out_tok = torch.empty(max_b, dtype=torch.int32, device="cuda:0")
 
-    def timed_decode(batch, n_steps, n_warm):
-        """Prefill `batch` prompts so that the timed steps end at the full context; device-timed."""
+    def timed_decode(batch, n_steps, n_warm, count_experts=True):
+        """Prefill `batch` prompts so that the timed steps end at the full context; device-timed.  Returns
+        (milliseconds, kernels launched, bytes the timed steps had to read, experts touched per layer and step
+        as (mean, least, most))."""
         plen = ctx - (n_steps + n_warm) - 1
-        slots = [eng.acquire_slot() for _ in range(batch)]
-        eng.step([StepEntry(s, toks(plen), []) for s in slots])
-        feed = [toks(batch) for _ in range(n_steps + n_warm + 1)]
+        prompts = [toks(plen) for _ in range(batch)]
+        feed = [toks(batch) for _ in range(n_steps + n_warm)]
 
-        def one(i):
+        def start():
+            slots = [eng.acquire_slot() for _ in range(batch)]
+            eng.step([StepEntry(s, p, []) for s, p in zip(slots, prompts)])
+            return slots
+
+        def one(slots, i):
             lg = eng.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
             K.argmax(lg, out_tok[:batch])
 
+        slots = start()
         for i in range(n_warm):
-            one(i)
+            one(slots, i)
         torch.cuda.synchronize()
         l0 = K.kernel_launches() + eng.graph_kernel_launches
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(n_warm, n_warm + n_steps):
-            one(i)
+            one(slots, i)
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1)
         launches = K.kernel_launches() + eng.graph_kernel_launches - l0
-        cap = eng.capture_routing(True)          # one more, untimed, step: how many experts a step touches
-        one(n_warm + n_steps)
-        torch.cuda.synchronize()
-        touched = [len(set(lst[0].flatten().tolist())) for lst in cap.values() if lst]
-        eng.capture_routing(False)
         for s in slots:
             eng.release_slot(s)
-        return ms, launches, (sum(touched) / len(touched) if touched else 0.0)
+        # the same prompts and the same feed once more, untimed, with the routing recorded: the experts that
+        # each of the timed steps touched in each layer
+        per_step = []
+        if count_experts:
+            cap = eng.capture_routing(True)
+            slots = start()
+            for i in range(n_warm + n_steps):
+                for lst in cap.values():
+                    lst.clear()
+                one(slots, i)
+                if i >= n_warm:
+                    torch.cuda.synchronize()
+                    per_step.append([len(set(lst[0].flatten().tolist())) for lst in cap.values() if lst])
+            eng.capture_routing(False)
+            for s in slots:
+                eng.release_slot(s)
+        else:
+            per_step = [[min(batch * cfg["num_experts_per_tok"], cfg["num_local_experts"])] * args.layers] * n_steps
+        means = [sum(x) / len(x) for x in per_step]
+        total_bytes = sum(decode_step_bytes(cfg, args.layers, batch, plen + n_warm + k + 1, m)
+                          for k, m in enumerate(means))
+        touched = (sum(means) / len(means), min(min(x) for x in per_step), max(max(x) for x in per_step))
+        return ms, launches, total_bytes, touched
 
-    # ---- prefill of 2,048 tokens, one sequence ------------------------------------------------------
+    def e2e_decode(batch, n_steps, n_warm):
+        """The same through `Model.generate`: host token ids in, sampled ids read back every step."""
+        plen = ctx - (n_steps + n_warm) - 1
+        prompts = [toks(plen) for _ in range(batch)]
+        # warm-up: the same batch for `n_warm` steps (it also captures this batch size's decode graph)
+        model.generate(prompts, max_new=n_warm + 1, temperature=0.0, stop_ids=[])
+        model.generate(prompts, max_new=n_steps + 1, temperature=0.0, stop_ids=[])
+        st = model.stats()
+        return batch * st.decode_steps / (st.decode_ms / 1e3)
+
+    def timed_prefill(n_seqs, reps):
+        times = []
+        for r in range(reps + 1):                            # the first pass warms up
+            slots = [eng.acquire_slot() for _ in range(n_seqs)]
+            entries = [StepEntry(x, toks(pre_n), [pre_n - 1]) for x in slots]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            eng.step(entries)
+            e1.record()
+            torch.cuda.synchronize()
+            if r:
+                times.append(e0.elapsed_time(e1))
+            for x in slots:
+                eng.release_slot(x)
+        return sorted(times)[len(times) // 2]
+
+    def prefill_record(n_seqs, ms):
+        pieces = -(-n_seqs * pre_n // eng.max_step_tokens)
+        flops = n_seqs * (prefill_flops(cfg, args.layers, pre_n) - 2.0 * V * cfg["hidden_size"]) \
+            + 2.0 * V * cfg["hidden_size"] * n_seqs
+        return {"value": round(n_seqs * pre_n / (ms / 1e3), 1), "tokens": n_seqs * pre_n, "ms": round(ms, 3),
+                "frac": round(flops / (ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                "frac_per_kernel": round(prefill_bound_ms(cfg, args.layers, pre_n, n_seqs, pieces, pk) / ms, 4),
+                "peak": f"bf16_tflops (burst, {pk['source']})", "tokens_per_piece": min(n_seqs * pre_n, eng.max_step_tokens)}
+
+    # ---- prefill of 2,048 tokens: one sequence, and eight in one call ---------------------------------------
     pre_n = 2048
-    s = eng.acquire_slot()
-    eng.step([StepEntry(s, toks(pre_n), [pre_n - 1])])
-    eng.release_slot(s)
-    torch.cuda.synchronize()
-    pre_ms = []
-    for _ in range(3):
-        s = eng.acquire_slot()
-        p = toks(pre_n)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        eng.step([StepEntry(s, p, [pre_n - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        pre_ms.append(e0.elapsed_time(e1))
-        eng.release_slot(s)
-    pre = sorted(pre_ms)[len(pre_ms) // 2]
-    pf = prefill_flops(cfg, args.layers, pre_n)
+    pre = timed_prefill(1, 3)
+    pre8 = None if args.skip_points else timed_prefill(8, 2)
 
     # ---- the headline: decode at the given batch ----------------------------------------------------
     clocks = ClockSampler()
     clocks.start()
-    ms, launches, touched = timed_decode(B, steps, warm)
+    ms, launches, step_bytes, touched = timed_decode(B, steps, warm)
     clock_rec = clocks.stop()
     value = B * steps / (ms / 1e3)
-    step_bytes = decode_step_bytes(cfg, args.layers, B, ctx - steps / 2, touched)
-    achieved = step_bytes / (ms / steps / 1e3) / 1e9
+    achieved = step_bytes / (ms / 1e3) / 1e9
 
     # ---- end to end through the Python entry point --------------------------------------------------
-    plen = ctx - (steps + warm) - 1
-    prompts = [toks(plen) for _ in range(B)]
-    # warm-up: the same batch for `warm` steps (it also captures this batch size's decode graph), then the timed run
-    model.generate(prompts, max_new=warm + 1, temperature=0.0, stop_ids=[])
-    model.generate(prompts, max_new=steps + 1, temperature=0.0, stop_ids=[])
-    st = model.stats()
-    e2e_value = B * st.decode_steps / (st.decode_ms / 1e3)
+    e2e_value = e2e_decode(B, steps, warm)
     h2d = eng.stager.bytes_staged
     d2h = B * 4
 
-    points = {}
+    points, points_e2e, points_frac = {}, {}, {}
     if not args.skip_points:
         for b in (1, 64):
             k = max(4, steps if b == 1 else steps // 2)          # batch-1 steps are short: time more of them
-            m, _, _ = timed_decode(b, k, max(3, warm) + (4 if b == 1 else 0))
+            w = max(3, warm) + (4 if b == 1 else 0)
+            m, _, nbytes, _ = timed_decode(b, k, w, count_experts=b > 1)
             points[f"decode_b{b}"] = round(b * k / (m / 1e3), 2)
+            points_frac[f"decode_b{b}"] = round(nbytes / (m / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+            points_e2e[f"decode_b{b}"] = round(e2e_decode(b, k, w), 2)
 
     # ---- where the time goes: phases of one prefill and of one decode step (eager, one stream) ---------
     timer = eng.profile_phases(True)
@@ -277,14 +352,18 @@ def run(args) -> dict:
                    "chunk": cfg["attention_chunk_size"], "nope_interval": cfg["nope_layer_interval"],
                    "global_batch": B, "seq_len": ctx, "decode_context_end": ctx, "parallelism": "single-gpu",
                    "l2": "inputs larger than L2 (a step reads > 10 GB of weights)",
-                   "experts_touched_per_layer": round(touched, 2)},
+                   "experts_touched_per_layer": round(touched[0], 2)},
         "e2e": {"value": round(e2e_value, 2), "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
-        "prefill": {"value": round(pre_n / (pre / 1e3), 1), "tokens": pre_n, "ms": round(pre, 3),
-                    "frac": round(pf / (pre / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "prefill": prefill_record(1, pre),
+        "prefill_b8": None if pre8 is None else prefill_record(8, pre8),
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"],
+                     "experts_touched": {"mean": round(touched[0], 2), "least": touched[1], "most": touched[2],
+                                         "counted": "over the timed steps, in an untimed replay of the same feed"}},
         "points": points,
+        "points_e2e": points_e2e,
+        "points_roofline_frac": points_frac,
         "phases": phases,
         "clocks": clock_rec,
         "build_s": round(build_s, 1),
@@ -340,6 +419,87 @@ def run_workload(args) -> dict:
             "clocks": clock_rec}
 
 
+def run_cpu_baseline(args) -> dict:
+    """Tokens per second on the host's cores at the two tiny configurations inside what the reference's engine
+    computes: the reference's own CPU engine (unmodified, compiled with tests/golden/ref_harness.cpp; one
+    forward_token call per token, as its generate loop does) and this repository's plain implementation (whole
+    sequences, one forward per generated token as its greedy loop does, and one forward over all positions)."""
+    import re
+    import tempfile
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama4 as P
+    import tiny
+    golden = os.path.join(ROOT, "tests", "golden")
+    ref = args.reference_root
+    out = {"metric": "CPU baseline: tok/s at the tiny reference-compatible configurations (float32)", "unit": "tok/s",
+           "impl": "cpu_baseline", "n_gpus": 0, "cpu_threads": os.cpu_count(), "points": {}}
+    exe = None
+    if ref and os.path.isdir(os.path.join(ref, "src", "engine")):
+        work = tempfile.mkdtemp(prefix="cpi_cpu_baseline_")
+        exe = os.path.join(work, "ref_harness")
+        srcs = [os.path.join(ref, p) for p in ("src/engine/llama4_cpu_engine.cpp", "src/model/safetensors_loader.cpp",
+                                               "src/platform/mmap_file.cpp")]
+        cuda_inc = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+        r = subprocess.run(["g++", "-std=c++20", "-O2", "-mavx2", "-mfma", "-fopenmp", f"-I{ref}/include",
+                            f"-I{cuda_inc}", os.path.join(golden, "ref_harness.cpp"), *srcs, "-o", exe],
+                           capture_output=True, text=True)
+        if r.returncode != 0:
+            out["reference_cpu_engine"] = "does not compile here: " + r.stderr.strip().splitlines()[-1][:200]
+            exe = None
+    else:
+        out["reference_cpu_engine"] = "no checkout given (--reference-root DIR)"
+    for name, n_tokens in (("R", 48), ("R2", 70)):
+        d = tiny.make_model_dir(name)
+        c = tiny.config(name)["text_config"]
+        rs = c["rope_scaling"]
+        tokens = tiny.random_tokens(n_tokens, c["vocab_size"], 77)
+        point = {"tokens": n_tokens, "layers": c["num_hidden_layers"], "hidden": c["hidden_size"]}
+        if exe:
+            argv = [exe, d, os.path.join(os.path.dirname(exe), f"logits_{name}.f32"), c["vocab_size"],
+                    c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
+                    c["num_hidden_layers"], c["num_local_experts"], c["intermediate_size"], c["intermediate_size"],
+                    rs["original_max_position_embeddings"], c["rope_theta"], rs["factor"], rs["low_freq_factor"],
+                    rs["high_freq_factor"], *tokens]
+            best = None
+            for _ in range(3):
+                r = subprocess.run([str(a) for a in argv], capture_output=True, text=True, check=True)
+                ms = float(re.search(r"forward_ms=([0-9.]+)", r.stderr).group(1))
+                best = ms if best is None else min(best, ms)
+            point["reference_cpu_engine_tok_s"] = round(n_tokens / (best / 1e3), 1)
+        pc, W = P.read_config(d), P.read_weights(d)
+        P.forward(pc, W, tokens)
+        t0 = time.perf_counter()
+        P.forward(pc, W, tokens)
+        point["plain_all_positions_tok_s"] = round(n_tokens / (time.perf_counter() - t0), 1)
+        t0 = time.perf_counter()
+        P.greedy_generate(pc, W, tokens[:n_tokens - 8], 8)
+        point["plain_greedy_tok_s"] = round(8 / (time.perf_counter() - t0), 2)
+        try:
+            import torch
+            gpu = torch.cuda.is_available()
+        except ImportError:
+            gpu = False
+        if gpu:                                     # the same model through this library, for scale
+            from cpi_b200.api import Model
+            for dtype in ("float32", "bfloat16"):
+                m = Model.load(d, dtype=dtype, max_batch=1, max_context=256)
+                m.generate([tokens[:n_tokens - 8]], max_new=64, temperature=0.0, stop_ids=[])
+                m.generate([tokens[:n_tokens - 8]], max_new=64, temperature=0.0, stop_ids=[])
+                st = m.stats()
+                point[f"cpi_b200_{dtype}_decode_tok_s"] = round(st.decode_steps / (st.decode_ms / 1e3), 1)
+        out["points"][name] = point
+    return out
+
+
+def reference_arm_reason() -> str:
+    """Why `--impl reference` has nothing to run, as found on this image (one line)."""
+    return ("kurulav1/cpi is a CMake C++/CUDA project (no setup.py or pyproject.toml, so pip has nothing to install); "
+            "its stock CMake build stops here at the first C++ file: CMakeLists.txt:40 passes '-Wall -Wextra -Wpedantic' "
+            "as one unquoted generator expression and g++ gets the option '-Wpedantic>'; and its CUDA engine carries "
+            "the 48-layer Scout sizes as compiled-in members (include/engine/llama4_cuda_engine.hpp:121-140) and runs "
+            "one sequence, so it could run neither this 24-layer configuration nor a batch of 8 unmodified")
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -350,12 +510,15 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k"], default="scout24")
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "cpu_baseline"], default="scout24")
+    ap.add_argument("--reference-root", default=os.environ.get("CPI_REFERENCE_ROOT"),
+                    help="a checkout of kurulav1/cpi (for --workload cpu_baseline)")
     args = ap.parse_args()
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "kurulav1/cpi is a CMake C++/CUDA project with neither setup.py nor pyproject.toml: "
-                          "pip cannot install it offline (Directory is not installable)"}))
+        print(json.dumps({"impl": "reference", "unavailable": reference_arm_reason()}))
+        return 0
+    if args.workload == "cpu_baseline":
+        print(json.dumps(run_cpu_baseline(args)))
         return 0
     if args.gpus != 1:
         print(json.dumps({"error": "cpi_b200 is a single-GPU library: run with --gpus 1", "n_gpus": args.gpus}))

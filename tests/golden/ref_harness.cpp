@@ -5,6 +5,7 @@
 //
 // usage: ref_harness MODEL_DIR OUT.f32 vocab hidden heads kv_heads head_dim layers experts expert_inter
 //                    shared_inter rope_orig_max theta factor low high  tok0 tok1 ...
+// It prints `forward_ms=<ms> tokens=<n>` (the wall time of the token loop alone) on standard error.
 #include <chrono>
 #include <cstdio>
 #include <cstdlib>
@@ -37,10 +38,16 @@ int main(int argc, char** argv) {
   e.initialize(o);
   FILE* f = std::fopen(argv[2], "wb");
   if (!f) return 2;
+  std::vector<float> all;
+  all.reserve((size_t)(argc - a) * e.logits_.size());
+  const auto t0 = std::chrono::steady_clock::now();
   for (int i = a, pos = 0; i < argc; ++i, ++pos) {
     e.forward_token(std::atoi(argv[i]), pos);
-    std::fwrite(e.logits_.data(), sizeof(float), e.logits_.size(), f);
+    all.insert(all.end(), e.logits_.begin(), e.logits_.end());
   }
+  const double ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+  std::fwrite(all.data(), sizeof(float), all.size(), f);
   std::fclose(f);
+  std::fprintf(stderr, "forward_ms=%.3f tokens=%d\n", ms, argc - a);
   return 0;
 }
