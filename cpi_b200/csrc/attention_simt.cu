@@ -4,7 +4,9 @@
 //   qkv_post   per token and head: optional weightless RMS norm of q and k, rotary position encoding,
 //              optional query temperature; writes q to its buffer and k, v into the cache pages.
 //   attention  one block per (token, head): scores over the keys the window allows, softmax and the
-//              weighted sum of values in float32, keys visited in position order.
+//              weighted sum of values in float32, keys visited in position order.  A position encoding
+//              that acts on the scores hands in a table: score(query at p, key at t) += bias[head][min(p - t,
+//              n_dist - 1)].
 //
 // Formulas (file:line of kurulav1/cpi): per-head norm src/engine/llama4_cpu_engine.cpp:308-317; RoPE pairs
 // (d, d + D/2) with angle float(p) * theta_d :167-193, :467; scores, softmax with 1/max(sum, 1e-20) and
@@ -226,6 +228,7 @@ struct AttnParams {
   int n_heads, n_kv_heads, head_dim;
   int window_kind, window_size;          // 0 all keys, 1 chunk of window_size, 2 last window_size keys
   float scale;
+  const float* score_bias; int n_dist;   // [NH, n_dist] float32 added to the scaled scores by distance, or null
 };
 
 __device__ __forceinline__ int window_low(int kind, int size, int pos) {
@@ -270,6 +273,7 @@ __global__ void __launch_bounds__(ATT_NT) attention_general_kernel(AttnParams p)
       float dot = 0.f;
       for (int d = 0; d < D; ++d) dot = fmaf(q_s[d], to_f32(kr[d]), dot);
       s = dot * p.scale;
+      if (p.score_bias) s += p.score_bias[(size_t)h * p.n_dist + min(pos - kp, p.n_dist - 1)];
     }
     const float m_new = fmaxf(m_run, block_max(s, scratch));
     const float e = valid ? expf(s - m_new) : 0.f;
@@ -342,13 +346,15 @@ extern "C" int cpi_attention_general(const void* q, void* out, const void* k_cac
                                      int dtype, const int* page_table, int max_blocks, int page_size,
                                      const int* token_seq, const int* token_pos, const int* seq_slot,
                                      int n_tokens, int n_heads, int n_kv_heads, int head_dim,
-                                     int window_kind, int window_size, float scale, cudaStream_t stream) {
+                                     int window_kind, int window_size, float scale, const float* score_bias,
+                                     int n_dist, cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   if (check_head("attention", n_heads, n_kv_heads, head_dim)) return 1;
+  CPI_REQUIRE(score_bias == nullptr || n_dist > 0, "attention: a score bias table needs at least one distance");
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention: window kind %d needs a size > 0", window_kind);
   CPI_REQUIRE(n_heads <= 65535, "attention: too many heads (%d)", n_heads);
   AttnParams p{q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos, seq_slot,
-               n_heads, n_kv_heads, head_dim, window_kind, window_size, scale};
+               n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias, n_dist};
   dim3 grid(n_tokens, n_heads);
   CPI_DISPATCH_DTYPE(dtype, T, cpi::launch_pdl(attention_general_kernel<T>, grid, ATT_NT, 0, stream, p));
   return check_launch("attention_general");

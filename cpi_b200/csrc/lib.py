@@ -283,14 +283,19 @@ def qkv_post(qkv, q_out, k_cache, v_cache, page_table, page_size, token_seq, tok
 
 
 def attention_general(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, *,
-                      n_heads, n_kv_heads, head_dim, window_kind, window_size, scale):
-    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot)
+                      n_heads, n_kv_heads, head_dim, window_kind, window_size, scale, score_bias=None):
+    """Attention of any head size and dtype over the paged cache.  `score_bias`: float32 [heads, n_dist] added
+    to the scaled scores, indexed by the distance query position - key position (the last column for longer)."""
+    _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, score_bias)
     assert q.is_contiguous() and out.is_contiguous() and q.dtype == out.dtype == k_cache.dtype
+    assert score_bias is None or (score_bias.dtype == torch.float32 and score_bias.is_contiguous()
+                                  and score_bias.dim() == 2 and score_bias.shape[0] == n_heads)
     T = q.shape[0]
     _call("cpi_attention_general", _p(q), _p(out), _p(k_cache), _p(v_cache), c_int(dtype_code(q.dtype)),
           _p(page_table), c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos),
           _p(seq_slot), c_int(T), c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind),
-          c_int(window_size), c_float(scale), _stream())
+          c_int(window_size), c_float(scale), _p(score_bias),
+          c_int(0 if score_bias is None else score_bias.shape[1]), _stream())
 
 
 _dec_scratch = {}

@@ -20,7 +20,7 @@ from ..cache.manager import KVRequirement
 from ..csrc import lib as K
 from ..phases import phase
 from ..weights.store import TensorReq
-from .base import Mixer, build_part, register_mixer
+from .base import Mixer, RotaryEncoding, ScoreBias, build_part, register_mixer
 from .linear import MODE_ADD, project
 
 
@@ -54,6 +54,7 @@ class AttentionMixer(Mixer):
         self.temperature = None if t is None else (float(t["floor_scale"]), float(t["attn_scale"]))
         self.ws = workspace
         self.w_qkv = self.w_o = None
+        self.rotary = self.score_bias = None
 
     # ---- weights ---------------------------------------------------------------------------------
     def _names(self):
@@ -77,6 +78,18 @@ class AttentionMixer(Mixer):
         del parts
         self.w_o = source.get(o, device).contiguous()
         self.position.prepare(device)
+        # what the position part is to this mixer: a rotation of q and k (done with the head norm and the cache
+        # write, in one kernel), a bias on the scores (taken by the general attention kernel only), or nothing
+        enc = self.position.encoding()
+        self.rotary = enc if isinstance(enc, RotaryEncoding) else None
+        self.score_bias = enc.table if isinstance(enc, ScoreBias) else None
+        if enc is not None and self.rotary is None and self.score_bias is None:
+            raise TypeError(f"attention: the position part '{self.position.spec.kind}' describes itself as "
+                            f"{type(enc).__name__}; this mixer's kernels take RotaryEncoding, ScoreBias or None")
+        if self.score_bias is not None and (self.score_bias.dim() != 2 or self.score_bias.shape[0] != self.nh
+                                            or self.score_bias.dtype != torch.float32):
+            raise ValueError(f"attention: a score bias must be float32 [{self.nh} heads, distances], got "
+                             f"{tuple(self.score_bias.shape)} {self.score_bias.dtype}")
 
     # ---- cache -----------------------------------------------------------------------------------
     def kv_requirement(self):
@@ -94,7 +107,8 @@ class AttentionMixer(Mixer):
         with phase("kv_store"):          # head norm, rotation, temperature and the write into the cache: one kernel
             K.qkv_post(qkv, q, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                        batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
-                       inv_freq=self.position.inv_freq, interleaved=self.position.interleaved,
+                       inv_freq=None if self.rotary is None else self.rotary.inv_freq,
+                       interleaved=self.rotary is not None and self.rotary.interleaved,
                        qk_norm=self.qk_norm, norm_before_rope=self.norm_before_rope,
                        norm_eps=self.qk_norm_eps, temperature=self.temperature,
                        write_kv=self.has_kv and cache.owns)
@@ -106,7 +120,8 @@ class AttentionMixer(Mixer):
 
     def attend(self, q, att, k_cache, v_cache, table, page_size, batch):
         wk = K.WINDOW_KINDS[self.window_kind]
-        if (use_tensor_core_kernels and batch.is_decode and q.dtype == torch.bfloat16
+        tensor_cores = use_tensor_core_kernels and self.score_bias is None     # those kernels add nothing to a score
+        if (tensor_cores and batch.is_decode and q.dtype == torch.bfloat16
                 and K.attention_decode_supported(self.nh, self.nkv, self.d, page_size)):
             # keys per sequence that the window lets through, at most (a bucketed bound: the split count
             # then stays the same from step to step, which a captured graph needs)
@@ -124,7 +139,7 @@ class AttentionMixer(Mixer):
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                                window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)
             return
-        if (use_tensor_core_kernels and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
+        if (tensor_cores and not batch.is_decode and q.dtype == torch.bfloat16 and batch.n_q_tiles
                 and K.attention_prefill_supported(self.nh, self.nkv, self.d, page_size)):
             K.attention_prefill(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                 batch.seq_slot, batch.tile_tok0, batch.tile_rows, n_heads=self.nh,
@@ -134,4 +149,4 @@ class AttentionMixer(Mixer):
         K.attention_general(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                             batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                             window_kind=K.WINDOW_KINDS[self.window_kind], window_size=self.window_size,
-                            scale=self.scale)
+                            scale=self.scale, score_bias=self.score_bias)

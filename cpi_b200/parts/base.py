@@ -8,7 +8,7 @@ step's `StepBatch`, and -- for mixers -- the cache and state views the engine ha
 Interfaces
 ----------
 Norm          requirements(); load(src, dev); __call__(x, out_dtype, rows=None) -> tensor
-Position      (no weights) prepare(dev); describes how q and k are encoded; consumed by its mixer
+Position      (no weights) prepare(dev); encoding() -> RotaryEncoding | ScoreBias | None, consumed by its mixer
 Mixer         requirements(); load(src, dev); kv_requirement(); state_requirements();
               forward(h, residual, batch, cache)        # residual += mixer(h)
 FeedForward   requirements(); load(src, dev); forward(h, residual, batch)   # residual += ffn(h)
@@ -25,6 +25,7 @@ graphs only if all its parts do.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Callable
 
 import torch
@@ -54,11 +55,31 @@ class Norm(Part):
         raise NotImplementedError
 
 
+@dataclass(frozen=True)
+class RotaryEncoding:
+    """q and k are rotated pairwise: the pair d of a head at position p turns by the angle p * inv_freq[d]
+    (float32 [head_dim / 2] on the device); `interleaved` pairs (2d, 2d + 1), otherwise (d, d + head_dim / 2)."""
+    inv_freq: torch.Tensor
+    interleaved: bool = False
+
+
+@dataclass(frozen=True)
+class ScoreBias:
+    """Positions act on the attention scores: table[head, min(query position - key position, n - 1)] (float32
+    [heads, n] on the device) is added to the scaled score of a query and a key; q and k stay as projected."""
+    table: torch.Tensor
+
+
 class Position(Part):
-    """How a mixer encodes positions into q and k; `prepare` builds device tables."""
+    """How positions enter a mixer.  `prepare` builds device tables; `encoding()` then says what the part is to
+    its mixer: a `RotaryEncoding`, a `ScoreBias`, or None (positions do not enter).  A mixer takes the kinds
+    its kernels know and refuses the others by name."""
 
     def prepare(self, device) -> None:
         pass
+
+    def encoding(self):
+        return None
 
 
 class Mixer(Part):

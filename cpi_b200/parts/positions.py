@@ -10,7 +10,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .base import Position, register_position
+from .base import Position, RotaryEncoding, register_position
 
 
 def llama3_frequencies(head_dim: int, theta: float, scaling) -> np.ndarray:
@@ -54,9 +54,10 @@ class RotaryPosition(Position):
     def prepare(self, device):
         self.inv_freq = torch.from_numpy(self.frequencies).to(device)
 
+    def encoding(self):
+        return RotaryEncoding(self.inv_freq, self.interleaved)
+
 
 @register_position("none")
 class NoPosition(Position):
     graph_safe = True
-    interleaved = False
-    inv_freq = None

@@ -55,7 +55,11 @@ def test_position_part_matches_plain_frequencies():
     pos = build_part("position", spec.layers[0].mixer["position"])
     assert (pos.frequencies == P.rope_frequencies(c)).all() and not pos.interleaved
     none = build_part("position", spec.layers[3].mixer["position"])
-    assert none.inv_freq is None
+    assert none.encoding() is None
+    pos.prepare(DEV)
+    enc = pos.encoding()
+    assert type(enc).__name__ == "RotaryEncoding" and not enc.interleaved
+    assert (enc.inv_freq.cpu().numpy() == P.rope_frequencies(c)).all()
     d, spec, c, W = _llama4("B")
     posb = build_part("position", spec.layers[0].mixer["position"])
     assert (posb.frequencies == P.rope_frequencies(c)).all() and posb.interleaved
@@ -270,7 +274,7 @@ def _register_toy_ffn_and_position():
     ReLU experts by the largest of the token's first features, and a position encoding that the attention
     mixer consumes like rotary frequencies (positions divided by a constant: linear interpolation)."""
     import numpy as np
-    from cpi_b200.parts import FeedForward, Position, register_feed_forward, register_position
+    from cpi_b200.parts import FeedForward, Position, RotaryEncoding, register_feed_forward, register_position
     from cpi_b200.weights import TensorReq
 
     @register_feed_forward("toy_routed_relu")
@@ -297,8 +301,6 @@ def _register_toy_ffn_and_position():
 
     @register_position("toy_interpolated")
     class Interpolated(Position):
-        interleaved = True
-
         def __init__(self, spec, prefix=""):
             super().__init__(spec, prefix)
             d, div = int(spec["head_dim"]), float(spec["divide_by"])
@@ -308,6 +310,9 @@ def _register_toy_ffn_and_position():
 
         def prepare(self, device):
             self.inv_freq = torch.from_numpy(self.frequencies).to(device)
+
+        def encoding(self):
+            return RotaryEncoding(self.inv_freq, interleaved=True)
 
     return RoutedRelu, Interpolated
 
@@ -375,6 +380,109 @@ def test_toy_routed_feed_forward_and_toy_positions_register_build_and_step():
     rows += [(out[0], ra[33]), (out[1], rb[12])]
     e.release_slot(sb)
     for t in range(34, 40):
+        rows.append((e.step([StepEntry(sa, [a[t]], [0])]).float().cpu()[0], ra[t]))
+    e.release_slot(sa)
+    e.check_device_errors()
+    for got, want in rows:
+        assert float((got - want).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_position_that_biases_the_scores_and_one_the_mixer_refuses(dtype):
+    """Positions need not rotate anything: a position part defined here describes itself as a bias on the scores
+    by (head, distance), with a slope per head and distances beyond the table's end sharing its last column.
+    The attention mixer takes it (on its general kernel) in prompts, unequal batches and decoding; a part that
+    describes itself as something the mixer's kernels do not know is refused when the model is built."""
+    from dataclasses import dataclass
+    from cpi_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from cpi_b200.engine import Engine, StepEntry
+    from cpi_b200.engine.model import tensor_requirements
+    from cpi_b200.parts import Position, ScoreBias, register_position
+    from cpi_b200.weights import DictSource, RandomSource
+    H, V, NH, NKV, D, I, N_DIST = 64, 90, 4, 2, 64, 96, 24
+
+    @register_position("toy_distance_bias")
+    class DistanceBias(Position):
+        graph_safe = True
+
+        def __init__(self, spec, prefix=""):
+            super().__init__(spec, prefix)
+            slopes = torch.tensor([float(spec["slope"]) * (h + 1) for h in range(int(spec["heads"]))])
+            self.table_cpu = -slopes[:, None] * torch.arange(int(spec["distances"]), dtype=torch.float32)[None, :]
+            self.table = None
+
+        def prepare(self, device):
+            self.table = self.table_cpu.contiguous().to(device)
+
+        def encoding(self):
+            return ScoreBias(self.table)
+
+    @dataclass
+    class Unknown:
+        anything: int = 0
+
+    @register_position("toy_unknown_kind")
+    class Strange(Position):
+        def encoding(self):
+            return Unknown()
+
+    def spec_with(pos):
+        norm = lambda w: PartSpec("rmsnorm", {"size": H, "eps": 1e-5, "weight": w})
+        attn = PartSpec("attention", {"hidden_size": H, "num_heads": NH, "num_kv_heads": NKV, "head_dim": D,
+                                      "softmax_scale": D ** -0.5, "position": pos, "qk_norm": False,
+                                      "qk_norm_eps": 0.0, "window": {"kind": "full", "size": 0},
+                                      "query_temperature": None})
+        ffn = PartSpec("dense_swiglu", {"hidden_size": H, "intermediate_size": I})
+        layers = tuple(LayerSpec(prefix=f"l{i}.", block=PartSpec("pre_norm"), mixer=attn, feed_forward=ffn,
+                                 mixer_norm=norm("n1.weight"), feed_forward_norm=norm("n2.weight")) for i in range(2))
+        return ModelSpec(architecture="ToyBias", hidden_size=H, vocab_size=V,
+                         embedding=PartSpec("token_embedding", {"weight": "emb.weight"}), layers=layers,
+                         run_order=(RunEntry(0), RunEntry(1)), final_norm=norm("norm.weight"),
+                         head=PartSpec("linear_head", {"weight": "head.weight"}), initializer_range=0.2)
+
+    pos = PartSpec("toy_distance_bias", {"heads": NH, "slope": 0.11, "distances": N_DIST})
+    spec = spec_with(pos)
+    src = RandomSource(tensor_requirements(spec), 9, 0.2)
+    drawn = {n: src.get(n, "cpu") for n in src.names()}
+    W = {n: t.float() for n, t in drawn.items()}
+    with pytest.raises(TypeError, match="toy_unknown_kind.*Unknown"):
+        Engine(spec_with(PartSpec("toy_unknown_kind", {})), DictSource(drawn), dtype=dtype, max_tokens=64)
+    e = Engine(spec, DictSource(drawn), dtype=dtype, max_tokens=512)
+    assert e.use_graphs
+    table = DistanceBias(pos).table_cpu
+
+    def plain(tokens):
+        n = len(tokens)
+        x = W["emb.weight"][tokens]
+        pt = torch.arange(n)
+        dist = (pt[:, None] - pt[None, :]).clamp(0, N_DIST - 1)
+        causal = pt[None, :] <= pt[:, None]
+        for i in range(2):
+            h = P.rmsnorm(x, W[f"l{i}.n1.weight"], 1e-5)
+            q = (h @ W[f"l{i}.self_attn.q_proj.weight"].T).reshape(n, NH, D)
+            k = (h @ W[f"l{i}.self_attn.k_proj.weight"].T).reshape(n, NKV, D)
+            v = (h @ W[f"l{i}.self_attn.v_proj.weight"].T).reshape(n, NKV, D)
+            out = torch.empty(n, NH, D)
+            for hd in range(NH):
+                s = (q[:, hd] @ k[:, hd // (NH // NKV)].T) * D ** -0.5 + table[hd][dist]
+                s = s.masked_fill(~causal, float("-inf"))
+                out[:, hd] = torch.softmax(s, -1) @ v[:, hd // (NH // NKV)]
+            x = x + out.reshape(n, NH * D) @ W[f"l{i}.self_attn.o_proj.weight"].T
+            h2 = P.rmsnorm(x, W[f"l{i}.n2.weight"], 1e-5)
+            f = f"l{i}.feed_forward."
+            x = x + P.swiglu_mlp(h2, W[f + "gate_proj.weight"], W[f + "up_proj.weight"], W[f + "down_proj.weight"])
+        return P.rmsnorm(x, W["norm.weight"], 1e-5) @ W["head.weight"].T
+
+    a, b = tiny.random_tokens(70, V, 1), tiny.random_tokens(13, V, 2)
+    ra, rb = plain(a), plain(b)
+    tol = (2e-5 if dtype == "float32" else 2e-2) * float(ra.abs().max())
+    sa, sb = e.acquire_slot(), e.acquire_slot()
+    out = e.step([StepEntry(sa, a[:50], [0, 30, 49]), StepEntry(sb, b[:12], [11])]).float().cpu()
+    rows = [(out[0], ra[0]), (out[1], ra[30]), (out[2], ra[49]), (out[3], rb[11])]
+    out = e.step([StepEntry(sa, [a[50]], [0]), StepEntry(sb, [b[12]], [0])]).float().cpu()
+    rows += [(out[0], ra[50]), (out[1], rb[12])]
+    e.release_slot(sb)
+    for t in range(51, 70):
         rows.append((e.step([StepEntry(sa, [a[t]], [0])]).float().cpu()[0], ra[t]))
     e.release_slot(sa)
     e.check_device_errors()
