@@ -2,9 +2,11 @@
 //
 // A block serves one (split, key/value head, sequence): the G query heads that share the key/value head
 // form the rows of a 16-row MMA tile, so every key and value byte is read once per group and not once
-// per head.  Keys and values arrive page by page (64 positions x D) through cp.async into a
-// double-buffered, XOR-swizzled shared-memory tile; each of the four warps owns 16 keys of the page
-// and runs its own online softmax (scores S = Q K^T and the product P V on mma.sync m16n8k16 with
+// per head.  Keys and values arrive page by page: a (page, head) tile of 64 positions x D is contiguous
+// in the cache, and one thread fetches it with the copy engine (cp.async.bulk.tensor boxes of 64 positions
+// x 64 features with the 128-byte swizzle) into a ring of shared-memory stages, several pages ahead of the
+// arithmetic; an mbarrier per stage says when its bytes have landed.  Each of the four warps owns 16 keys
+// of the page and runs its own online softmax (scores S = Q K^T and the product P V on mma.sync m16n8k16 with
 // float32 accumulators; a 5..16-row problem is below the 64-row minimum of tcgen05, and the kernel is
 // bound by the cache bytes, not by the tensor pipe).  Warps, then splits, are merged with the usual
 // (max, sum) rescaling; with one split the block writes the output itself, otherwise it writes
@@ -12,9 +14,12 @@
 //
 // Reference: gqa_decode_kernel (src/kernels/kernels_attention_decode.cu:868-951) visits one key per
 // iteration with three block barriers each; formulas as in src/engine/llama4_cpu_engine.cpp:195-250.
-// Positions outside [window low, pos] are masked, and their tile rows are zero-filled so that stale
-// page contents can never reach the result.
+// Positions outside [window low, pos] are masked; in a page that holds such positions their value rows
+// are overwritten with zeros in shared memory before use, so that stale page contents can never reach
+// the result (0 x NaN would).  The waits on the copy engine are bounded: when one runs out the block
+// raises the error word, skips its arithmetic, gives the copies in flight time to land and returns.
 #include "common.cuh"
+#include <cuda.h>
 
 namespace cpi {
 namespace dec {
@@ -32,15 +37,36 @@ struct Params {
   float scale_log2;                                 // softmax scale * log2(e)
   int n_splits;
   float* part_o; float* part_ml;                    // [T, NH, splits, D], [T, NH, splits, 2]
+  int* error_flag;                                  // set to 1 when a wait on the copy engine ran out
 };
 
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
-  const int n = valid ? 16 : 0;                     // 0 source bytes: the 16 bytes are zero-filled
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(n) : "memory");
+constexpr uint32_t kSpinLimit = 1u << 24;
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1) : "memory");
+}
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
@@ -67,9 +93,11 @@ __device__ __forceinline__ int window_low(int kind, int size, int pos) {
   return 0;
 }
 
-// shared tile: PAGE rows of D bf16; 16-byte chunk c of row r is stored at chunk c ^ (r & 7)
+// Shared tile of PAGE rows x D bf16 as the copy engine's 128-byte swizzle leaves it: one box of 64 features
+// (rows of 128 bytes) after the other, and within a box the 16-byte chunk c of row r at chunk c ^ (r & 7).
+// `chunk` counts the row's 16-byte chunks 0 .. D/8 - 1; the result is in elements.
 template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
-  return row * D + ((chunk ^ (row & 7)) << 3);
+  return (chunk >> 3) * (PAGE * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
 }
 
 // out[th, :] = sum_s w_s O_s / sum_s w_s l_s,  w_s = 2^(m_s - max m), for one (token, head); at most
@@ -150,19 +178,35 @@ __device__ __forceinline__ void combine_head(const float* __restrict__ part_o, c
   }
 }
 
+template <int D> struct Stages { static constexpr int N = D > 64 ? 3 : 4; };    // pages in flight per block
+
 template <int D>
-__global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
-  pdl_launch_dependents();
-  pdl_wait();
-  constexpr int CH = D / 8;                 // 16-byte chunks per row
+__global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                              const __grid_constant__ CUtensorMap map_v, Params p) {
   constexpr int KS = D / 16;                // k-steps of Q K^T
   constexpr int NO = D / 8;                 // n-tiles of the output
-  extern __shared__ __align__(128) uint8_t smem_raw[];
-  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [2][PAGE][D]
-  __nv_bfloat16* v_s = k_s + 2 * PAGE * D;                                     // [2][PAGE][D]
+  constexpr int STAGES = Stages<D>::N;
+  constexpr int TILE = PAGE * D;            // elements of one (page, head) tile
+  constexpr uint32_t STAGE_TX = 2u * TILE * 2u;       // bytes of a stage: keys and values
+  extern __shared__ uint8_t smem_dyn[];
+  __shared__ uint64_t full_bar[STAGES];
+  __shared__ int abort_s;                   // set by the first thread whose wait ran out; the others then stop waiting
+  // the swizzle is a function of the address: tiles start on 1024-byte boundaries
+  uint8_t* smem_raw = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~uintptr_t(1023));
+  __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);            // [STAGES][PAGE][D]
+  __nv_bfloat16* v_s = k_s + STAGES * TILE;                                    // [STAGES][PAGE][D]
 
   const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  pdl_launch_dependents();
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full_bar[s], 1);
+    abort_s = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  pdl_wait();
+  volatile int* aborted = &abort_s;
   const int G = p.n_heads / p.n_kv_heads;
   const int pos = p.token_pos[t];
   const int slot = p.seq_slot[p.token_seq[t]];
@@ -173,6 +217,19 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
   const int per = (n_blocks + p.n_splits - 1) / p.n_splits;
   const int b_begin = b_lo + split * per;
   const int b_end = min(b_hi + 1, b_begin + per);
+
+  // one thread asks the copy engine for the page of block `blk` into stage `st`
+  auto load_tile = [&](int blk, int st) {
+    const int row0 = (table[blk] * p.n_kv_heads + kvh) * PAGE;      // first row of the (page, head) tile
+    mbar_expect_tx(&full_bar[st], STAGE_TX);
+#pragma unroll
+    for (int h = 0; h < D / 64; ++h) {
+      tma_load_2d(k_s + st * TILE + h * (PAGE * 64), &map_k, &full_bar[st], h * 64, row0);
+      tma_load_2d(v_s + st * TILE + h * (PAGE * 64), &map_v, &full_bar[st], h * 64, row0);
+    }
+  };
+  if (tid == 0)
+    for (int i = 0; i < STAGES && b_begin + i < b_end; ++i) load_tile(b_begin + i, i);
 
   // ---- Q fragments: rows = the group's heads (rows >= G are zero) ----
   const int r0 = lane >> 2, j = lane & 3;
@@ -189,36 +246,31 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
     }
   }
 
-  auto load_tile = [&](int blk, int buf) {
-    const int page = table[blk];
-    const size_t base = ((size_t)page * p.n_kv_heads + kvh) * (size_t)(PAGE * D);
-    const int first = blk * PAGE;
-#pragma unroll
-    for (int i = 0; i < PAGE * CH / NT; ++i) {
-      const int c = tid + i * NT;
-      const int row = c / CH, ch = c % CH;
-      const int kp = first + row;
-      const bool valid = kp >= lo && kp <= pos;
-      const size_t g = base + (size_t)row * D + ch * 8;
-      cp_async16(k_s + buf * PAGE * D + tile_off<D>(row, ch), p.k_cache + g, valid);
-      cp_async16(v_s + buf * PAGE * D + tile_off<D>(row, ch), p.v_cache + g, valid);
-    }
-    cp_async_commit();
-  };
-
   float m_run[2] = {-1e30f, -1e30f}, l_run[2] = {0.f, 0.f};
   float o[NO][4];
 #pragma unroll
   for (int i = 0; i < NO; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
 
-  if (b_begin < b_end) load_tile(b_begin, 0);
   for (int blk = b_begin; blk < b_end; ++blk) {
-    const int buf = (blk - b_begin) & 1;
-    if (blk + 1 < b_end) { load_tile(blk + 1, buf ^ 1); cp_async_wait<1>(); } else { cp_async_wait<0>(); }
-    __syncthreads();
-    const __nv_bfloat16* kt = k_s + buf * PAGE * D;
-    const __nv_bfloat16* vt = v_s + buf * PAGE * D;
+    const int it = blk - b_begin, buf = it % STAGES;
+    // every thread passes the barrier at the end of each round whether its wait held or not
+    bool live = !*aborted;
+    if (live && !mbar_wait(&full_bar[buf], (it / STAGES) & 1)) { *aborted = 1; live = false; }
+    const bool ragged = blk * PAGE < lo || blk * PAGE + PAGE - 1 > pos;      // the page holds positions outside the window
+    if (live) {
+    const __nv_bfloat16* kt = k_s + buf * TILE;
+    __nv_bfloat16* vt = v_s + buf * TILE;
     const int key0 = warp * 16;                       // this warp's 16 keys of the page
+    if (ragged) {
+      // this warp's value rows outside [lo, pos] become zeros (two lanes per row, D / 16 chunks each)
+      const int row = key0 + (lane >> 1), kp = blk * PAGE + row;
+      if (kp < lo || kp > pos) {
+#pragma unroll
+        for (int c = 0; c < D / 16; ++c)
+          *reinterpret_cast<uint4*>(vt + tile_off<D>(row, (lane & 1) * (D / 16) + c)) = make_uint4(0u, 0u, 0u, 0u);
+      }
+      __syncwarp();
+    }
 
     // ---- S = Q K^T for 16 keys: two n-tiles of 8 ----
     float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
@@ -278,7 +330,18 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(Params p) {
       mma_bf16(o[2 * nt2], pa, b[0], b[1]);
       mma_bf16(o[2 * nt2 + 1], pa, b[2], b[3]);
     }
-    __syncthreads();                                  // the buffer is loaded again two pages later
+    }
+    // the zeros written above must be ordered before the copy engine writes this stage again
+    if (ragged) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();                                  // every warp is done with the stage: it is asked for again
+    if (tid == 0 && blk + STAGES < b_end && !*aborted) load_tile(blk + STAGES, buf);
+  }
+  __syncthreads();
+  if (*aborted) {
+    // a wait ran out: say so, give the copies in flight time to land before the shared memory is released
+    if (tid == 0 && p.error_flag) atomicExch(p.error_flag, 1);
+    for (int i = 0; i < 2000; ++i) __nanosleep(1000);
+    return;
   }
   // l is a sum over this thread's columns only: complete it over the quad
 #pragma unroll
@@ -347,32 +410,62 @@ extern "C" int cpi_attention_decode_supported(int n_heads, int n_kv_heads, int h
 
 // q, out [T, NH, D] bfloat16, one token per sequence.  part_o needs T*NH*splits*D floats, part_ml
 // T*NH*splits*2 floats (both unused when n_splits == 1).
-extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache,
+namespace cpi { namespace tc {
+int get_map_2d_bf16(const void* ptr, uint64_t inner, uint64_t rows, uint64_t row_stride_bytes, uint32_t box_inner,
+                    uint32_t box_rows, CUtensorMap* out);
+} }
+
+// Blocks of the kernel that share an SM (by their shared memory), for the caller's choice of `n_splits`.
+extern "C" int cpi_attention_decode_blocks_per_sm(int head_dim) {
+  const int stages = head_dim > 64 ? dec::Stages<128>::N : dec::Stages<64>::N;
+  const int smem = stages * 2 * dec::PAGE * head_dim * 2 + 2048;
+  int dev = 0, per_sm = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess) {
+    cudaGetLastError();
+    return 1;
+  }
+  const int n = per_sm / smem;
+  return n < 1 ? 1 : n;
+}
+
+// `n_pages`: pages of the cache tensors k_cache, v_cache [n_pages, n_kv_heads, page_size, head_dim].
+// `error_flag`: an int32 on the device that is set to 1 when a block's wait on the copy engine runs out (may be null).
+extern "C" int cpi_attention_decode(const void* q, void* out, const void* k_cache, const void* v_cache, long n_pages,
                                     const int* page_table, int max_blocks, int page_size, const int* token_seq,
                                     const int* token_pos, const int* seq_slot, int n_tokens, int n_heads,
                                     int n_kv_heads, int head_dim, int window_kind, int window_size, float scale,
-                                    int n_splits, float* part_o, float* part_ml, cudaStream_t stream) {
+                                    int n_splits, float* part_o, float* part_ml, int* error_flag,
+                                    cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   CPI_REQUIRE(cpi_attention_decode_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_decode: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention_decode: window kind %d needs a size > 0", window_kind);
   CPI_REQUIRE(n_splits >= 1 && n_splits <= dec::kMaxSplits && n_tokens <= 65535, "attention_decode: bad grid (%d splits of at most %d, %d tokens)", n_splits, dec::kMaxSplits, n_tokens);
   CPI_REQUIRE(n_splits == 1 || (part_o && part_ml), "attention_decode: split scratch is missing");
+  CPI_REQUIRE(n_pages > 0 && (reinterpret_cast<uintptr_t>(k_cache) & 15) == 0 && (reinterpret_cast<uintptr_t>(v_cache) & 15) == 0,
+              "attention_decode: the cache must hold at least one page and be 16-byte aligned");
   dec::Params p{(const __nv_bfloat16*)q, (__nv_bfloat16*)out, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,
                 page_table, max_blocks, token_seq, token_pos, seq_slot, n_heads, n_kv_heads, window_kind, window_size,
-                scale * 1.4426950408889634f, n_splits, part_o, part_ml};
+                scale * 1.4426950408889634f, n_splits, part_o, part_ml, error_flag};
+  // the cache as rows of head_dim features: a (page, head) tile is 64 consecutive rows
+  CUtensorMap mk, mv;
+  const uint64_t kv_rows = (uint64_t)n_pages * n_kv_heads * dec::PAGE;
+  if (tc::get_map_2d_bf16(k_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, dec::PAGE, &mk)) return 1;
+  if (tc::get_map_2d_bf16(v_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, dec::PAGE, &mv)) return 1;
   dim3 grid(n_splits, n_kv_heads, n_tokens);
-  const int smem_tiles = 4 * dec::PAGE * head_dim * 2;
+  const int stages = head_dim == 128 ? dec::Stages<128>::N : dec::Stages<64>::N;
+  const int smem_tiles = stages * 2 * dec::PAGE * head_dim * 2;
   const int smem_merge = (4 * 16 * head_dim + 128) * 4;
-  const int smem = smem_tiles > smem_merge ? smem_tiles : smem_merge;
+  const int smem = (smem_tiles > smem_merge ? smem_tiles : smem_merge) + 1024;
   if (head_dim == 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(dec::attention_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    cpi::launch_pdl(dec::attention_decode_kernel<128>, grid, dec::NT, smem, stream, p);
+    cpi::launch_pdl(dec::attention_decode_kernel<128>, grid, dec::NT, smem, stream, mk, mv, p);
   } else {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(dec::attention_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }
-    cpi::launch_pdl(dec::attention_decode_kernel<64>, grid, dec::NT, smem, stream, p);
+    cpi::launch_pdl(dec::attention_decode_kernel<64>, grid, dec::NT, smem, stream, mk, mv, p);
   }
   if (check_launch("attention_decode")) return 2;
   if (n_splits > 1) {
@@ -427,7 +520,7 @@ static int static_scratch(float** out) {
 extern "C" long cpi_attention_decode_noalloc_capacity() { return cpi::dec::kStaticScratchFloats; }
 
 extern "C" int cpi_attention_decode_noalloc(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                            const int* page_table, int max_blocks, int page_size,
+                                            long n_pages, const int* page_table, int max_blocks, int page_size,
                                             const int* token_seq, const int* token_pos, const int* seq_slot,
                                             int n_tokens, int n_heads, int n_kv_heads, int head_dim, int window_kind,
                                             int window_size, float scale, int n_splits, cudaStream_t stream) {
@@ -442,7 +535,7 @@ extern "C" int cpi_attention_decode_noalloc(const void* q, void* out, const void
   if (dec::static_scratch(&scratch)) return 1;
   float* part_o = scratch;
   float* part_ml = scratch + (long)n_tokens * n_heads * n_splits * head_dim;
-  return cpi_attention_decode(q, out, k_cache, v_cache, page_table, max_blocks, page_size, token_seq, token_pos,
-                              seq_slot, n_tokens, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale,
-                              n_splits, part_o, part_ml, stream);
+  return cpi_attention_decode(q, out, k_cache, v_cache, n_pages, page_table, max_blocks, page_size, token_seq,
+                              token_pos, seq_slot, n_tokens, n_heads, n_kv_heads, head_dim, window_kind, window_size,
+                              scale, n_splits, part_o, part_ml, nullptr, stream);
 }

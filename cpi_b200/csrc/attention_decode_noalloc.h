@@ -28,7 +28,9 @@
 //     at the same time on one GPU (different streams, or different host threads) race on the array;
 //     keep such calls in one stream or order them yourself.
 //   * Shapes: the same as cpi_attention_decode (bfloat16, head size 64 or 128, pages of 64 positions,
-//     at most 16 query heads per key/value head).
+//     at most 16 query heads per key/value head).  `n_pages` is the number of pages that k_cache and
+//     v_cache hold ([n_pages, n_kv_heads, 64, head_dim] each): the copy engine's descriptors of the two
+//     tensors are made from it, on the host, without touching device memory.
 //
 // Returns 0 after launching on `stream`, non-zero with a message in cpi_last_error() otherwise.
 #pragma once
@@ -41,7 +43,7 @@ extern "C" {
 long cpi_attention_decode_noalloc_capacity(void);
 
 int cpi_attention_decode_noalloc(const void* q, void* out, const void* k_cache, const void* v_cache,
-                                 const int* page_table, int max_blocks, int page_size, const int* token_seq,
+                                 long n_pages, const int* page_table, int max_blocks, int page_size, const int* token_seq,
                                  const int* token_pos, const int* seq_slot, int n_tokens, int n_heads,
                                  int n_kv_heads, int head_dim, int window_kind, int window_size, float scale,
                                  int n_splits, cudaStream_t stream);

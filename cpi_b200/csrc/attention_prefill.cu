@@ -1,16 +1,19 @@
-// Prefill attention in bfloat16 on tcgen05: tiles of 128 queries of one head against the paged cache.
+// Prefill attention in bfloat16 on tcgen05: two tiles of 128 queries of one head against the paged cache.
 //
-// A CTA owns 128 consecutive tokens of one sequence and one query head.  Warp 8 streams key/value tiles
-// (128 positions = two cache pages, through TMA with the 128-byte swizzle, three stages each for keys and
-// values: a tile's load takes about as long as a tile's arithmetic, so it is requested two tiles ahead); one thread of
-// warp 9 issues the MMAs; warps 0-7 are the softmax: threads r and 128 + r own query row r (half of a
-// tile's key columns each), so row maxima and sums need no shuffles.  Per key tile:
+// A CTA owns up to 256 consecutive tokens of one sequence and one query head: query tile A (the first 128
+// rows) and query tile B (the rest).  Warp 8 streams key/value tiles (128 positions = two cache pages, through
+// TMA with the 128-byte swizzle) into a ring of five shared-memory slots, K(i), V(i), K(i+1), ...: both query
+// tiles use every key and value tile, so each is fetched once for 256 queries.  One thread of warp 9 issues
+// the MMAs; warps 0-3 are the softmax of tile A, warps 4-7 of tile B: thread r of a group owns query row r
+// and all 128 key columns of a tile, so row maxima and sums need no shuffles.  Per key tile and query tile:
 //     S = Q K^T            tcgen05.mma, both operands K-major from shared memory, S in tensor memory
-//                          (two S buffers: the MMAs run two tiles ahead of the softmax)
-//     P = 2^(S*c - m)      read S with tcgen05.ld, mask by position, write P as bf16 back into tensor memory
-//                          (two P buffers, so the softmax of tile i+1 does not wait for the P V of tile i)
+//     P = 2^(S*c - m)      read S with tcgen05.ld, mask by position, write P as bf16 over the first 64 columns
+//                          of the S it came from
 //     O += P V             tcgen05.mma with P as the A operand from tensor memory, accumulating in tensor
 //                          memory; V consumed MN-major straight from the page layout [position][dim]
+// Tensor memory holds S and O of both query tiles (4 x 128 columns).  The products of the two tiles alternate
+// in the issue order (P_A V, Q_A K'^T, P_B V, Q_B K'^T), so the tensor pipe works for one tile while the
+// other's softmax runs; the exponentials of a tile (16,384 on 16 per cycle) take as long as its two products.
 // m is a reference maximum that is raised, and O rescaled in tensor memory, only when the row maximum
 // has outgrown it by 2^8; the division by the row sum comes once, at the end.
 // Masks: key position <= query position, and >= the window's low end (chunk or sliding window).  The
@@ -201,6 +204,8 @@ __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.
 // outgrown it by more than this many powers of two; the accumulated output then needs rescaling only
 // then (rarely after the first tiles), and intermediate values stay below 2^kRescaleSlack.
 constexpr float kRescaleSlack = 8.0f;
+constexpr int kRingSlots = 5;           // key and value tiles in shared memory at a time
+constexpr int kTileRows = 2 * BQ;       // query rows a CTA takes: two tiles of 128
 
 template <int D>
 __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_constant__ CUtensorMap map_q,
@@ -208,43 +213,44 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
                                                                 const __grid_constant__ CUtensorMap map_v, Params p) {
   constexpr int HALVES = D / 64;                       // 64-element (128-byte) column blocks of a row
   constexpr uint32_t HALF_BYTES = 128 * 128;           // 128 rows x 128 bytes
-  constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES;
+  constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES;    // one query tile of 128 rows
   constexpr uint32_t KV_BYTES = HALVES * HALF_BYTES;   // one of K or V, 128 positions
-  constexpr uint32_t TMEM_COLS = 512;                  // S twice (128 columns each), O (D columns), P twice (64 each)
-  constexpr int KS = 3;                                // stages of K and of V
+  constexpr uint32_t TMEM_COLS = 512;                  // S of tile A, S of tile B (128 columns each), O of A, O of B
+  constexpr int NSLOT = kRingSlots;                    // ring of key and value tiles: K(i), V(i), K(i+1), ...
   // (aligned by declaration: with head size 128 the tiles fill what an SM has, there is no room for slack)
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  __shared__ uint64_t q_full, k_full[KS], k_empty[KS], v_full[KS], v_empty[KS], s_full[2], p_full[2], o_done[2];
+  __shared__ uint64_t q_full, kv_full[NSLOT], kv_empty[NSLOT], s_full[2], p_full[2], o_done[2];
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s;
-  __shared__ float xch_s[1][2][128];                   // the two halves of a row add their sums at the end
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  uint8_t* smem = smem_raw;
-  uint8_t* q_s = smem;
-  uint8_t* k_s = q_s + Q_BYTES;                        // [KS stages]
-  uint8_t* v_s = k_s + KS * KV_BYTES;                  // [KS stages]
+  uint8_t* q_s = smem_raw;                             // [2 query tiles]
+  uint8_t* ring = q_s + 2 * Q_BYTES;                   // [NSLOT]
 
   pdl_launch_dependents();
   pdl_wait();
-  const int tile = blockIdx.x, head = blockIdx.y;
+  const int tile = blockIdx.y, head = blockIdx.x;       // heads are the fast axis: all heads of the longest tile start first
   const int kvh = head / (p.n_heads / p.n_kv_heads);
   const int tok0 = p.tile_tok0[tile], rows = p.tile_rows[tile];
   const int slot = p.seq_slot[p.token_seq[tok0]];
+  // the tile's rows are consecutive positions of one sequence; rows 0-127 are query tile A, the rest tile B
   const int pos_first = p.token_pos[tok0], pos_last = pos_first + rows - 1;
-  const int lo_first = window_low(p.window_kind, p.window_size, pos_first);
-  const int kt_begin = lo_first / BKV, kt_end = pos_last / BKV + 1;
-  const int n_kt = kt_end - kt_begin;
+  const int rows_x[2] = {min(rows, BQ), max(rows - BQ, 0)};
+  const bool has_b = rows_x[1] > 0;
+  const int p0_x[2] = {pos_first, pos_first + BQ};                         // first position of A, of B
+  const int p1_x[2] = {pos_first + rows_x[0] - 1, pos_last};               // last position of A, of B
+  // key tiles (of 128 positions) that each query tile meets; the window's low end never decreases with the position
+  const int kb_x[2] = {window_low(p.window_kind, p.window_size, p0_x[0]) / BKV,
+                       has_b ? window_low(p.window_kind, p.window_size, p0_x[1]) / BKV : 0};
+  const int ke_x[2] = {p1_x[0] / BKV + 1, has_b ? p1_x[1] / BKV + 1 : 0};
+  const int kt0 = kb_x[0], kt1 = has_b ? ke_x[1] : ke_x[0];               // the union: every tile in it is met by A or B
 
   if (tid == 0) {
     mbar_init(&q_full, 1);
-    for (int s = 0; s < KS; ++s) {
-      mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1);
-      mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1);
-    }
+    for (int s = 0; s < NSLOT; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&s_full[s], 1);
-      mbar_init(&p_full[s], 8); mbar_init(&o_done[s], 1);
+      mbar_init(&p_full[s], 4); mbar_init(&o_done[s], 1);
     }
     abort_s = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -256,126 +262,147 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
   fence_before_sync();
   __syncthreads();
   fence_after_sync();
-  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256, tmem_p = tmem_base_s + 384;
+  const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 256;        // + 128 for tile B, both
   volatile int* abort_flag = &abort_s;
   bool ok = true;
 
   if (warp == 8) {
     if (lane == 0) {
-      // ---- TMA producer: keys and values have barriers of their own, so that the keys of tile i+2 can
-      //      come as soon as Q K^T of tile i is done, long before its P V ----
-      mbar_expect_tx(&q_full, Q_BYTES);
-      for (int h = 0; h < HALVES; ++h) tma_load_2d(q_s + h * HALF_BYTES, &map_q, &q_full, head * D + h * 64, tok0);
+      // ---- TMA producer: Q of both tiles, then K(kt0), V(kt0), K(kt0 + 1), ... through the ring ----
+      mbar_expect_tx(&q_full, Q_BYTES * (has_b ? 2 : 1));
+      for (int x = 0; x < (has_b ? 2 : 1); ++x)
+        for (int h = 0; h < HALVES; ++h)
+          tma_load_2d(q_s + x * Q_BYTES + h * HALF_BYTES, &map_q, &q_full, head * D + h * 64, tok0 + x * BQ);
       const int* table = p.page_table + (size_t)slot * p.max_blocks;
       const int last_block = pos_last / PAGE;
-      for (int i = 0; i < n_kt; ++i) {
-        const int s = i % KS;
-        const int blk0 = (kt_begin + i) * (BKV / PAGE);
+      int n = 0;                                         // item of the ring: 2 (kt - kt0) for keys, + 1 for values
+      for (int kt = kt0; kt < kt1 && ok; ++kt) {
+        const int blk0 = kt * (BKV / PAGE);
         const int n_pages = min(BKV / PAGE, last_block - blk0 + 1);
         const uint32_t bytes = (uint32_t)n_pages * HALVES * (PAGE * 128);
-        if (i >= KS && !mbar_wait(&k_empty[s], ((i / KS) - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(&k_full[s], bytes);
-        for (int pg = 0; pg < n_pages; ++pg) {
-          const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
-          for (int h = 0; h < HALVES; ++h)
-            tma_load_2d(k_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_k, &k_full[s], h * 64, row);
-        }
-        if (i >= KS && !mbar_wait(&v_empty[s], ((i / KS) - 1) & 1, abort_flag)) break;
-        mbar_expect_tx(&v_full[s], bytes);
-        for (int pg = 0; pg < n_pages; ++pg) {
-          const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
-          for (int h = 0; h < HALVES; ++h)
-            tma_load_2d(v_s + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), &map_v, &v_full[s], h * 64, row);
+        for (int which = 0; which < 2; ++which, ++n) {
+          const int s = n % NSLOT;
+          if (n >= NSLOT && !mbar_wait(&kv_empty[s], ((n / NSLOT) - 1) & 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&kv_full[s], bytes);
+          for (int pg = 0; pg < n_pages; ++pg) {
+            const int row = (table[blk0 + pg] * p.n_kv_heads + kvh) * PAGE;
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_2d(ring + s * KV_BYTES + h * HALF_BYTES + pg * (PAGE * 128), which ? &map_v : &map_k,
+                          &kv_full[s], h * 64, row);
+          }
         }
       }
     }
   } else if (warp == 9) {
-    // ---- MMA issuer.  Order: S(0), S(1), then for each tile  O += P V,  S(i+2).  The two S buffers let
-    //      Q K^T run two tiles ahead of the softmax; the tensor pipe executes in issue order.
-    //      This warp shares its scheduler with two softmax warps that always have something to issue, so
-    //      every instruction it spends between two MMAs delays the tensor pipe (measured: with descriptor
-    //      arithmetic, divisions by the stage count and a predicate per MMA, issuing a tile's 16 MMAs took
-    //      2.4 times as long as running them).  Hence: the whole warp runs the loop (uniform values), stage
-    //      and phase are counters, descriptors are built once and advanced by additions, and the accumulate
-    //      flags are compile-time. ----
+    // ---- MMA issuer.  Two query tiles share every key and value tile.  Per key tile kt:
+    //          O_A += P_A V(kt);  S_A = Q_A K(kt+1)^T;   O_B += P_B V(kt);  S_B = Q_B K(kt+1)^T
+    //      so that while the softmax threads of one query tile work on its S, the tensor pipe runs the other
+    //      tile's products.  P is written over the S it came from (as bf16, the first 64 columns) and is the
+    //      A operand of P V from tensor memory; the next Q K^T of the same query tile is issued after that
+    //      P V and the pipe runs in issue order, so it cannot overwrite a P that is still being read.
+    //      The whole warp runs the loop (uniform values stay on the uniform datapath); only the tcgen05
+    //      instructions sit under the elected lane. ----
     constexpr uint32_t idesc_s = instr_desc(BQ, BKV, 0);
     constexpr uint32_t idesc_o = instr_desc(BQ, D, 1);
-    constexpr uint64_t kStageUnits = KV_BYTES >> 4;     // a stage further, in the descriptor's 16-byte units
-    const uint64_t dq = smem_desc(smem_u32(q_s), 16, 1024);
-    const uint64_t dk0 = smem_desc(smem_u32(k_s), 16, 1024), dv0 = smem_desc(smem_u32(v_s), HALF_BYTES, 1024);
-    int qk_st = 0, qk_ph = 0;                            // stage and phase of the next Q K^T; likewise for P V
-    uint64_t dk = dk0;
-    auto issue_qk = [&](int s) -> bool {                 // s = S buffer
-      if (!__all_sync(0xffffffffu, mbar_wait(&k_full[qk_st], qk_ph, abort_flag))) return false;
+    constexpr uint64_t kSlotUnits = KV_BYTES >> 4;      // a ring slot further, in the descriptor's 16-byte units
+    const uint64_t dq[2] = {smem_desc(smem_u32(q_s), 16, 1024), smem_desc(smem_u32(q_s + Q_BYTES), 16, 1024)};
+    const uint64_t dk0 = smem_desc(smem_u32(ring), 16, 1024), dv0 = smem_desc(smem_u32(ring), HALF_BYTES, 1024);
+    // Everything the loop needs is a counter that is advanced by additions (this warp shares its scheduler with
+    // two softmax warps: every instruction between two MMAs is time the tensor pipe stands still).  Ring slot
+    // and phase of the next key tile and of the next value tile to be used, per query tile:
+    int ks[2], kph[2], vs[2], vph[2], pph[2] = {0, 0}, first_pv[2] = {1, 1};
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const int nk = 2 * (kb_x[x] - kt0), nv = nk + 1;
+      ks[x] = nk % NSLOT; kph[x] = (nk / NSLOT) & 1;
+      vs[x] = nv % NSLOT; vph[x] = (nv / NSLOT) & 1;
+    }
+    // S_x = Q_x K^T on the key tile in ring slot ks[x]; `release`: no later product reads that key tile
+    auto issue_qk = [&](int x, bool release) -> bool {
+      if (!__all_sync(0xffffffffu, mbar_wait(&kv_full[ks[x]], kph[x], abort_flag))) return false;
       fence_after_sync();
       if (elect_one()) {
-        umma_bf16_c<false>(tmem_s + s * 128, dq, dk, idesc_s);
+        const uint64_t dk = dk0 + (uint64_t)ks[x] * kSlotUnits;
+        umma_bf16_c<false>(tmem_s + x * 128, dq[x], dk, idesc_s);
 #pragma unroll
-        for (int ks = 1; ks < D / 16; ++ks) {
-          const uint64_t off = (uint64_t)(((ks >> 2) * HALF_BYTES + (ks & 3) * 32) >> 4);
-          umma_bf16_c<true>(tmem_s + s * 128, dq + off, dk + off, idesc_s);
+        for (int k = 1; k < D / 16; ++k) {
+          const uint64_t off = (uint64_t)(((k >> 2) * HALF_BYTES + (k & 3) * 32) >> 4);
+          umma_bf16_c<true>(tmem_s + x * 128, dq[x] + off, dk + off, idesc_s);
         }
-        umma_commit(&s_full[s]);
-        umma_commit(&k_empty[qk_st]);
+        umma_commit(&s_full[x]);
+        if (release) umma_commit(&kv_empty[ks[x]]);
       }
       __syncwarp();
-      if (++qk_st == KS) { qk_st = 0; qk_ph ^= 1; dk = dk0; } else { dk += kStageUnits; }
+      ks[x] += 2;                                        // the next key tile is two ring items further
+      if (ks[x] >= NSLOT) { ks[x] -= NSLOT; kph[x] ^= 1; }
+      return true;
+    };
+    // O_x += P_x V on the value tile in ring slot vs[x]
+    auto issue_pv = [&](int x, bool release) -> bool {
+      if (!__all_sync(0xffffffffu, mbar_wait(&p_full[x], pph[x], abort_flag) &&
+                                       mbar_wait(&kv_full[vs[x]], vph[x], abort_flag))) return false;
+      fence_after_sync();
+      if (elect_one()) {
+        const uint64_t dv = dv0 + (uint64_t)vs[x] * kSlotUnits;
+        const uint32_t pa = tmem_s + x * 128, od = tmem_o + x * 128;
+        if (first_pv[x]) umma_bf16_a_tmem_c<false>(od, pa, dv, idesc_o);
+        else umma_bf16_a_tmem_c<true>(od, pa, dv, idesc_o);
+#pragma unroll
+        for (int j = 1; j < BKV / 16; ++j)
+          umma_bf16_a_tmem_c<true>(od, pa + j * 8, dv + (uint64_t)(j * (2048 >> 4)), idesc_o);
+        umma_commit(&o_done[x]);
+        if (release) umma_commit(&kv_empty[vs[x]]);
+      }
+      __syncwarp();
+      first_pv[x] = 0;
+      pph[x] ^= 1;
+      vs[x] += 2;
+      if (vs[x] >= NSLOT) { vs[x] -= NSLOT; vph[x] ^= 1; }
       return true;
     };
     ok = __all_sync(0xffffffffu, mbar_wait(&q_full, 0, abort_flag));
-    ok = ok && issue_qk(0);
-    if (ok && n_kt > 1) ok = issue_qk(1);
-    int pv_st = 0, pv_ph = 0, sp_ph = 0;                 // sp_ph: phase of the S / P buffer pair
-    uint64_t dv = dv0;
-    for (int i = 0; i < n_kt && ok; ++i) {
-      const int s = i & 1;
-      ok = __all_sync(0xffffffffu, mbar_wait(&p_full[s], sp_ph, abort_flag) && mbar_wait(&v_full[pv_st], pv_ph, abort_flag));
-      if (!ok) break;
-      fence_after_sync();
-      if (elect_one()) {
-        const uint32_t pa = tmem_p + s * 64;
-        if (i > 0) umma_bf16_a_tmem_c<true>(tmem_o, pa, dv, idesc_o);
-        else umma_bf16_a_tmem_c<false>(tmem_o, pa, dv, idesc_o);
-#pragma unroll
-        for (int j = 1; j < BKV / 16; ++j)
-          umma_bf16_a_tmem_c<true>(tmem_o, pa + j * 8, dv + (uint64_t)(j * (2048 >> 4)), idesc_o);
-        umma_commit(&o_done[s]);
-        umma_commit(&v_empty[pv_st]);
+    const int kb_b = has_b ? kb_x[1] : 0x7fffffff, ke_a = ke_x[0];
+    ok = ok && issue_qk(0, kb_b != kt0);
+    if (ok && kb_b == kt0) ok = issue_qk(1, true);
+    for (int kt = kt0; kt < kt1 && ok; ++kt) {
+      // which query tiles meet key tile kt, and kt + 1 (B's range ends with the union's, A's begins with it)
+      const bool a_now = kt < ke_a, b_now = kt >= kb_b;
+      const bool a_next = kt + 1 < ke_a, b_next = kt + 1 >= kb_b && kt + 1 < kt1;
+      if (a_now) {
+        ok = issue_pv(0, !b_now);
+        if (ok && a_next) ok = issue_qk(0, !b_next);
       }
-      __syncwarp();
-      if (++pv_st == KS) { pv_st = 0; pv_ph ^= 1; dv = dv0; } else { dv += kStageUnits; }
-      sp_ph ^= s;                                        // both buffers of the pair done: next phase
-      if (i + 2 < n_kt) ok = issue_qk(s);                // S[s] is free: the softmax of tile i has read it
+      if (ok && b_now) ok = issue_pv(1, true);
+      if (ok && b_next) ok = issue_qk(1, true);
     }
   } else {
-    // ---- softmax: eight warps.  Query row r belongs to threads r and 128 + r; the first takes the key
-    //      columns 0-63 of a tile, the second 64-127 (a warp may touch the 32 lanes of tensor memory given
-    //      by its number modulo 4, so warps w and w + 4 share rows).  Two warps per scheduler hide each
-    //      other's latencies.  Each half reads the whole row for its maximum, so the halves need not meet
-    //      until the row sums are added at the end.  O stays in tensor memory. ----
-    const int row = tid & 127, half = tid >> 7;
-    const bool live = row < rows;
-    const int qp = live ? p.token_pos[tok0 + row] : -1;
+    // ---- softmax: warps 0-3 own query tile A, warps 4-7 tile B; thread r of a group owns query row r and all
+    //      128 key columns of a tile (a warp may touch the 32 lanes of tensor memory given by its number modulo
+    //      4).  Row maxima and sums need no shuffles, and the maximum is exact before any exponential is taken.
+    //      O stays in tensor memory and is rescaled only when a row maximum has outgrown its reference. ----
+    const int x = warp >> 2, row = tid & 127;
+    const bool live = row < rows_x[x];
+    const int qp = live ? p0_x[x] + row : -1;
     const int lo = live ? window_low(p.window_kind, p.window_size, qp) : 0;
+    const int lo_last = window_low(p.window_kind, p.window_size, p1_x[x]);
     const uint32_t lane_addr = (uint32_t)((warp & 3) * 32) << 16;
-    constexpr int HC = BKV / 2;                         // key columns of a tile per thread
-    const int c0 = half * HC;
-    float m_ref = -1e30f, l_run = 0.f;                  // reference maximum of the exponentials; this half's row sum
+    const uint32_t s_row = tmem_s + x * 128 + lane_addr, o_row = tmem_o + x * 128 + lane_addr;
+    float m_ref = -1e30f, l_run = 0.f;                  // reference maximum of the exponentials; the row's sum
     const float sc = p.scale_log2;                      // > 0: the maximum may be taken before scaling
-    const int lo_last = window_low(p.window_kind, p.window_size, pos_last);
-    for (int i = 0; i < n_kt; ++i) {
-      const int key0 = (kt_begin + i) * BKV;
-      const uint32_t s_row = tmem_s + (i & 1) * 128 + lane_addr;
-      const uint32_t p_addr = tmem_p + (i & 1) * 64 + lane_addr + (c0 >> 1);
+    // the union's last key tile holds positions beyond the newest one: their value rows are zeroed by the group
+    // whose P V on that tile is issued first (A if it meets the tile, otherwise B)
+    const bool zero_duty = x == 0 ? (kt1 - 1 >= kb_x[0] && kt1 - 1 < ke_x[0]) : !(kt1 - 1 >= kb_x[0] && kt1 - 1 < ke_x[0]);
+    int j = 0;
+    bool okl = rows_x[x] > 0;
+    for (int kt = kb_x[x]; kt < ke_x[x] && okl; ++kt, ++j) {
+      const int key0 = kt * BKV;
       // (tensor-memory loads and votes are warp-wide: a warp gives up as a whole)
-      bool okl = __all_sync(0xffffffffu, mbar_wait(&s_full[i & 1], (i >> 1) & 1, abort_flag));
-      // this tile's P buffer was last read by P V of tile i - 2
-      if (okl && i >= 2) okl = __all_sync(0xffffffffu, mbar_wait(&o_done[i & 1], ((i >> 1) - 1) & 1, abort_flag));
-      // the last tile: zero the value rows beyond the newest position (thread r of the first half: key row r)
-      if (okl && i == n_kt - 1 && half == 0) {
-        okl = __all_sync(0xffffffffu, mbar_wait(&v_full[i % KS], (i / KS) & 1, abort_flag));
+      okl = __all_sync(0xffffffffu, mbar_wait(&s_full[x], j & 1, abort_flag));
+      if (okl && kt == kt1 - 1 && zero_duty) {
+        const int n = 2 * (kt - kt0) + 1, sl = n % NSLOT;
+        okl = __all_sync(0xffffffffu, mbar_wait(&kv_full[sl], (n / NSLOT) & 1, abort_flag));
         if (okl && key0 + row > pos_last) {
-          uint8_t* vs = v_s + (i % KS) * KV_BYTES;
+          uint8_t* vs = ring + sl * KV_BYTES;
 #pragma unroll
           for (int h = 0; h < HALVES; ++h) {
             uint4* r4 = reinterpret_cast<uint4*>(vs + h * HALF_BYTES + row * 128);
@@ -385,107 +412,97 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
         }
         fence_async_proxy();                             // the MMA reads V through the async proxy
       }
+      if (!okl) break;
       fence_after_sync();
-      // One pass over this thread's half of S: P = 2^(s*c - m_ref) as bf16 into tensor memory, the sum, and
-      // the maximum.  A tile that lies wholly inside every row's window needs no position tests.
-      const bool no_mask = key0 + BKV - 1 <= pos_first && key0 >= lo_last;
-      float mx = -INFINITY, ls = 0.f;
+      // a tile that lies wholly inside every row's window needs no position tests
+      const bool no_mask = key0 + BKV - 1 <= p0_x[x] && key0 >= lo_last;
+      // One pass over the row's 128 columns of S, 32 at a time with the next chunk's load in flight: the
+      // maximum, P = 2^(s c - ref) as packed bf16, and the sum.  P is kept in registers until the pass is
+      // known to stand, because it goes over the S it came from.
+      uint32_t w[BKV / 32][16];
+      float mx, ls;
       auto pass = [&](const float ref) {
         const float nref = -ref;
         float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY}, ls4[4] = {0.f, 0.f, 0.f, 0.f};
-        uint32_t raw[BKV / 32][32];
-        // The whole row is read for its maximum (so that the two halves of a row decide alike without
-        // talking to each other: no barrier per tile, and the halves drift apart, one's exponentials
-        // under the other's waits), the exponentials are taken of this thread's half only.  Chunk order:
-        // the other half's two chunks first, then this half's.
-        const int first = (half ^ 1) * HC;
-        // all four loads go out together: their latencies overlap, and one wait covers them
-#pragma unroll
-        for (int cc = 0; cc < BKV / 32; ++cc) tmem_ld32_issue(s_row + (cc < 2 ? first : c0) + (cc & 1) * 32, raw[cc]);
+        uint32_t raw[2][32];
+        tmem_ld32_issue(s_row, raw[0]);
+        tmem_ld32_issue(s_row + 32, raw[1]);
         tmem_wait_ld();
 #pragma unroll
         for (int cc = 0; cc < BKV / 32; ++cc) {
-          const int c = ((cc < 2 ? first : c0) + (cc & 1) * 32);     // column of this chunk within the tile
           float v[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) v[e] = __uint_as_float(raw[cc][e]);
           if (no_mask) {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
-            if (cc >= 2) {
-#pragma unroll
-              for (int e = 0; e < 32; ++e) v[e] = exp2_fast(fmaf(v[e], sc, nref));
+            for (int e = 0; e < 32; ++e) {
+              const float sv = __uint_as_float(raw[cc & 1][e]);
+              mx4[e & 3] = fmaxf(mx4[e & 3], sv);
+              v[e] = exp2_fast(fmaf(sv, sc, nref));
             }
           } else {
 #pragma unroll
             for (int e = 0; e < 32; ++e) {
-              const int kp = key0 + c + e;
+              const int kp = key0 + cc * 32 + e;
               const bool in = kp <= qp && kp >= lo;
-              if (in) mx4[e & 3] = fmaxf(mx4[e & 3], v[e]);
-              if (cc >= 2) v[e] = in ? exp2_fast(fmaf(v[e], sc, nref)) : 0.f;
+              const float sv = __uint_as_float(raw[cc & 1][e]);
+              if (in) mx4[e & 3] = fmaxf(mx4[e & 3], sv);
+              v[e] = in ? exp2_fast(fmaf(sv, sc, nref)) : 0.f;
             }
           }
-          if (cc >= 2) {
+          if (cc + 2 < BKV / 32) tmem_ld32_issue(s_row + (cc + 2) * 32, raw[cc & 1]);     // this buffer is consumed
 #pragma unroll
-            for (int e = 0; e < 32; ++e) ls4[e & 3] += v[e];
-            uint32_t w[16];
+          for (int e = 0; e < 32; ++e) ls4[e & 3] += v[e];
 #pragma unroll
-            for (int g = 0; g < 16; ++g) w[g] = pack_bf16(v[2 * g], v[2 * g + 1]);
-            tmem_st16_nowait(p_addr + ((cc & 1) * 16), w);
-          }
+          for (int g = 0; g < 16; ++g) w[cc][g] = pack_bf16(v[2 * g], v[2 * g + 1]);
+          if (cc == 1) tmem_wait_ld();
         }
         mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sc;
         ls = (ls4[0] + ls4[1]) + (ls4[2] + ls4[3]);
-        tmem_wait_st();
       };
       // Optimistic: against the reference maximum the row already has.  Only if some row of the warp has
-      // outgrown its reference (always on its first tile) is the reference raised, O rescaled in tensor
-      // memory, and the pass repeated.  Both halves of a row compute the same maximum and so decide alike.
-      if (!okl) break;
+      // outgrown its reference by more than the slack (always on its first tile) is the reference raised, O
+      // rescaled in tensor memory, and the pass repeated: S is still whole, nothing has been stored yet.
       pass(m_ref);
       const bool grow = mx > m_ref + (m_ref < -1e29f ? 0.f : kRescaleSlack);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_ref;
         const float f = exp2f(m_ref - m_new);
-        bool ok2 = true;
-        if (i > 0) {
-          // O is rescaled in place, half of its columns by each half: every P V issued so far must have landed
-          ok2 = __all_sync(0xffffffffu, mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag));
+        if (j > 0) {
+          // every P V issued so far for this query tile must have landed
+          okl = __all_sync(0xffffffffu, mbar_wait(&o_done[x], (j - 1) & 1, abort_flag));
+          if (!okl) break;
           fence_after_sync();
-          if (ok2) {
 #pragma unroll 1
-            for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
-              float v[32];
-              tmem_ld32(tmem_o + lane_addr + c, v);
+          for (int c = 0; c < D; c += 32) {
+            float v[32];
+            tmem_ld32(o_row + c, v);
 #pragma unroll
-              for (int e = 0; e < 32; ++e) v[e] *= f;
-              tmem_st32(tmem_o + lane_addr + c, v);
-            }
+            for (int e = 0; e < 32; ++e) v[e] *= f;
+            tmem_st32(o_row + c, v);
           }
         }
         l_run *= f;
         m_ref = m_new;
-        if (ok2) pass(m_ref);
+        pass(m_ref);
       }
+#pragma unroll
+      for (int cc = 0; cc < BKV / 32; ++cc) tmem_st16_nowait(s_row + cc * 16, w[cc]);
       l_run += ls;
+      tmem_wait_st();
       fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full[i & 1]);        // one arrival per warp
+      if (lane == 0) mbar_arrive(&p_full[x]);            // one arrival per warp
     }
-    // the output: O / l once the last P V is done; each half writes half of the columns
-    xch_s[0][half][row] = l_run;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const float l_all = xch_s[0][0][row] + xch_s[0][1][row];
-    ok = !abort_s && n_kt > 0;
-    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_done[(n_kt - 1) & 1], ((n_kt - 1) >> 1) & 1, abort_flag));
+    // the output: O / l once the last P V is done
+    ok = okl && !abort_s && j > 0;
+    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_done[x], (j - 1) & 1, abort_flag));
     fence_after_sync();
     if (ok) {
-      const float inv = 1.0f / fmaxf(l_all, 1e-20f);
-      __nv_bfloat16* dst = p.out + ((size_t)(tok0 + row) * p.n_heads + head) * D;
+      const float inv = 1.0f / fmaxf(l_run, 1e-20f);
+      __nv_bfloat16* dst = p.out + ((size_t)(tok0 + x * BQ + row) * p.n_heads + head) * D;
 #pragma unroll 1
-      for (int c = half * (D / 2); c < (half + 1) * (D / 2); c += 32) {
+      for (int c = 0; c < D; c += 32) {
         float v[32];
-        tmem_ld32(tmem_o + lane_addr + c, v);
+        tmem_ld32(o_row + c, v);
         if (live) {
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
@@ -512,14 +529,17 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
 
 using namespace cpi;
 
+extern "C" int cpi_attention_prefill_tile_rows() { return pre::kTileRows; }
+
 extern "C" int cpi_attention_prefill_supported(int n_heads, int n_kv_heads, int head_dim, int page_size) {
   if (n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
   return (head_dim == 64 || head_dim == 128) && page_size == pre::PAGE;
 }
 
 // q, out [T, NH*D] bfloat16; k_cache, v_cache [n_pages, NKV, 64, D] bfloat16 of one layer.
-// tile_tok0 / tile_rows (device, int32 [n_tiles]): first packed token and valid rows (1..128) of each query
-// tile; the tokens of a tile belong to one sequence and have consecutive positions.
+// tile_tok0 / tile_rows (device, int32 [n_tiles]): first packed token and valid rows (1..256, see
+// cpi_attention_prefill_tile_rows) of each CTA's queries; they belong to one sequence and have consecutive
+// positions.
 extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cache, const void* v_cache, long n_pages,
                                      const int* page_table, int max_blocks, int page_size, const int* token_seq,
                                      const int* token_pos, const int* seq_slot, const int* tile_tok0,
@@ -530,7 +550,7 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
   CPI_REQUIRE(cpi_attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size),
               "attention_prefill: unsupported shape (heads %d/%d, head size %d, page %d)", n_heads, n_kv_heads, head_dim, page_size);
   CPI_REQUIRE(window_kind == 0 || window_size > 0, "attention_prefill: window kind %d needs a size > 0", window_kind);
-  CPI_REQUIRE(n_heads <= 65535, "attention_prefill: too many heads");
+  CPI_REQUIRE(n_tiles <= 65535, "attention_prefill: too many query tiles in one launch (%d)", n_tiles);
   CUtensorMap mq, mk, mv;
   const uint64_t q_width = (uint64_t)n_heads * head_dim;
   if (tc::get_map_2d_bf16(q, q_width, (uint64_t)n_tokens, q_width * 2, 64, pre::BQ, &mq)) return 1;
@@ -539,9 +559,9 @@ extern "C" int cpi_attention_prefill(const void* q, void* out, const void* k_cac
   if (tc::get_map_2d_bf16(v_cache, (uint64_t)head_dim, kv_rows, (uint64_t)head_dim * 2, 64, pre::PAGE, &mv)) return 1;
   pre::Params p{(__nv_bfloat16*)out, page_table, max_blocks, token_pos, token_seq, seq_slot, tile_tok0, tile_rows,
                 n_heads, n_kv_heads, window_kind, window_size, scale * 1.4426950408889634f, error_flag};
-  dim3 grid(n_tiles, n_heads);
+  dim3 grid(n_heads, n_tiles);
   const int halves = head_dim / 64;
-  const int smem = halves * 128 * 128 * (1 + 6);             // Q, three stages of K and of V
+  const int smem = halves * 128 * 128 * (2 + pre::kRingSlots);     // Q of both tiles, the ring of K and V tiles
   if (head_dim == 128) {
     static bool set = false;
     if (!set) { cudaFuncSetAttribute(pre::attention_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); set = true; }

@@ -97,7 +97,7 @@ def case_attention_decode(a) -> None:
     out = torch.empty_like(q)
     seq = torch.arange(B, dtype=torch.int32, device=DEV)
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
-    base, slots, pages = B * NKV, 3 * 148, -(-ctx // 64)
+    base, slots, pages = B * NKV, K.attention_decode_blocks_per_sm(D) * K.sm_count(), -(-ctx // 64)
     splits = a.splits or max(1, min(slots // base if base <= slots else -(-4 * slots // base),
                                     pages // 4 if base > slots else pages // 2))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
@@ -117,7 +117,8 @@ def case_attention_prefill(a) -> None:
     seq = torch.zeros(T, dtype=torch.int32, device=DEV)
     pos = torch.arange(T, dtype=torch.int32, device=DEV)
     slot = torch.zeros(1, dtype=torch.int32, device=DEV)
-    tiles = [(t0, min(128, T - t0)) for t0 in range(0, T, 128)][::-1]
+    R = K.PREFILL_TILE_ROWS
+    tiles = [(t0, min(R, T - t0)) for t0 in range(0, T, R)][::-1]
     tok0 = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device=DEV)
     rows = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device=DEV)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)

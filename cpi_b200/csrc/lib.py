@@ -17,6 +17,7 @@ MODE_STORE, MODE_ADD, MODE_SWIGLU = 0, 1, 2
 WINDOW_FULL, WINDOW_CHUNK, WINDOW_SLIDING = 0, 1, 2
 WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SLIDING}
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
+PREFILL_TILE_ROWS = 256          # most query rows of one sequence that a block of the prefill attention kernel takes
 
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
@@ -323,10 +324,16 @@ def attention_decode(q, out, k_cache, v_cache, page_table, page_size, token_seq,
             _dec_scratch[idx] = buf
             scratch_generation += 1
         po, pml = buf, buf[T * n_heads * n_splits * head_dim:]
-    _call("cpi_attention_decode", _p(q), _p(out), _p(k_cache), _p(v_cache), _p(page_table),
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.shape == v_cache.shape
+    _call("cpi_attention_decode", _p(q), _p(out), _p(k_cache), _p(v_cache), c_long(k_cache.shape[0]), _p(page_table),
           c_int(page_table.shape[1]), c_int(page_size), _p(token_seq), _p(token_pos), _p(seq_slot), c_int(T),
           c_int(n_heads), c_int(n_kv_heads), c_int(head_dim), c_int(window_kind), c_int(window_size), c_float(scale),
-          c_int(n_splits), _p(po), _p(pml), _stream())
+          c_int(n_splits), _p(po), _p(pml), _p(tc_error_flag(q.device)), _stream())
+
+
+def attention_decode_blocks_per_sm(head_dim: int) -> int:
+    """Blocks of the decode attention kernel that share an SM."""
+    return int(load().cpi_attention_decode_blocks_per_sm(c_int(head_dim)))
 
 
 def attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size) -> bool:
@@ -336,7 +343,7 @@ def attention_prefill_supported(n_heads, n_kv_heads, head_dim, page_size) -> boo
 
 def attention_prefill(q, out, k_cache, v_cache, page_table, page_size, token_seq, token_pos, seq_slot, tile_tok0,
                       tile_rows, *, n_heads, n_kv_heads, head_dim, window_kind, window_size, scale):
-    """bfloat16 attention of query tiles (<= 128 consecutive tokens of one sequence each) on tcgen05."""
+    """bfloat16 attention of query tiles (<= PREFILL_TILE_ROWS consecutive tokens of one sequence each) on tcgen05."""
     _need_cuda(q, out, k_cache, v_cache, page_table, token_seq, token_pos, seq_slot, tile_tok0, tile_rows)
     assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
     assert q.dtype == out.dtype == k_cache.dtype == torch.bfloat16
@@ -407,6 +414,7 @@ def moe_lists(topk_idx, topk_gate, group_offsets, row_token, row_scale, row_of_s
 
 
 def moe_combine(residual, y, row_of_slot, *, top_k):
+    """residual[t] += y[row_of_slot[t, 0]] + ... + y[row_of_slot[t, top_k - 1]]."""
     _need_cuda(residual, y, row_of_slot)
     T, H = residual.shape
     assert residual.dtype == torch.float32 and residual.is_contiguous() and y.is_contiguous()

@@ -13,7 +13,7 @@ from dataclasses import dataclass
 import torch
 
 
-Q_TILE = 128      # query rows per tile of the prefill attention kernel
+from ..csrc.lib import PREFILL_TILE_ROWS as Q_TILE      # query rows that one block of the prefill attention kernel takes
 
 
 @dataclass
@@ -34,7 +34,7 @@ class StepBatch:
     starts: list
     n_new: list
     ctx_bucket: int = 0                # an upper bound of the longest context, a power of two (sizes key splits)
-    n_q_tiles: int = 0                 # prefill only: tiles of up to 128 consecutive tokens of one sequence,
+    n_q_tiles: int = 0                 # prefill only: tiles of up to Q_TILE consecutive tokens of one sequence,
     tile_tok0: torch.Tensor = None     # first packed token of each tile, longest context first
     tile_rows: torch.Tensor = None     # tokens in each tile
 

@@ -129,7 +129,8 @@ class AttentionMixer(Mixer):
             if self.window_kind != "full":
                 longest = min(longest, self.window_size + page_size)
             pages = -(-longest // page_size)
-            base, slots = batch.n_tokens * self.nkv, 3 * K.sm_count()       # three blocks fit an SM
+            base = batch.n_tokens * self.nkv
+            slots = K.attention_decode_blocks_per_sm(self.d) * K.sm_count()     # blocks that run at once
             if base <= slots:
                 want = slots // base                                # one full wave and no more
             else:

@@ -380,7 +380,7 @@ def test_compare_logits_measures():
 
 def test_step_batch_layout_on_the_host():
     """What a step's index arrays hold for an unequal batch: packed tokens, each token's sequence and
-    position, wanted rows as packed indices, and the query tiles of a prefill (128 tokens of one sequence
+    position, wanted rows as packed indices, and the query tiles of a prefill (256 tokens of one sequence
     at most, the tile with the most keys first)."""
     import torch
     from cpi_b200.engine.batch import BatchStager
@@ -396,10 +396,10 @@ def test_step_batch_layout_on_the_host():
     assert b.seq_slot.tolist() == slots and b.seq_start.tolist() == starts and b.seq_new.tolist() == [300, 3, 130]
     assert b.want_rows.tolist() == [0, 299, 303 + 129]
     tiles = list(zip(b.tile_tok0.tolist(), b.tile_rows.tolist()))
-    assert sorted(tiles) == [(0, 128), (128, 128), (256, 44), (300, 3), (303, 128), (431, 2)]
+    assert sorted(tiles) == [(0, 256), (256, 44), (300, 3), (303, 130)]
     ends = [b.token_pos[t0 + r - 1].item() + 1 for t0, r in tiles]                   # keys each tile may see
-    assert ends == sorted(ends, reverse=True) and b.n_q_tiles == 6
-    assert b.ctx_bucket == 512 and st.bytes_staged == 4 * (3 * 433 + 3 * 3 + 3 + 2 * 6)
+    assert ends == sorted(ends, reverse=True) and b.n_q_tiles == 4
+    assert b.ctx_bucket == 512 and st.bytes_staged == 4 * (3 * 433 + 3 * 3 + 3 + 2 * 4)
     d = st.stage([4, 9], [300, 330], [[5], [6]], [[0], [0]], torch.float32)
     assert d.is_decode and d.n_q_tiles == 0 and d.token_pos.tolist() == [300, 330] and d.want_rows.tolist() == [0, 1]
     assert b.tokens.tolist() == toks[0] + toks[1] + toks[2]                         # the ring: the step before is intact

@@ -624,7 +624,7 @@ def test_attention_decode_far_key():
         assert torch.allclose(out.view(NH, D)[kvh * 5 + 2].float(), v[pg, kvh, off].float(), atol=2e-2)
 
 
-def _prefill_case(NH, NKV, D, window, seqs, seed=0):
+def _prefill_case(NH, NKV, D, window, seqs, seed=0, tile=128):
     """seqs: list of (cached positions before the step, new tokens).  Returns everything a launch needs."""
     page = 64
     lengths = [s + n for s, n in seqs]
@@ -639,8 +639,8 @@ def _prefill_case(NH, NKV, D, window, seqs, seed=0):
     for i, (s, n) in enumerate(seqs):
         token_seq += [i] * n
         token_pos += list(range(s, s + n))
-        for off in range(0, n, 128):
-            tiles.append((base + off, min(128, n - off)))
+        for off in range(0, n, tile):
+            tiles.append((base + off, min(tile, n - off)))
         base += n
     T = base
     q = rnd(T, NH * D, dtype=torch.bfloat16, seed=seed + 7)
@@ -651,11 +651,17 @@ def _prefill_case(NH, NKV, D, window, seqs, seed=0):
                 lengths=lengths, pos=token_pos, seq=token_seq)
 
 
+@pytest.mark.parametrize("tile", [256, 128, 200])
 @pytest.mark.parametrize("NH,NKV,D,window", [(4, 2, 128, ("full", 0)), (6, 6, 64, ("chunk", 200)),
                                              (5, 1, 128, ("sliding", 130)), (8, 2, 64, ("chunk", 128))])
-def test_attention_prefill_tensor_core_kernel(NH, NKV, D, window):
+def test_attention_prefill_tensor_core_kernel(NH, NKV, D, window, tile):
+    """Query tiles of up to 256 rows (two tiles of 128 per block), of exactly 128 (the second tile absent) and of 200
+    (a ragged second tile), against sequences that start on a filled cache, in the middle of a page and of a key
+    tile, with windows whose low end falls between the two query tiles."""
     page = 64
-    c = _prefill_case(NH, NKV, D, window, [(0, 1), (0, 129), (0, 300), (70, 200), (256, 64), (0, 64)])
+    assert K().load().cpi_attention_prefill_tile_rows() == K().PREFILL_TILE_ROWS == 256
+    c = _prefill_case(NH, NKV, D, window, [(0, 1), (0, 129), (0, 300), (70, 200), (256, 64), (0, 64), (100, 700),
+                                           (130, 256)], tile=tile)
     out = torch.full_like(c["q"], float("nan"))
     wk, wsz = window
     scale = 1.0 / math.sqrt(D)

@@ -40,7 +40,8 @@ def _call_noalloc(lib, c, out, n_splits, window=(0, 0)):
     fn = lib.cpi_attention_decode_noalloc
     fn.restype = c_int
     p = lambda t: c_void_p(t.data_ptr())
-    return fn(p(c["q"]), p(out), p(c["k"]), p(c["v"]), p(c["table"]), c_int(c["table"].shape[1]), c_int(c["page"]),
+    return fn(p(c["q"]), p(out), p(c["k"]), p(c["v"]), c_long(c["k"].shape[0]), p(c["table"]),
+              c_int(c["table"].shape[1]), c_int(c["page"]),
               p(c["token_seq"]), p(c["token_pos"]), p(c["seq_slot"]), c_int(c["q"].shape[0]), c_int(c["NH"]),
               c_int(c["NKV"]), c_int(c["D"]), c_int(window[0]), c_int(window[1]), c_float(c["D"] ** -0.5),
               c_int(n_splits), c_void_p(torch.cuda.current_stream().cuda_stream))
