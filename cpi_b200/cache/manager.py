@@ -6,11 +6,13 @@ src/engine/llama4_cuda_engine.cu:258-265).  Here:
 
 * A **slot** stands for one live sequence: its length and, per group, its row of the page table.
   Slots come from a free list, go back when the sequence ends, and are used again.
-* Keys and values live in **pages** of `page_size` positions.  Run entries whose mixers declare equal
-  needs (same heads, head size and window) form a **group** with storage, page table and free list of
-  its own: `k, v [entries, pages, kv heads, page_size, head_dim]`.  A sequence's block b (positions
-  b*page_size ...) is page `table[slot, b]` of its group.  Nothing is zeroed: positions at or beyond a
-  sequence's length are never read.
+* What a mixer keeps per position lives in **pages** of `page_size` positions.  Run entries whose mixers
+  declare equal needs (same streams, same window) form a **group** with storage, page table and free
+  list of its own.  A group stores one tensor per **stream** that its requirement names:
+  `[entries, pages, heads, page_size, dim]`; attention's two streams are "k" and "v" of equal shape, a
+  mixer that keeps something else per position (one compressed vector, say) names its own streams with
+  their own shapes.  A sequence's block b (positions b*page_size ...) is page `table[slot, b]` of its
+  group, for every stream alike.  Positions at or beyond a sequence's length are never read.
 * A group with a window gives back, at the start of a step, the blocks that no later position can
   see (all positions before the chunk that holds the sequence's next position, or before the last
   `size` positions).
@@ -37,11 +39,16 @@ class CacheFull(CacheError):
 
 @dataclass(frozen=True)
 class KVRequirement:
-    """What an attention-like mixer keeps per position."""
+    """What a mixer keeps per position.  By default two streams, "k" and "v", of `n_kv_heads` heads of
+    `head_dim` elements; `streams` names others instead: a tuple of (name, heads, dim)."""
     n_kv_heads: int
     head_dim: int
     window_kind: str = "full"       # "full" | "chunk" | "sliding"
     window_size: int = 0
+    streams: tuple = ()             # () = (("k", n_kv_heads, head_dim), ("v", n_kv_heads, head_dim))
+
+    def stream_shapes(self) -> tuple:
+        return self.streams or (("k", self.n_kv_heads, self.head_dim), ("v", self.n_kv_heads, self.head_dim))
 
     def first_needed_position(self, next_pos: int) -> int:
         """Smallest position that a query at `next_pos` or later can still see."""
@@ -93,10 +100,14 @@ class KVGroup:
         self.req, self.entries = req, list(entries)
         self.page_size, self.max_blocks = page_size, max_blocks
         self.pool = PagePool(n_pages)
-        shape = (len(entries), n_pages, req.n_kv_heads, page_size, req.head_dim)
         # zeroed once: a tensor-core kernel multiplies masked positions by zero, which needs finite values
-        self.k = torch.zeros(shape, dtype=dtype, device=device)
-        self.v = torch.zeros(shape, dtype=dtype, device=device)
+        self.streams = {}
+        for name, heads, dim in req.stream_shapes():
+            if name in self.streams:
+                raise CacheError(f"a cache requirement names the stream '{name}' twice")
+            self.streams[name] = torch.zeros((len(entries), n_pages, int(heads), page_size, int(dim)), dtype=dtype,
+                                             device=device)
+        self.k, self.v = self.streams.get("k"), self.streams.get("v")
         self.table_host = torch.zeros((max_slots, max_blocks), dtype=torch.int32)
         self.table = torch.zeros((max_slots, max_blocks), dtype=torch.int32, device=device)
         self.blocks: list[dict] = [dict() for _ in range(max_slots)]     # slot -> {block: page}
@@ -104,8 +115,15 @@ class KVGroup:
         self._index = {e: i for i, e in enumerate(self.entries)}
 
     def layer_views(self, entry: int):
+        if self.k is None or self.v is None:
+            raise CacheError(f"run entry {entry} keeps the streams {sorted(self.streams)}, not keys and values")
         i = self._index[entry]
         return self.k[i], self.v[i]
+
+    def stream_view(self, entry: int, name: str):
+        if name not in self.streams:
+            raise CacheError(f"run entry {entry} keeps the streams {sorted(self.streams)}, not '{name}'")
+        return self.streams[name][self._index[entry]]
 
     def ensure(self, slot: int, length: int, n_new: int) -> None:
         """Free what the window no longer needs, then hold a page for every block of [length, length+n_new)."""
@@ -272,6 +290,11 @@ class CacheManager:
         g = self.group_of_entry[entry]
         k, v = g.layer_views(entry)
         return k, v, g.table, g.page_size
+
+    def stream_view(self, entry: int, name: str):
+        """(tensor [pages, heads, page_size, dim], page_table, page_size) of one named stream of run entry `entry`."""
+        g = self.group_of_entry[entry]
+        return g.stream_view(entry, name), g.table, g.page_size
 
     def state_view(self, entry: int, name: str) -> torch.Tensor:
         return self.state[(entry, name)]

@@ -116,6 +116,11 @@ class CacheView:
         """(k, v, page_table, page_size): k, v are [pages, kv heads, page_size, head_dim]."""
         return self._m.kv_view(self._entry)
 
+    def stream(self, name: str):
+        """(tensor [pages, heads, page_size, dim], page_table, page_size) of a stream that the mixer's
+        `KVRequirement.streams` names (attention's are "k" and "v")."""
+        return self._m.stream_view(self._entry, name)
+
     def state(self, name: str) -> torch.Tensor:
         """[slots, *shape] tensor of the named per-sequence state."""
         return self._m.state_view(self._entry, name)

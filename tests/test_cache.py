@@ -159,3 +159,29 @@ def test_a_step_that_does_not_fit_takes_nothing():
     w.check_room([([s], [40]), ([s], [40]), ([s], [40])])
     with pytest.raises(CacheFull):
         w.check_room([([s], [120])])                              # one piece holds all its pages at once
+
+
+def test_a_group_stores_the_streams_its_requirement_names():
+    """Keys and values of equal shape are only the default: a mixer may keep one compressed vector per position,
+    or streams of unequal widths; its group stores exactly those, paged like any other."""
+    import torch
+    latent = KVRequirement(0, 0, streams=(("latent", 1, 24), ("rope_k", 1, 8)))
+    m = CacheManager({0: KVRequirement(2, 16), 1: latent, 2: latent}, {}, max_tokens=64, max_seqs=2, page_size=16,
+                     device="cpu", dtype=torch.float32)
+    assert len(m.groups) == 2
+    lat, table, page = m.stream_view(2, "latent")
+    assert lat.shape == (4, 1, 16, 24) and page == 16 and m.stream_view(1, "rope_k")[0].shape == (4, 1, 16, 8)
+    assert m.stream_view(1, "latent")[0].data_ptr() != lat.data_ptr()            # a layer of its own per run entry
+    assert m.stream_view(0, "k")[0].shape == (4, 2, 16, 16) and m.kv_view(0)[0].shape == (4, 2, 16, 16)
+    with pytest.raises(CacheError, match="latent"):
+        m.kv_view(1)
+    with pytest.raises(CacheError, match="'v'"):
+        m.stream_view(1, "v")
+    s = m.acquire()
+    m.prepare_step([s], [20]); m.commit_step([s], [20])
+    assert [g.pages_held() for g in m.groups] == [2, 2]
+    m.release(s)
+    m.check_consistency()
+    with pytest.raises(CacheError, match="twice"):
+        CacheManager({0: KVRequirement(0, 0, streams=(("a", 1, 4), ("a", 1, 4)))}, {}, max_tokens=16, page_size=16,
+                     device="cpu", dtype=torch.float32)

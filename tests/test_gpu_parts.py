@@ -488,3 +488,97 @@ def test_toy_position_that_biases_the_scores_and_one_the_mixer_refuses(dtype):
     e.check_device_errors()
     for got, want in rows:
         assert float((got - want).abs().max()) <= tol
+
+
+def test_toy_mixer_with_one_latent_stream_per_position_registers_builds_and_steps():
+    """A mixer that keeps neither keys nor values but ONE compressed vector per position (a stream of its own
+    name and width in the paged cache) and attends over those: defined here, registered, built and stepped without
+    a change to the library: whole prompts, an unequal batch, prompt tokens on a filled cache, decoding, and a
+    second round in the slots and pages that the first gave back."""
+    from cpi_b200.cache import KVRequirement
+    from cpi_b200.config import LayerSpec, ModelSpec, PartSpec, RunEntry
+    from cpi_b200.engine import Engine, StepEntry
+    from cpi_b200.engine.model import tensor_requirements
+    from cpi_b200.parts import Mixer, register_mixer
+    from cpi_b200.weights import DictSource, RandomSource, TensorReq
+    H, V, I, L, NH = 48, 70, 64, 24, 3
+
+    @register_mixer("toy_latent_attention")
+    class LatentAttention(Mixer):
+        def __init__(self, spec, prefix="", workspace=None, owns_cache=True):
+            super().__init__(spec, prefix)
+
+        def requirements(self):
+            return [TensorReq(self.prefix + "lat.down", (L, H)), TensorReq(self.prefix + "lat.q", (NH * L, H)),
+                    TensorReq(self.prefix + "lat.out", (H, NH * L))]
+
+        def load(self, source, device):
+            self.wd, self.wq, self.wo = (source.get(self.prefix + n, device).float() for n in ("lat.down", "lat.q", "lat.out"))
+
+        def kv_requirement(self):
+            return KVRequirement(0, 0, streams=(("latent", 1, L),))
+
+        def forward(self, h, residual, batch, cache):
+            pages, table, page = cache.stream("latent")                 # [pages, 1, page, L]
+            x = h.float()
+            off = 0
+            for slot, start, n in zip(batch.slots, batch.starts, batch.n_new):
+                pos = torch.arange(start, start + n, device=h.device)
+                pg = table[slot, (pos // page).long()].long()
+                pages[pg, 0, (pos % page).long()] = (x[off:off + n] @ self.wd.T).to(pages.dtype)
+                allp = torch.arange(0, start + n, device=h.device)
+                c = pages[table[slot, (allp // page).long()].long(), 0, (allp % page).long()].float()   # [start + n, L]
+                q = (x[off:off + n] @ self.wq.T).view(n, NH, L)
+                s = torch.einsum("nhl,tl->nht", q, c) * L ** -0.5
+                s = s.masked_fill(allp[None, None, :] > pos[:, None, None], float("-inf"))
+                o = torch.einsum("nht,tl->nhl", torch.softmax(s, -1), c).reshape(n, NH * L)
+                residual[off:off + n] += o @ self.wo.T
+                off += n
+
+    norm = lambda w: PartSpec("rmsnorm", {"size": H, "eps": 1e-5, "weight": w})
+    layers = tuple(LayerSpec(prefix=f"l{i}.", block=PartSpec("pre_norm"), mixer=PartSpec("toy_latent_attention", {}),
+                             feed_forward=PartSpec("dense_swiglu", {"hidden_size": H, "intermediate_size": I}),
+                             mixer_norm=norm("n1.weight"), feed_forward_norm=norm("n2.weight")) for i in range(2))
+    spec = ModelSpec(architecture="ToyLatent", hidden_size=H, vocab_size=V,
+                     embedding=PartSpec("token_embedding", {"weight": "emb.weight"}), layers=layers,
+                     run_order=(RunEntry(0), RunEntry(1)), final_norm=norm("norm.weight"),
+                     head=PartSpec("linear_head", {"weight": "emb.weight"}), initializer_range=0.15)
+    src = RandomSource(tensor_requirements(spec), 6, 0.15)
+    drawn = {n: src.get(n, "cpu") for n in src.names()}
+    W = {n: t.float() for n, t in drawn.items()}
+    e = Engine(spec, DictSource(drawn), dtype="float32", max_tokens=256)
+    assert len(e.cache.groups) == 1 and sorted(e.cache.groups[0].streams) == ["latent"]
+    assert e.cache.groups[0].streams["latent"].shape == (2, 4, 1, 64, L)
+
+    def plain(tokens):
+        n = len(tokens)
+        x = W["emb.weight"][tokens]
+        causal = torch.arange(n)[None, :] <= torch.arange(n)[:, None]
+        for i in range(2):
+            h = P.rmsnorm(x, W[f"l{i}.n1.weight"], 1e-5)
+            c = h @ W[f"l{i}.lat.down"].T
+            q = (h @ W[f"l{i}.lat.q"].T).view(n, NH, L)
+            s = torch.einsum("nhl,tl->nht", q, c) * L ** -0.5
+            s = s.masked_fill(~causal[:, None, :], float("-inf"))
+            x = x + torch.einsum("nht,tl->nhl", torch.softmax(s, -1), c).reshape(n, NH * L) @ W[f"l{i}.lat.out"].T
+            h2 = P.rmsnorm(x, W[f"l{i}.n2.weight"], 1e-5)
+            f = f"l{i}.feed_forward."
+            x = x + P.swiglu_mlp(h2, W[f + "gate_proj.weight"], W[f + "up_proj.weight"], W[f + "down_proj.weight"])
+        return P.rmsnorm(x, W["norm.weight"], 1e-5) @ W["emb.weight"].T
+
+    a, b = tiny.random_tokens(100, V, 1), tiny.random_tokens(12, V, 2)
+    ra, rb = plain(a), plain(b)
+    tol = 2e-5 * float(ra.abs().max())
+    for round_ in range(2):
+        sa, sb = e.acquire_slot(), e.acquire_slot()
+        out = e.step([StepEntry(sa, a[:60], [0, 59]), StepEntry(sb, b[:9], [8])]).cpu()
+        rows = [(out[0], ra[0]), (out[1], ra[59]), (out[2], rb[8])]
+        out = e.step([StepEntry(sa, a[60:90], [0, 29]), StepEntry(sb, [b[9]], [0])]).cpu()     # across a page boundary
+        rows += [(out[0], ra[60]), (out[1], ra[89]), (out[2], rb[9])]
+        e.release_slot(sb)
+        for t in range(90, 100):
+            rows.append((e.step([StepEntry(sa, [a[t]], [0])]).cpu()[0], ra[t]))
+        e.release_slot(sa)
+        e.cache.check_consistency()
+        for got, want in rows:
+            assert float((got - want).abs().max()) <= tol
