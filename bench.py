@@ -21,6 +21,8 @@ For N > 1 GPUs it prints one line that says the library is single-GPU and exits 
 `phases` holds device milliseconds per phase of one prefill of 2,048 tokens and of one decode step, taken
 after everything else with the steps run eagerly on one stream (so their sum exceeds the step times above).
 
+`--workload contexts`: 12 Scout layers, decode at (batch, context) of (1, 32768), (8, 32768), (64, 8192), (1, 131072)
+and (8, 131072), and one prefill of 32,768 tokens, each with its roofline fraction.
 `--workload cpu_baseline` times, on the host's cores, the reference's own unmodified CPU engine (compiled from
 DIR with tests/golden/ref_harness.cpp, token by token as its generate loop runs it,
 src/engine/llama4_cpu_engine.cpp:516-566) and this repository's plain implementation at the two tiny
@@ -129,11 +131,17 @@ def layer_weight_bytes(c, touched_experts: float) -> float:
 
 
 def decode_step_bytes(c, layers, batch, context, touched_experts) -> float:
-    """Bytes one decode step has to read: every weight it uses once and the cache of the live requests."""
+    """Bytes one decode step has to read: every weight it uses once and the cache of the live requests (a layer
+    with chunked attention reads the keys of the newest position's chunk only)."""
     H, V = c["hidden_size"], c["vocab_size"]
     kv_per_token = 2 * c["num_key_value_heads"] * c["head_dim"] * 2
+    C, every = c["attention_chunk_size"], c["nope_layer_interval"]
+    keys = 0.0
+    for i in range(layers):
+        nope = every > 0 and (i + 1) % every == 0
+        keys += context if (nope or C <= 0) else (context - 1) % C + 1
     return (layers * layer_weight_bytes(c, touched_experts) + 2.0 * V * H + 2.0 * batch * H
-            + layers * batch * context * kv_per_token)
+            + batch * keys * kv_per_token)
 
 
 def prefill_flops(c, layers, n_tokens) -> float:
@@ -419,6 +427,94 @@ def run_workload(args) -> dict:
             "clocks": clock_rec}
 
 
+def run_contexts(args) -> dict:
+    """Decode at longer contexts and a long single prefill, 12 layers of Scout's sizes: (batch, context) of
+    (1, 32768), (8, 32768), (64, 8192), (1, 131072), (8, 131072), and a prefill of one 32,768-token prompt.  Every
+    cache is filled by a real prefill; decode steps are device-timed as in the default run; the bytes of a step
+    count every weight once (experts by the expected number touched under uniform routing) and the keys and
+    values that each layer's window lets through."""
+    import torch
+    from cpi_b200.api import Model
+    from cpi_b200.csrc import lib as K
+    from cpi_b200.engine import StepEntry
+    pk = peaks()
+    cfg = dict(SCOUT)
+    L = 12
+    cfg["num_hidden_layers"] = L
+    V, E = cfg["vocab_size"], cfg["num_local_experts"]
+    g = torch.Generator().manual_seed(7)
+    out = {"metric": "decode tok/s at longer contexts (12 layers of Llama4 Scout sizes, bf16, random weights)",
+           "unit": "tok/s", "n_gpus": 1, "dtype": "bf16", "impl": "cpi_b200", "higher_is_better": True,
+           "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)",
+           "config": {"model": "llama4-scout-layer-sizes", "layers": L, "layers_full_model": FULL_LAYERS,
+                      "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+                      "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "experts": E,
+                      "expert_inter": cfg["intermediate_size"], "vocab": V, "chunk": cfg["attention_chunk_size"],
+                      "nope_interval": cfg["nope_layer_interval"], "parallelism": "single-gpu"},
+           "points": {}, "clocks": None}
+    steps, warm = 16, 4
+    clocks = ClockSampler()
+    clocks.start()
+    for batch, ctx in ((1, 32768), (8, 32768), (64, 8192), (1, 131072), (8, 131072)):
+        model = Model.random(cfg, seed=0, dtype="bfloat16", max_batch=batch, max_context=ctx + 64, device="cuda:0")
+        eng = model.engine
+        plen = ctx - steps - warm
+        slots = [eng.acquire_slot() for _ in range(batch)]
+        for s in slots:                                   # one prompt at a time: the pieces stay 8,192 tokens
+            eng.step([StepEntry(s, torch.randint(0, V, (plen,), generator=g).tolist(), [])])
+        tok = torch.empty(batch, dtype=torch.int32, device="cuda:0")
+        feed = [torch.randint(0, V, (batch,), generator=g).tolist() for _ in range(steps + warm)]
+
+        def one(i):
+            lg = eng.step([StepEntry(s, [feed[i][j]], [0]) for j, s in enumerate(slots)])
+            K.argmax(lg, tok)
+
+        for i in range(warm):
+            one(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warm, warm + steps):
+            one(i)
+        e1.record()
+        torch.cuda.synchronize()
+        eng.check_device_errors()
+        ms = e0.elapsed_time(e1) / steps
+        touched = E * (1.0 - (1.0 - 1.0 / E) ** batch)
+        nbytes = decode_step_bytes(cfg, L, batch, ctx - steps / 2, touched)
+        out["points"][f"decode_b{batch}_ctx{ctx}"] = {
+            "tok_s": round(batch / (ms / 1e3), 1), "ms_per_step": round(ms, 3),
+            "roofline_frac": round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+            "cache_gb_held": round(sum(g_.k.numel() * 2 * 2 for g_ in eng.cache.groups) / 1e9, 1)}
+        if (batch, ctx) == (1, 32768):                    # the long single prefill, on the same model
+            for s in slots:
+                eng.release_slot(s)
+            slots = []
+            times = []
+            for r in range(2):
+                s = eng.acquire_slot()
+                p = torch.randint(0, V, (32768,), generator=g).tolist()
+                e0.record()
+                eng.step([StepEntry(s, p, [32767])])
+                e1.record()
+                torch.cuda.synchronize()
+                times.append(e0.elapsed_time(e1))
+                eng.release_slot(s)
+            pms = min(times)
+            # flops of 12 layers at 32,768 tokens: the linear parts per token, attention by each layer's window
+            fl = prefill_flops(cfg, L, 32768)
+            out["points"]["prefill_1x32768"] = {"tok_s": round(32768 / (pms / 1e3), 1), "ms": round(pms, 2),
+                                                "frac": round(fl / (pms / 1e3) / (pk["bf16_tflops"] * 1e12), 4),
+                                                "peak": f"bf16_tflops (burst, {pk['source']})"}
+        for s in slots:
+            eng.release_slot(s)
+        del model, eng
+        torch.cuda.empty_cache()
+    out["clocks"] = clocks.stop()
+    out["value"] = out["points"]["decode_b8_ctx32768"]["tok_s"]
+    return out
+
+
 def run_cpu_baseline(args) -> dict:
     """Tokens per second on the host's cores at the two tiny configurations inside what the reference's engine
     computes: the reference's own CPU engine (unmodified, compiled with tests/golden/ref_harness.cpp; one
@@ -510,7 +606,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--skip-points", action="store_true")
-    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "cpu_baseline"], default="scout24")
+    ap.add_argument("--workload", choices=["scout24", "maverick4", "long131k", "contexts", "cpu_baseline"],
+                    default="scout24")
     ap.add_argument("--reference-root", default=os.environ.get("CPI_REFERENCE_ROOT"),
                     help="a checkout of kurulav1/cpi (for --workload cpu_baseline)")
     args = ap.parse_args()
@@ -524,6 +621,9 @@ def main() -> int:
         print(json.dumps({"error": "cpi_b200 is a single-GPU library: run with --gpus 1", "n_gpus": args.gpus}))
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload == "contexts":
+        print(json.dumps(run_contexts(args)))
+        return 0
     print(json.dumps(run(args) if args.workload == "scout24" else run_workload(args)))
     return 0
 

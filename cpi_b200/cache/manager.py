@@ -174,7 +174,7 @@ class CacheManager:
 
     def __init__(self, kv_requirements: dict, state_requirements: dict, *, max_tokens: int,
                  max_seqs: Optional[int] = None, max_seq_len: Optional[int] = None, page_size: int = 64,
-                 dtype: torch.dtype = torch.bfloat16, device="cuda"):
+                 dtype: torch.dtype = torch.bfloat16, device="cuda", max_step_tokens: Optional[int] = None):
         if page_size < 1 or max_tokens < 1:
             raise CacheError("page_size and max_tokens must be positive")
         self.page_size = page_size
@@ -186,7 +186,11 @@ class CacheManager:
         by_req: dict = {}
         for entry, req in sorted(kv_requirements.items()):
             by_req.setdefault(req, []).append(entry)
-        self.groups = [KVGroup(req, entries, self.n_pages, page_size, self.max_slots, self.max_blocks,
+        # A group with a window never holds more of a sequence than the window and the step that is being
+        # added (pages before the window are given back when a step starts), so its storage is sized for
+        # that and not for whole sequences: `max_step_tokens` is the most tokens one step brings a sequence.
+        self.max_step_tokens = max_step_tokens
+        self.groups = [KVGroup(req, entries, self.pages_for(req), page_size, self.max_slots, self.max_blocks,
                                dtype, device) for req, entries in by_req.items()]
         self.group_of_entry = {e: g for g in self.groups for e in g.entries}
         self.state: dict = {}
@@ -197,6 +201,15 @@ class CacheManager:
         self._free_slots = list(range(self.max_slots - 1, -1, -1))
         self._live = [False] * self.max_slots
         self.lengths = [0] * self.max_slots
+
+    def pages_for(self, req: KVRequirement) -> int:
+        """Pages that a group of this requirement gets: all of the cache's for full attention; for a window,
+        per sequence the window plus one step, if that is less."""
+        if req.window_kind == "full" or self.max_step_tokens is None or req.window_size <= 0:
+            return self.n_pages
+        span = min(self.max_seq_len, req.window_size - 1 + min(self.max_step_tokens, self.max_seq_len))
+        per_seq = -(-span // self.page_size) + 1          # a span that starts inside a page touches one page more
+        return max(1, min(self.n_pages, self.max_slots * per_seq))
 
     # ---- slots ---------------------------------------------------------------------------------
     @property
@@ -265,7 +278,8 @@ class CacheManager:
                     if free < 0:
                         raise CacheFull(f"the cache is full: {self.tokens_held()} of {self.n_pages * ps} "
                                         f"positions are held by {len(self.live_slots())} sequences and the step "
-                                        f"needs more than the rest")
+                                        f"needs more than the rest (group with window '{g.req.window_kind}': "
+                                        f"{g.pool.n_pages} pages)")
                     at[s] = length + n
 
     def prepare_step(self, slots: list, n_new: list) -> list:

@@ -57,10 +57,11 @@ class Engine:
         self.model = DecoderModel(spec, self.dtype, self.device, self.ws)
         self.model.load(source)
         kv, state = self.model.cache_requirements()
-        self.cache = CacheManager(kv, state, max_tokens=max_tokens, max_seqs=max_seqs, max_seq_len=max_seq_len,
-                                  page_size=page_size, dtype=self.dtype, device=self.device)
-        self.stager = BatchStager(self.device)
         self.max_step_tokens = max(1, int(max_step_tokens))
+        self.cache = CacheManager(kv, state, max_tokens=max_tokens, max_seqs=max_seqs, max_seq_len=max_seq_len,
+                                  page_size=page_size, dtype=self.dtype, device=self.device,
+                                  max_step_tokens=self.max_step_tokens)
+        self.stager = BatchStager(self.device)
         self.steps_run = 0
         # Decode steps (one token per sequence) are captured into CUDA graphs, one per (sequences, wanted
         # rows, context bucket): the first step of a kind runs eagerly, the second is captured, later ones

@@ -185,3 +185,28 @@ def test_a_group_stores_the_streams_its_requirement_names():
     with pytest.raises(CacheError, match="twice"):
         CacheManager({0: KVRequirement(0, 0, streams=(("a", 1, 4), ("a", 1, 4)))}, {}, max_tokens=16, page_size=16,
                      device="cpu", dtype=torch.float32)
+
+
+def test_a_windowed_group_is_sized_for_its_window_and_one_step():
+    """Told the most tokens a step brings, the cache gives a group with a window only the pages that a sequence can
+    hold there at a time (the window and the step being added), not whole sequences; what the window has left behind
+    is given back as a sequence grows, so a long sequence passes through."""
+    import torch
+    full, chunk = KVRequirement(2, 16), KVRequirement(2, 16, "chunk", 64)
+    m = CacheManager({0: full, 1: chunk}, {}, max_tokens=8192, max_seqs=2, max_seq_len=4096, page_size=16,
+                     device="cpu", dtype=torch.float32, max_step_tokens=32)
+    g_full, g_chunk = (g for g in m.groups)
+    assert g_full.pool.n_pages == 512
+    assert g_chunk.pool.n_pages == 2 * (-(-(63 + 32) // 16) + 1) == 14
+    a, b = m.acquire(), m.acquire()
+    for _ in range(59):                                       # 1,888 positions each, 32 at a time
+        m.prepare_step([a, b], [32, 32]); m.commit_step([a, b], [32, 32])
+        assert g_chunk.pages_held() <= 14
+    m.check_consistency()
+    assert g_full.pages_held() == 2 * 118
+    with pytest.raises(CacheFull, match="chunk"):             # a step larger than it was told does not fit the window's group
+        m.prepare_step([a], [200])
+    assert g_full.pages_held() == 2 * 118 and m.lengths[a] == 1888
+    # without the figure every group holds whole sequences, as before
+    n = CacheManager({0: full, 1: chunk}, {}, max_tokens=4096, max_seqs=2, page_size=16, device="cpu", dtype=torch.float32)
+    assert [g.pool.n_pages for g in n.groups] == [256, 256]
