@@ -350,7 +350,6 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
 #pragma unroll
         for (int j = 1; j < BKV / 16; ++j)
           umma_bf16_a_tmem_c<true>(od, pa + j * 8, dv + (uint64_t)(j * (2048 >> 4)), idesc_o);
-        umma_commit(&o_done[x]);
         if (release) umma_commit(&kv_empty[vs[x]]);
       }
       __syncwarp();
@@ -375,6 +374,9 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
       if (ok && b_now) ok = issue_pv(1, true);
       if (ok && b_next) ok = issue_qk(1, true);
     }
+    // every product has been issued: one arrival says that O of both query tiles is complete
+    if (ok && elect_one()) { umma_commit(&o_done[0]); umma_commit(&o_done[1]); }
+    __syncwarp();
   } else {
     // ---- softmax: warps 0-3 own query tile A, warps 4-7 tile B; thread r of a group owns query row r and all
     //      128 key columns of a tile (a warp may touch the 32 lanes of tensor memory given by its number modulo
@@ -467,10 +469,8 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
         const float m_new = grow ? mx : m_ref;
         const float f = exp2f(m_ref - m_new);
         if (j > 0) {
-          // every P V issued so far for this query tile must have landed
-          okl = __all_sync(0xffffffffu, mbar_wait(&o_done[x], (j - 1) & 1, abort_flag));
-          if (!okl) break;
-          fence_after_sync();
+          // Every P V issued so far for this query tile has landed: the Q K^T whose S was waited for above was
+          // issued after the last of them, and its arrival covers everything issued before it.
 #pragma unroll 1
           for (int c = 0; c < D; c += 32) {
             float v[32];
@@ -494,7 +494,7 @@ __global__ void __launch_bounds__(320) attention_prefill_kernel(const __grid_con
     }
     // the output: O / l once the last P V is done
     ok = okl && !abort_s && j > 0;
-    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_done[x], (j - 1) & 1, abort_flag));
+    ok = __all_sync(0xffffffffu, ok && mbar_wait(&o_done[x], 0, abort_flag));
     fence_after_sync();
     if (ok) {
       const float inv = 1.0f / fmaxf(l_run, 1e-20f);
