@@ -253,6 +253,41 @@ def gemm_tc_pair(a, w, out, mode=MODE_STORE, *, m_rows=None, out_rows=None, row_
     return True
 
 
+# ---- load time ----------------------------------------------------------------------------------------------
+def random_normal(out, start, seed, std, table):
+    """out.view(-1)[k] = table[hash(seed, start + k)] * std, rounded to out's dtype (float32 or bfloat16), for a
+    contiguous CUDA tensor; `table`: float32 [65536] on the same device."""
+    _need_cuda(out, table)
+    assert out.is_contiguous() and table.dtype == torch.float32 and table.numel() == 65536 and table.is_contiguous()
+    rc = load().cpi_random_normal(_p(out), c_int(dtype_code(out.dtype)), c_long(int(start)), c_long(out.numel()),
+                                  ctypes.c_ulonglong(int(seed) & 0xFFFFFFFFFFFFFFFF), c_float(std), _p(table), _stream())
+    if rc:
+        raise KernelError(load().cpi_last_error().decode())
+
+
+def widen_f16(src, dst):
+    """dst (float32) = src (float16), exactly; contiguous CUDA tensors of equal size."""
+    _need_cuda(src, dst)
+    assert src.dtype == torch.float16 and dst.dtype == torch.float32 and src.is_contiguous() and dst.is_contiguous()
+    assert src.numel() == dst.numel()
+    if load().cpi_widen_f16(_p(src), _p(dst), c_long(src.numel()), _stream()):
+        raise KernelError(load().cpi_last_error().decode())
+
+
+def transpose_last2(src, dst=None):
+    """dst [..., c, r] = src [..., r, c] for a contiguous CUDA tensor of 2- or 4-byte elements."""
+    _need_cuda(src, dst)
+    assert src.is_contiguous() and src.dim() >= 2 and src.element_size() in (2, 4)
+    r, c = src.shape[-2], src.shape[-1]
+    g = src.numel() // (r * c) if src.numel() else 0
+    if dst is None:
+        dst = torch.empty(*src.shape[:-2], c, r, dtype=src.dtype, device=src.device)
+    assert dst.is_contiguous() and dst.dtype == src.dtype and dst.numel() == src.numel()
+    if load().cpi_transpose(_p(src), _p(dst), c_int(src.element_size()), c_long(g), c_int(r), c_int(c), _stream()):
+        raise KernelError(load().cpi_last_error().decode())
+    return dst
+
+
 def gather_rows(src, rows, dst):
     """dst[r] = src[rows[r]] for 2-D tensors whose rows are multiples of 16 bytes."""
     _need_cuda(src, rows, dst)

@@ -31,6 +31,13 @@ def _stack(a, b):
     return torch.cat([a.to(dt), b.to(dt)], dim=0).contiguous()
 
 
+def _turned(t):
+    """[E, in, out] as stored -> [E, out, in], contiguous (the library's transposing kernel on a GPU)."""
+    if t.is_cuda and t.element_size() in (2, 4):
+        return K.transpose_last2(t.contiguous())
+    return t.transpose(1, 2).contiguous()
+
+
 @register_feed_forward("dense_swiglu")
 class DenseSwiGLU(FeedForward):
     graph_safe = True
@@ -105,12 +112,8 @@ class MoESwiGLU(FeedForward):
 
     def load(self, source, device):
         self.w_router = source.get(self.n_router, device).contiguous()
-        t = source.get(self.n_gate_up, device)
-        self.w_gate_up = t.transpose(1, 2).contiguous()          # [E, 2I, H]
-        del t
-        t = source.get(self.n_down, device)
-        self.w_down = t.transpose(1, 2).contiguous()             # [E, H, I]
-        del t
+        self.w_gate_up = _turned(source.get(self.n_gate_up, device))          # [E, 2I, H]
+        self.w_down = _turned(source.get(self.n_down, device))                # [E, H, I]
         if self.shared is not None:
             self.shared.load(source, device)
 

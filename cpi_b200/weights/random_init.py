@@ -44,6 +44,16 @@ def _normal_table() -> torch.Tensor:
     return _TABLE
 
 
+_TABLE_DEV: dict = {}
+
+
+def _normal_table_on(device) -> torch.Tensor:
+    key = str(device)
+    if key not in _TABLE_DEV:
+        _TABLE_DEV[key] = _normal_table().to(device).contiguous()
+    return _TABLE_DEV[key]
+
+
 def counter_normal(tensor_seed: int, start: int, n: int, std: float, device) -> torch.Tensor:
     """float32 [n]: the draws number start .. start + n - 1 of the stream `tensor_seed`.  Integer mixing
     (64-bit multiplications wrap and shifts are made logical by a mask: the same on every device), 16 bits
@@ -86,6 +96,11 @@ class RandomSource(WeightSource):
             return torch.ones(r.shape, dtype=self.dtype, device=device)
         ts = _tensor_seed(self.seed, name)
         out = torch.empty(r.shape, dtype=self.dtype, device=device)
+        if device.type == "cuda" and self.dtype in (torch.bfloat16, torch.float32):
+            # on a GPU the kernel library draws the tensor in place: the same integer arithmetic, the same bits
+            from ..csrc import lib as K
+            K.random_normal(out, 0, ts, self.std, _normal_table_on(device))
+            return out
         flat = out.view(-1)
         step = 1 << 26                     # bound the int64 staging buffers
         for i in range(0, flat.numel(), step):

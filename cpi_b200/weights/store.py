@@ -91,6 +91,13 @@ class SafetensorsSource(WeightSource):
         kd = kept_dtype(t.dtype)
         if torch.device(device).type == "cpu":
             return t.to(kd).clone() if t.dtype == kd else t.to(kd)
+        if t.dtype == torch.float16 and kd == torch.float32:
+            # the stored bytes go up as they are and are widened on the device by the kernel library
+            from ..csrc import lib as K
+            raw = t.to(device=device, non_blocking=False).contiguous()
+            out = torch.empty(raw.shape, dtype=torch.float32, device=device)
+            K.widen_f16(raw, out)
+            return out
         return t.to(device=device, dtype=kd, non_blocking=False)
 
     def close(self):

@@ -761,3 +761,26 @@ def test_sample_kernel_keeps_the_k_most_probable_with_ties_by_index(V, quantum):
             continue
         assert int(out[r]) == pick, (r, cases[r % len(cases)], int(out[r]), pick)
     assert near <= 2
+
+
+# ------------------------------------------------------------------------------------------------ load time
+def test_load_time_kernels_random_fill_widen_and_transpose():
+    """The kernels that run once at load: the counter-based random fill gives the host generator's bits (any start,
+    any length, both dtypes); float16 is widened exactly; the experts' matrices are turned for odd sizes too."""
+    from cpi_b200.weights.random_init import _normal_table_on, counter_normal
+    table = _normal_table_on(torch.device(DEV))
+    for n, start, seed, std, dt in [(1, 0, 5, 0.02, torch.bfloat16), (1000003, 0, 0x7FFFFFFFFFFFFFFF, 0.05, torch.bfloat16),
+                                    (4099, 123456789012, 42, 1.0, torch.float32), (70000, 7, 1 << 40, 0.02, torch.float32)]:
+        out = torch.empty(n, dtype=dt, device=DEV)
+        K().random_normal(out, start, seed, std, table)
+        ref = counter_normal(seed, start, n, std, "cpu").to(dt)
+        assert torch.equal(out.cpu(), ref), (n, start, seed)
+    h = (torch.randn(5, 77, generator=torch.Generator().manual_seed(1)) * 100).half().to(DEV)
+    h[0, 0], h[0, 1], h[0, 2] = 65504.0, 6e-8, float("-inf")
+    w = torch.empty(5, 77, dtype=torch.float32, device=DEV)
+    K().widen_f16(h, w)
+    assert torch.equal(w, h.float())
+    for shape, dt in [((3, 70, 129), torch.bfloat16), ((1, 33, 31), torch.float32), ((4, 128, 256), torch.bfloat16),
+                      ((65, 100), torch.float32)]:
+        a = rnd(*shape, dtype=dt, seed=9)
+        assert torch.equal(K().transpose_last2(a), a.transpose(-1, -2).contiguous())
