@@ -205,8 +205,11 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
-  pdl_wait();
   volatile int* aborted = &abort_s;
+  // Positions, slots and the page table were put in place by copies that ended before this step's first kernel;
+  // they, and every cache page but the one that holds the newest position, are not written by the kernel before
+  // this one (the head rotation stores the newest position's key and value only).  So the first pages are asked for
+  // BEFORE the wait on that kernel: a block's first page takes ~3 us to arrive, which now passes under its tail.
   const int G = p.n_heads / p.n_kv_heads;
   const int pos = p.token_pos[t];
   const int slot = p.seq_slot[p.token_seq[t]];
@@ -228,8 +231,12 @@ __global__ void __launch_bounds__(NT) attention_decode_kernel(const __grid_const
       tma_load_2d(v_s + st * TILE + h * (PAGE * 64), &map_v, &full_bar[st], h * 64, row0);
     }
   };
+  int asked = 0;                                                     // (thread 0) stages asked for so far
   if (tid == 0)
-    for (int i = 0; i < STAGES && b_begin + i < b_end; ++i) load_tile(b_begin + i, i);
+    for (; asked < STAGES && b_begin + asked < b_end && b_begin + asked != b_hi; ++asked) load_tile(b_begin + asked, asked);
+  pdl_wait();
+  if (tid == 0)
+    for (; asked < STAGES && b_begin + asked < b_end; ++asked) load_tile(b_begin + asked, asked);
 
   // ---- Q fragments: rows = the group's heads (rows >= G are zero) ----
   const int r0 = lane >> 2, j = lane & 3;
