@@ -198,3 +198,54 @@ def test_scout_layer_sizes_through_the_three_schedules(dtype):
     finally:
         if dtype == "bfloat16":
             shutil.rmtree(_dirs.pop("scout"), ignore_errors=True)
+
+
+@pytest.mark.parametrize("name,dtype,seed", [("A", "float32", 0), ("B", "float32", 1), ("B", "bfloat16", 2),
+                                             ("R2", "float32", 3), ("C", "bfloat16", 4), ("C", "bfloat16", 5)])
+def test_drawn_schedules_against_plain(name, dtype, seed):
+    """Schedules drawn from a seed: batches of one to four requests with drawn prompt lengths (a single token
+    among them), drawn places at which logits are wanted, a drawn number of decoded tokens per request so that
+    requests leave the batch at drawn times, and `max_step_tokens` by turns absent, 37, 64 and 129; a cache that holds little more than
+    the largest batch, so that pages and slots go round.  Every recorded row against the plain implementation."""
+    import random
+    rng = random.Random(1000 + seed)
+    longest = 400 if name == "C" else 150
+    V = vocab(name)
+    batches = []
+    for b in range(4):
+        reqs = {}
+        for i in range(rng.randint(1, 4)):
+            p = 1 if rng.random() < 0.15 else rng.randint(2, longest)
+            d = rng.randint(0, 10)
+            reqs[f"b{b}r{i}"] = (tiny.random_tokens(p + d, V, 7000 + 97 * seed + 11 * b + i), p)
+        batches.append(reqs)
+    need = max(sum(-(-len(t) // 64) * 64 for t, _ in reqs.values()) for reqs in batches)
+    cap = (None, 37, 64, 129)[seed % 4]
+    e = make_engine(name, dtype, max_seqs=4, max_tokens=need, **({"max_step_tokens": cap} if cap else {}))
+    rp = Replay(e)
+    positions = {}
+    for reqs in batches:
+        items = []
+        for rid, (t, p) in reqs.items():
+            want = sorted({p - 1} | {rng.randrange(p) for _ in range(rng.randint(0, 6))})
+            items.append((rid, t[:p], want))
+            positions[rid] = list(want)
+        rp.step(items)
+        live, step = dict(reqs), 0
+        while live:
+            for rid in [r for r, (t, p) in live.items() if p + step >= len(t)]:
+                rp.end(rid)
+                del live[rid]
+            if not live:
+                break
+            rp.step([(rid, [t[p + step]], [0]) for rid, (t, p) in live.items()])
+            for rid, (t, p) in live.items():
+                positions[rid].append(p + step)
+            step += 1
+        e.cache.check_consistency()
+        assert e.cache.free_slots == e.cache.max_slots
+    e.check_device_errors()
+    all_reqs = {rid: t for reqs in batches for rid, (t, p) in reqs.items()}
+    worst = compare_with_plain(model_dir(name), all_reqs, rp, dtype, positions)
+    print(f"drawn schedule {seed} ({name} {dtype}, pieces of {cap}): {len(all_reqs)} requests, "
+          f"worst relative error {worst:.3e}")
