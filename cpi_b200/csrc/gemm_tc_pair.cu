@@ -362,6 +362,7 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_persistent_kernel(const __gr
   __shared__ uint32_t tmem_base_s;
   __shared__ int abort_s, n_live_s;
   __shared__ int slot_group[kMaxSlots], slot_t0[kMaxSlots], slot_rows[kMaxSlots];     // groups: the token tiles that hold rows
+  __shared__ short slot_first[kMaxSlots], slot_count[kMaxSlots];                     // ... and their group's first tile and tile count
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   uint8_t* ring = smem;
@@ -375,8 +376,14 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_persistent_kernel(const __gr
     if (tid == 0) {
       int n = 0;
       for (int g = 0; g < p.n_groups; ++g) {
-        const int b = p.group_offsets[g], e = p.group_offsets[g + 1];
-        for (int t = b; t < e && n < kMaxSlots; t += p.bn) { slot_group[n] = g; slot_t0[n] = t; slot_rows[n] = min(p.bn, e - t); ++n; }
+        const int b = p.group_offsets[g], e = p.group_offsets[g + 1], first = n;
+        // a group with more rows than a tile takes is cut into tiles of about equal size (a multiple of 32 rows):
+        // the tile numbers go round the SM pairs, and a full tile beside a nearly empty one would give every
+        // second pair the full ones
+        const int count = (e - b + p.bn - 1) / p.bn;
+        const int per = count > 0 ? (((e - b + count - 1) / count + 31) & ~31) : p.bn;
+        for (int t = b; t < e && n < kMaxSlots; t += per) { slot_group[n] = g; slot_t0[n] = t; slot_rows[n] = min(per, e - t); ++n; }
+        for (int i = first; i < n; ++i) { slot_first[i] = (short)first; slot_count[i] = (short)(n - first); }
       }
       n_live_s = n;
     }
@@ -387,12 +394,17 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_persistent_kernel(const __gr
   const int n_clusters = gridDim.x >> 1, cluster_id = blockIdx.x >> 1;
   const int n_kt = p.k_tiles;
   // tile number -> (first token row, rows, weight pair, group).  Dense: bands of 8 token tiles as in the kernel
-  // above.  Groups: a token tile's weight pairs follow each other (the tile's rows stay in the L2, the weights
-  // are streamed).
+  // above.  Groups: group after group, within a group weight pair after weight pair, and the group's token tiles
+  // for one weight pair next to each other: the SM pairs that run them at the same time share the weights' way
+  // through the L2, so a group's weights are read from memory once however many token tiles it has, and its rows
+  // (a few MB) stay in the L2 while its weight pairs go by.
   auto tile_of = [&](int pid, int& t0, int& n_valid_t, int& pair_n, int& group) {
     if (grouped) {
-      const int slot = pid / n_pairs;
-      pair_n = pid - slot * n_pairs;
+      const int s = pid / n_pairs;                       // a tile of the group (its tiles own n_pairs numbers each)
+      const int first = slot_first[s], count = slot_count[s];
+      const int local = pid - first * n_pairs;
+      pair_n = local / count;
+      const int slot = first + (local - pair_n * count);
       group = slot_group[slot]; t0 = slot_t0[slot]; n_valid_t = slot_rows[slot];
       return;
     }
