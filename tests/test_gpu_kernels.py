@@ -574,7 +574,8 @@ def test_argmax_first_maximum_and_odd_vocabulary():
 
 @pytest.mark.parametrize("NH,NKV,D,window,splits", [(40, 8, 128, ("full", 0), 1), (40, 8, 128, ("full", 0), 7),
                                                     (6, 2, 64, ("chunk", 100), 3), (16, 1, 128, ("sliding", 70), 2),
-                                                    (5, 5, 64, ("chunk", 64), 4)])
+                                                    (5, 5, 64, ("chunk", 64), 4), (40, 8, 128, ("full", 0), 8),
+                                                    (40, 8, 128, ("full", 0), 12), (6, 2, 64, ("sliding", 200), 9)])
 def test_attention_decode_tensor_core_kernel(NH, NKV, D, window, splits):
     page = 64
     lengths = [1, 64, 65, 700, 333, 128]
