@@ -68,6 +68,7 @@ class Model:
         return self.generator.generate(reqs, on_token)
 
     def generate_requests(self, requests: Sequence[GenerationRequest], on_token=None) -> list:
+        """The same for requests that each bring their own length, sampling parameters and stop ids."""
         return self.generator.generate(requests, on_token)
 
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], logits="last"):

@@ -99,7 +99,7 @@ def case_attention_decode(a) -> None:
     pos = torch.full((B,), ctx - 1, dtype=torch.int32, device=DEV)
     base, slots, pages = B * NKV, K.attention_decode_blocks_per_sm(D) * K.sm_count(), -(-ctx // 64)
     splits = a.splits or max(1, min(slots // base if base <= slots else -(-4 * slots // base),
-                                    pages // 4 if base > slots else pages // 2))
+                                    pages // 4, K.MAX_DECODE_SPLITS))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
     fn = lambda: K.attention_decode(q, out, k, v, table, 64, seq, pos, seq, n_heads=NH, n_kv_heads=NKV, head_dim=D,
                                     window_kind=0, window_size=0, scale=D ** -0.5, n_splits=splits)

@@ -45,5 +45,5 @@ extern "C" int cpi_sm_count() { return cpi::sm_count(); }
 
 extern "C" const char* cpi_last_error() { return cpi::g_error; }
 
-// Identifies the build: the loader checks it against the sources it was built from.
+// The calling convention of this library's entry points; the loader refuses a library that answers another number.
 extern "C" int cpi_abi_version() { return 1; }

@@ -641,17 +641,6 @@ extern "C" void cpi_gemm_tc_wait_probe(int spin_limit, int tx_extra) {
   g_tx_extra = tx_extra > 0 ? (uint32_t)tx_extra : 0;
 }
 
-extern "C" int cpi_gemm_tc_max_clusters(int bn, int swiglu, int size) { return tc::max_clusters_for(bn, swiglu != 0, size); }
-extern "C" int cpi_gemm_tc_blocks_per_sm(int bn, int swiglu) {
-  switch (bn) {
-    case 16:  return swiglu ? tc::Variant<16, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<16, tc::kStore, __nv_bfloat16>::blocks_per_sm();
-    case 32:  return swiglu ? tc::Variant<32, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<32, tc::kStore, __nv_bfloat16>::blocks_per_sm();
-    case 64:  return swiglu ? tc::Variant<64, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<64, tc::kStore, __nv_bfloat16>::blocks_per_sm();
-    case 128: return swiglu ? tc::Variant<128, tc::kSwiglu, __nv_bfloat16>::blocks_per_sm() : tc::Variant<128, tc::kStore, __nv_bfloat16>::blocks_per_sm();
-  }
-  return 0;
-}
-
 // Token-tile width and split count for a launch (also used by the caller to size the scratch).
 // tiles_hint = expected token tiles per group (rows per group / bn, rounded up), groups_hint = groups in use.
 extern "C" int cpi_gemm_tc_plan(int T, int N, int K, int n_groups, int swiglu, int* bn_out, int* splits_out,

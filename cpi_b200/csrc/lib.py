@@ -19,6 +19,8 @@ WINDOW_KINDS = {"full": WINDOW_FULL, "chunk": WINDOW_CHUNK, "sliding": WINDOW_SL
 MAX_DECODE_SPLITS = 256          # key splits that the combine kernel of decode attention takes
 PREFILL_TILE_ROWS = 256          # most query rows of one sequence that a block of the prefill attention kernel takes
 
+ABI_VERSION = 1                  # what cpi_abi_version() of a matching library answers
+
 _lib = None
 scratch_generation = 0    # grows whenever a scratch buffer of this module is (re)allocated
 launch_count = 0          # kernels launched through this module since import (bench reports it)
@@ -37,6 +39,9 @@ def load():
         except OSError as e:
             raise KernelError(f"cpi_b200: cannot load the kernel library {path}: {e}") from None
         _lib.cpi_last_error.restype = ctypes.c_char_p
+        if _lib.cpi_abi_version() != ABI_VERSION:
+            raise KernelError(f"cpi_b200: {path} has ABI version {_lib.cpi_abi_version()}, this package "
+                              f"wants {ABI_VERSION}")
     return _lib
 
 
@@ -44,10 +49,6 @@ def kernel_launches() -> int:
     """Kernels this library has launched from host code (graph replays are counted by the engine)."""
     load().cpi_launch_count.restype = c_long
     return int(load().cpi_launch_count())
-
-
-def library_file() -> str:
-    return _build.library_path(build_if_missing=False)
 
 
 def dtype_code(dt: torch.dtype) -> int:

@@ -135,7 +135,7 @@ class AttentionMixer(Mixer):
                 want = slots // base                                # one full wave and no more
             else:
                 want = -(-4 * slots // base)                        # several waves of smaller blocks
-            n_splits = max(1, min(want, pages // 4 if base > slots else pages // 2, K.MAX_DECODE_SPLITS))
+            n_splits = max(1, min(want, pages // 4, K.MAX_DECODE_SPLITS))    # a block takes four pages or more
             K.attention_decode(q, att, k_cache, v_cache, table, page_size, batch.token_seq, batch.token_pos,
                                batch.seq_slot, n_heads=self.nh, n_kv_heads=self.nkv, head_dim=self.d,
                                window_kind=wk, window_size=self.window_size, scale=self.scale, n_splits=n_splits)

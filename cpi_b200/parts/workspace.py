@@ -25,5 +25,3 @@ class Workspace:
             self.generation += 1
         return buf[:n].view(*shape)
 
-    def bytes_held(self) -> int:
-        return sum(b.numel() * b.element_size() for b in self._buffers.values())
