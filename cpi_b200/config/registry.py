@@ -107,6 +107,24 @@ def cli_options() -> list:
     return out
 
 
+PLUGINS_ENV = "CPI_B200_PLUGINS"
+_plugins_loaded = False
+
+
 def _ensure_builtin() -> None:
-    # the built-in architectures register themselves when the package of architectures is imported
+    """The built-in architectures register themselves when the package of architectures is imported.  After
+    them come the modules that the environment variable CPI_B200_PLUGINS names (comma separated, importable
+    names): a module outside this package registers parts and architectures the same way, and every program
+    of the package (the command lines, the replay tool) then knows them by their config.json name."""
+    global _plugins_loaded
     from .. import models  # noqa: F401
+    if _plugins_loaded:
+        return
+    _plugins_loaded = True
+    import importlib
+    import os
+    for name in filter(None, (x.strip() for x in os.environ.get(PLUGINS_ENV, "").split(","))):
+        try:
+            importlib.import_module(name)
+        except ImportError as e:
+            raise ConfigError(f"{PLUGINS_ENV}: cannot import '{name}': {e}") from None
