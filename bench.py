@@ -354,7 +354,7 @@ def run(args) -> dict:
               "decode_ms": {k: round(v / 4, 3) for k, v in ph.get("decode", {}).items()}}
 
     return {
-        "metric": "decode tok/s @ batch 8 (Llama4 Scout layer sizes, bf16, random weights)",
+        "metric": f"decode tok/s @ batch {B} (Llama4 Scout layer sizes, bf16, random weights)",
         "value": round(value, 2), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warm,
         "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: uniform random token ids, random-init weights N(0, 0.02)",
