@@ -185,12 +185,15 @@ def test_replay_tool_runs_an_architecture_from_a_plugin(plugin_dir, name, dtype)
     env = dict(os.environ, CPI_B200_PLUGINS="toy_sliding_arch",
                PYTHONPATH=plugin_dir + os.pathsep + os.environ.get("PYTHONPATH", ""))
     tol = 2e-5 if dtype == "float32" else 2e-2
-    for mode in ("whole", "batched"):
+    # whole; as one batch with the last two tokens one by one; each alone with its last 60 tokens one by one (the
+    # longer requests then decode far past the window, and the window's group gives pages back as they go)
+    for mode, tail in (("whole", 2), ("batched", 2), ("tail32", 60)):
         out = os.path.join(plugin_dir, f"out_{name}_{dtype}_{mode}")
         need = sum(-(-len(t) // 64) * 64 for t in reqs.values())
         r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", dtype,
                             "--out", out, "--max-tokens", str(need), "--trace", trace, "--mode", mode,
-                            "--batch-size", "3", "--tail", "2"], env=env, capture_output=True, text=True, timeout=600)
+                            "--batch-size", "3", "--tail", str(tail)], env=env, capture_output=True, text=True,
+                           timeout=600)
         assert r.returncode == 0, r.stderr[-2000:]
         got = TraceOutput(out)
         worst = 0.0
